@@ -1,0 +1,269 @@
+// Memory-bound kernels around the matrix products: embedding gather,
+// residual add fused with RMSNorm, per-head q/k RMSNorm fused with the NeoX
+// rotation and the cache write, and the gated activation.  Sums of squares,
+// the residual sum and the rotation are float32 whatever the storage type.
+//
+// Semantics restated from the reference's scalar ops: rms_norm_mul
+// (crates/model/src/ops.rs:40-59), rope_neox (ops.rs:142-159), silu
+// (ops.rs:176-178), and the order norm -> rotation -> cache write of
+// crates/model/src/qwen35/cpu.rs:295-323.
+#include "common.cuh"
+
+// ---------------------------------------------------------------------------
+// Embedding gather: h[t,:] = E[tok_t,:] widened to float32 (no scale).
+// ---------------------------------------------------------------------------
+template <typename TW>
+__global__ void embed_kernel(const TW* __restrict__ table, const int* __restrict__ tokens,
+                             float* __restrict__ h, int d, int vocab) {
+  const int t = blockIdx.x;
+  int tok = tokens[t];
+  tok = tok < 0 ? 0 : (tok >= vocab ? vocab - 1 : tok);  // never read outside the table
+  const TW* row = table + (size_t)tok * d;
+  float* out = h + (size_t)t * d;
+  for (int i = threadIdx.x; i < d; i += blockDim.x) out[i] = to_f32(row[i]);
+}
+
+LLMX_API int llmx_embed(const void* table, int table_dtype, const int* tokens, float* h,
+                        int n_tokens, int d, int vocab, cudaStream_t stream) {
+  if (n_tokens <= 0) return 0;
+  if (d <= 0 || vocab <= 0) return LLMX_REFUSED(1);
+  const int threads = d >= 1024 ? 256 : 128;
+  if (table_dtype == LLMX_F32)
+    embed_kernel<float><<<n_tokens, threads, 0, stream>>>((const float*)table, tokens, h, d, vocab);
+  else if (table_dtype == LLMX_BF16)
+    embed_kernel<bf16><<<n_tokens, threads, 0, stream>>>((const bf16*)table, tokens, h, d, vocab);
+  else
+    return LLMX_REFUSED(2);
+  return LLMX_LAUNCH_STATUS();
+}
+
+// ---------------------------------------------------------------------------
+// Residual add + RMSNorm.  For output row r (source row t = rows ? rows[r] : r):
+//   v = h[t,:] + sum_s delta[s][t,:]      (partials added in the order s = 0..S-1)
+//   if write_h: h[t,:] = v
+//   out[r,:] = v * (1/sqrt(mean(v^2)+eps)) * gain
+// One block per row; the row is staged in shared memory as float32.
+// ---------------------------------------------------------------------------
+#define NORM_THREADS 256
+
+template <typename TD, typename TO>
+__global__ void add_rms_norm_kernel(float* __restrict__ h, const TD* __restrict__ delta, int n_split,
+                                    size_t split_stride, const int* __restrict__ rows,
+                                    const float* __restrict__ gain, float eps, TO* __restrict__ out,
+                                    int d, int write_h) {
+  extern __shared__ float row_buf[];
+  __shared__ float red[32];
+  const int r = blockIdx.x;
+  const int t = rows ? rows[r] : r;
+  float* hrow = h + (size_t)t * d;
+  float ss = 0.f;
+  for (int i = threadIdx.x; i < d; i += NORM_THREADS) {
+    float v = hrow[i];
+    if (delta) {
+      const TD* p = delta + (size_t)t * d + i;
+      for (int s = 0; s < n_split; ++s) v += to_f32(p[s * split_stride]);
+      if (write_h) hrow[i] = v;
+    }
+    row_buf[i] = v;
+    ss += v * v;
+  }
+  const float total = block_sum(ss, red);
+  const float scale = 1.0f / sqrtf(total / (float)d + eps);
+  if (out) {
+    TO* orow = out + (size_t)r * d;
+    for (int i = threadIdx.x; i < d; i += NORM_THREADS) orow[i] = from_f32<TO>((row_buf[i] * scale) * gain[i]);
+  }
+}
+
+template <typename TD, typename TO>
+static int launch_add_rms_norm(float* h, const void* delta, int n_split, size_t split_stride, const int* rows,
+                               int n_rows, const float* gain, float eps, void* out, int d, int write_h,
+                               cudaStream_t stream) {
+  const size_t smem = (size_t)d * sizeof(float);
+  auto kernel = add_rms_norm_kernel<TD, TO>;
+  if (smem > 48 * 1024) {
+    if (smem > 200 * 1024) return LLMX_REFUSED(3);
+    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return (int)e;
+  }
+  kernel<<<n_rows, NORM_THREADS, smem, stream>>>(h, (const TD*)delta, n_split, split_stride, rows, gain, eps,
+                                                 (TO*)out, d, write_h);
+  return LLMX_LAUNCH_STATUS();
+}
+
+LLMX_API int llmx_add_rms_norm(float* h, const void* delta, int delta_dtype, int n_split, long long split_stride,
+                               const int* rows, int n_rows, const float* gain, float eps, void* out,
+                               int out_dtype, int d, int write_h, cudaStream_t stream) {
+  if (n_rows <= 0) return 0;
+  if (d <= 0 || (delta && n_split < 1)) return LLMX_REFUSED(1);
+#define CASE(TD, TO) \
+  return launch_add_rms_norm<TD, TO>(h, delta, n_split, (size_t)split_stride, rows, n_rows, gain, eps, out, d, write_h, stream)
+  if (delta_dtype == LLMX_F32 && out_dtype == LLMX_F32) CASE(float, float);
+  if (delta_dtype == LLMX_F32 && out_dtype == LLMX_BF16) CASE(float, bf16);
+  if (delta_dtype == LLMX_BF16 && out_dtype == LLMX_F32) CASE(bf16, float);
+  if (delta_dtype == LLMX_BF16 && out_dtype == LLMX_BF16) CASE(bf16, bf16);
+#undef CASE
+  return LLMX_REFUSED(2);
+}
+
+// ---------------------------------------------------------------------------
+// Per-head RMSNorm of q and k, NeoX rotation of both, and the cache write of
+// k and v.  Input qkv [T, (H+2G)*D]: q heads, then k heads, then v heads.
+// One warp per (token, head).  The normalised head is staged in shared memory
+// so that a dim can read its rotation partner (i, i + n_rot/2) at any D.
+// cos/sin tables are [max_pos, n_rot/2] float32, made on the host in float64.
+// ---------------------------------------------------------------------------
+#define QKV_WARPS 4
+
+template <typename TA, typename TC>
+__global__ void qk_norm_rope_cache_kernel(const TA* __restrict__ qkv, TA* __restrict__ q_out,
+                                          TC* __restrict__ k_cache, TC* __restrict__ v_cache,
+                                          const int* __restrict__ block_table, int table_width,
+                                          const int* __restrict__ token_seq, const int* __restrict__ token_pos,
+                                          const float* __restrict__ q_gain, const float* __restrict__ k_gain,
+                                          float eps, const float* __restrict__ cos_t,
+                                          const float* __restrict__ sin_t, int n_rot, int H, int G, int D,
+                                          int write_cache) {
+  extern __shared__ float head_buf[];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int t = blockIdx.y;
+  const int slot = blockIdx.x * QKV_WARPS + warp;  // which head of the fused row
+  const int n_slots = write_cache ? H + 2 * G : H;
+  if (slot >= n_slots) return;
+  float* buf = head_buf + warp * D;
+  const TA* src = qkv + (size_t)t * (H + 2 * G) * D + (size_t)slot * D;
+  const int pos = token_pos[t];
+  const bool is_q = slot < H, is_k = !is_q && slot < H + G;
+
+  TC* cache_row = nullptr;
+  if (!is_q) {
+    const int g = is_k ? slot - H : slot - H - G;
+    const int page = block_table[(size_t)token_seq[t] * table_width + pos / LLMX_PAGE];
+    cache_row = (is_k ? k_cache : v_cache) + cache_row_offset(page, g, pos % LLMX_PAGE, G, D);
+  }
+  if (!is_q && !is_k) {  // v: stored as it is
+    for (int i = lane; i < D; i += 32) cache_row[i] = from_f32<TC>(to_f32(src[i]));
+    return;
+  }
+  const float* gain = is_q ? q_gain : k_gain;
+  float ss = 0.f;
+  for (int i = lane; i < D; i += 32) {
+    const float v = to_f32(src[i]);
+    buf[i] = v;
+    ss += v * v;
+  }
+  if (gain) {
+    const float scale = 1.0f / sqrtf(warp_sum(ss) / (float)D + eps);
+    for (int i = lane; i < D; i += 32) buf[i] = (buf[i] * scale) * gain[i];
+  }
+  __syncwarp();
+  const int half = n_rot >> 1;
+  const float* c = cos_t ? cos_t + (size_t)pos * half : nullptr;
+  const float* s = sin_t ? sin_t + (size_t)pos * half : nullptr;
+  TA* qrow = is_q ? q_out + (size_t)t * H * D + (size_t)slot * D : nullptr;
+  for (int i = lane; i < D; i += 32) {
+    float v = buf[i];
+    if (i < half) {
+      v = buf[i] * c[i] - buf[i + half] * s[i];
+    } else if (i < n_rot) {
+      v = buf[i - half] * s[i - half] + buf[i] * c[i - half];
+    }
+    if (is_q) qrow[i] = from_f32<TA>(v);
+    else cache_row[i] = from_f32<TC>(v);
+  }
+}
+
+LLMX_API int llmx_qk_norm_rope_cache(const void* qkv, void* q_out, int act_dtype, void* k_cache, void* v_cache,
+                                     int cache_dtype, const int* block_table, int table_width,
+                                     const int* token_seq, const int* token_pos, const float* q_gain,
+                                     const float* k_gain, float eps, const float* cos_t, const float* sin_t,
+                                     int n_rot, int n_tokens, int H, int G, int D, int write_cache,
+                                     cudaStream_t stream) {
+  if (n_tokens <= 0) return 0;
+  if (H <= 0 || G <= 0 || D <= 0 || n_rot < 0 || n_rot > D || (n_rot & 1)) return LLMX_REFUSED(1);
+  if (n_rot > 0 && (!cos_t || !sin_t)) return LLMX_REFUSED(4);
+  const int n_slots = write_cache ? H + 2 * G : H;
+  dim3 grid((n_slots + QKV_WARPS - 1) / QKV_WARPS, n_tokens);
+  const size_t smem = (size_t)QKV_WARPS * D * sizeof(float);
+  if (smem > 48 * 1024) return LLMX_REFUSED(3);
+#define CASE(TA, TC)                                                                                           \
+  qk_norm_rope_cache_kernel<TA, TC><<<grid, QKV_WARPS * 32, smem, stream>>>(                                   \
+      (const TA*)qkv, (TA*)q_out, (TC*)k_cache, (TC*)v_cache, block_table, table_width, token_seq, token_pos, \
+      q_gain, k_gain, eps, cos_t, sin_t, n_rot, H, G, D, write_cache)
+  if (act_dtype == LLMX_F32 && cache_dtype == LLMX_F32) CASE(float, float);
+  else if (act_dtype == LLMX_BF16 && cache_dtype == LLMX_BF16) CASE(bf16, bf16);
+  else if (act_dtype == LLMX_F32 && cache_dtype == LLMX_BF16) CASE(float, bf16);
+  else if (act_dtype == LLMX_BF16 && cache_dtype == LLMX_F32) CASE(bf16, float);
+  else return LLMX_REFUSED(2);
+#undef CASE
+  return LLMX_LAUNCH_STATUS();
+}
+
+// ---------------------------------------------------------------------------
+// Gated activation: act[t,f] = silu(g) * u with g = sum_s gu[s][t,f] and
+// u = sum_s gu[s][t,F+f]; silu(x) = x / (1 + exp(-x)) in float32.
+// ---------------------------------------------------------------------------
+template <typename TI, typename TO>
+__global__ void silu_gate_kernel(const TI* __restrict__ gu, int n_split, size_t split_stride,
+                                 TO* __restrict__ act, int n_tokens, int F) {
+  const size_t n = (size_t)n_tokens * F;
+  for (size_t idx = blockIdx.x * (size_t)blockDim.x + threadIdx.x; idx < n; idx += (size_t)gridDim.x * blockDim.x) {
+    const size_t t = idx / F, f = idx - t * F;
+    const TI* p = gu + t * 2 * (size_t)F + f;
+    float g = 0.f, u = 0.f;
+    for (int s = 0; s < n_split; ++s) {
+      g += to_f32(p[s * split_stride]);
+      u += to_f32(p[s * split_stride + F]);
+    }
+    act[idx] = from_f32<TO>((g / (1.0f + expf(-g))) * u);
+  }
+}
+
+LLMX_API int llmx_silu_gate(const void* gu, int in_dtype, int n_split, long long split_stride, void* act,
+                            int out_dtype, int n_tokens, int F, cudaStream_t stream) {
+  if (n_tokens <= 0) return 0;
+  if (F <= 0 || n_split < 1) return LLMX_REFUSED(1);
+  const size_t n = (size_t)n_tokens * F;
+  const int threads = 256;
+  const int blocks = (int)((n + threads - 1) / threads < 148 * 16 ? (n + threads - 1) / threads : 148 * 16);
+#define CASE(TI, TO) \
+  silu_gate_kernel<TI, TO><<<blocks, threads, 0, stream>>>((const TI*)gu, n_split, (size_t)split_stride, (TO*)act, n_tokens, F)
+  if (in_dtype == LLMX_F32 && out_dtype == LLMX_F32) CASE(float, float);
+  else if (in_dtype == LLMX_F32 && out_dtype == LLMX_BF16) CASE(float, bf16);
+  else if (in_dtype == LLMX_BF16 && out_dtype == LLMX_BF16) CASE(bf16, bf16);
+  else if (in_dtype == LLMX_BF16 && out_dtype == LLMX_F32) CASE(bf16, float);
+  else return LLMX_REFUSED(2);
+#undef CASE
+  return LLMX_LAUNCH_STATUS();
+}
+
+// ---------------------------------------------------------------------------
+// Sum of split partials into one tensor: out[i] = sum_s in[s][i].
+// ---------------------------------------------------------------------------
+template <typename TI, typename TO>
+__global__ void sum_splits_kernel(const TI* __restrict__ in, int n_split, size_t split_stride, TO* __restrict__ out,
+                                  size_t n) {
+  for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
+    float v = 0.f;
+    for (int s = 0; s < n_split; ++s) v += to_f32(in[s * split_stride + i]);
+    out[i] = from_f32<TO>(v);
+  }
+}
+
+LLMX_API int llmx_sum_splits(const void* in, int in_dtype, int n_split, long long split_stride, void* out,
+                             int out_dtype, long long n, cudaStream_t stream) {
+  if (n <= 0) return 0;
+  if (n_split < 1) return LLMX_REFUSED(1);
+  const int threads = 256;
+  const long long want = (n + threads - 1) / threads;
+  const int blocks = (int)(want < 148 * 16 ? want : 148 * 16);
+#define CASE(TI, TO) \
+  sum_splits_kernel<TI, TO><<<blocks, threads, 0, stream>>>((const TI*)in, n_split, (size_t)split_stride, (TO*)out, (size_t)n)
+  if (in_dtype == LLMX_F32 && out_dtype == LLMX_F32) CASE(float, float);
+  else if (in_dtype == LLMX_F32 && out_dtype == LLMX_BF16) CASE(float, bf16);
+  else if (in_dtype == LLMX_BF16 && out_dtype == LLMX_BF16) CASE(bf16, bf16);
+  else if (in_dtype == LLMX_BF16 && out_dtype == LLMX_F32) CASE(bf16, float);
+  else return LLMX_REFUSED(2);
+#undef CASE
+  return LLMX_LAUNCH_STATUS();
+}

@@ -1,0 +1,160 @@
+"""The engine: a model, its cache and the one step function.
+
+``step`` takes a batch of sequences that all start together (whole prompts of
+unequal lengths) or all go on (one token each, or several), runs only the
+tokens it is given as one batch, from the cache, and returns the logits at
+the wanted places.  Limits are checked before anything is launched, as the
+reference checks its forward (crates/gpu/src/qwen35.rs:1212-1222,
+crates/model/src/qwen35/cpu.rs:119-125).
+"""
+
+from __future__ import annotations
+
+import sys
+import time
+from dataclasses import dataclass
+from pathlib import Path
+from typing import Optional
+
+import torch
+
+from .. import kernels
+from ..cache import PAGE, Cache
+from ..config import read_config
+from ..errors import CacheMisuse, ContextOverflow
+from ..parts import Runtime
+from ..weights import load_checkpoint, random_tensors_on_device
+from .batch import StepBuffers, build_host_arrays
+from .model import DecoderModel
+
+
+@dataclass
+class LoadOptions:
+    """How a model is loaded (the reference sizes context and batch at load
+    time too, llmoxide/src/backend.rs:112-139).
+
+    ``max_tokens``: the most tokens live sequences hold at any time, each
+    sequence's count rounded up to a multiple of 64; it sizes the cache.
+    ``max_batch``: most sequences alive at once (slots).
+    ``max_step_tokens``: most tokens one step may bring."""
+
+    dtype: str = "bfloat16"
+    max_tokens: int = 16384
+    max_batch: int = 256
+    max_step_tokens: int = 16384
+    device: str = "cuda:0"
+    tensor_cores: bool = True
+    cuda_graphs: bool = True
+
+
+class Engine:
+    def __init__(self, config, weights: dict, options: LoadOptions):
+        kernels.require_gpu()
+        self.config, self.options = config, options
+        self.spec = config.to_spec()
+        self.device = torch.device(options.device)
+        torch.cuda.set_device(self.device)
+        max_seq = min(self.spec.max_positions, (options.max_tokens + PAGE - 1) // PAGE * PAGE)
+        self.rt = Runtime(dtype=options.dtype, device=self.device, max_positions=max_seq,
+                          tensor_cores=options.tensor_cores)
+        self.model = DecoderModel(self.spec, weights, self.rt)
+        n_slots = max(1, min(options.max_batch, (options.max_tokens + PAGE - 1) // PAGE))
+        self.cache = Cache(self.model.cache_needs(), n_slots, options.max_tokens, self.rt.cache_dtype,
+                           self.device, max_seq_len=max_seq)
+        self.buffers = StepBuffers(self.device)
+        self.n_steps = 0
+
+    # ---- loading -------------------------------------------------------------
+
+    @classmethod
+    def load(cls, folder, options: Optional[LoadOptions] = None, **kw) -> "Engine":
+        """From a model folder (config.json + model.safetensors); the model is
+        chosen by config.json's architecture name."""
+        options = options or LoadOptions(**kw)
+        kernels.require_gpu()
+        config = read_config(folder)
+        weights = load_checkpoint(folder, config.to_spec(), options.dtype, options.device)
+        return cls(config, weights, options)
+
+    @classmethod
+    def random(cls, config, seed: int = 0, options: Optional[LoadOptions] = None, **kw) -> "Engine":
+        """Random weights made on the device (see ``weights.random_init``)."""
+        options = options or LoadOptions(**kw)
+        kernels.require_gpu()
+        if not hasattr(config, "to_spec"):
+            config = read_config(config)
+        weights = random_tensors_on_device(config.to_spec(), seed, options.dtype, options.device)
+        return cls(config, weights, options)
+
+    # ---- slots -----------------------------------------------------------------
+
+    def acquire(self) -> int:
+        return self.cache.acquire()
+
+    def release(self, slot: int) -> None:
+        self.cache.release(slot)
+
+    def length(self, slot: int) -> int:
+        return self.cache.length(slot)
+
+    # ---- the step --------------------------------------------------------------
+
+    def step(self, entries, want=None) -> torch.Tensor:
+        """``entries``: [(slot, token ids)]; every sequence brings at least one
+        token, appended at its current length.  ``want``: per entry the places
+        among its tokens whose logits are asked for (default: the last).
+        Returns float32 logits [wanted, vocab] on the device, in the order of
+        the entries and of ``want``."""
+        ctx = self._prepare(entries, want)
+        logits = self.model.forward(ctx, self.cache)
+        for slot, toks in entries:
+            self.cache.alloc.commit(slot, len(toks))
+        self.n_steps += 1
+        return logits
+
+    def _prepare(self, entries, want):
+        if not entries:
+            raise ValueError("a step needs at least one sequence")
+        vocab = self.spec.vocab_size
+        seen = set()
+        total = 0
+        for slot, toks in entries:
+            if slot in seen:
+                raise CacheMisuse(f"slot {slot} appears twice in one step")
+            seen.add(slot)
+            if len(toks) == 0:
+                raise ValueError(f"slot {slot} brings no token")
+            lo, hi = min(toks), max(toks)
+            if lo < 0 or hi >= vocab:
+                raise ValueError(f"token id {lo if lo < 0 else hi} is outside the vocabulary of {vocab}")
+            total += len(toks)
+        if total > self.options.max_step_tokens:
+            raise ContextOverflow(total, self.options.max_step_tokens, "step limit (max_step_tokens)")
+        if want is None:
+            want = [[len(t) - 1] for _, t in entries]
+        for (slot, toks), ws in zip(entries, want):
+            for w in ws:
+                if not (0 <= w < len(toks)):
+                    raise ValueError(f"slot {slot}: wanted place {w} is outside its {len(toks)} tokens")
+        alloc = self.cache.alloc
+        lengths = [alloc.length(slot) for slot, _ in entries]
+        # Reserve for every sequence before anything runs; on failure give the
+        # pages of this step back by leaving lengths untouched (pages stay with
+        # their slots and are freed with them).
+        for slot, toks in entries:
+            alloc.reserve(slot, len(toks))
+        n_groups = max(1, self.cache.n_groups())
+        page_rows = [[alloc.page_row(slot, g) for slot, _ in entries] for g in range(n_groups)]
+        lay, buf, facts = build_host_arrays(entries, want, lengths, page_rows, n_groups)
+        return self.buffers.upload(lay, buf, facts)
+
+    # ---- facts -------------------------------------------------------------------
+
+    def info(self) -> dict:
+        """What the reference's ``Info`` carries (llmoxide/src/backend.rs:36-49)."""
+        return dict(architecture=self.spec.architecture, dtype=self.options.dtype, device=str(self.device),
+                    vocab_size=self.spec.vocab_size, hidden_size=self.spec.hidden_size,
+                    n_layers=len(self.spec.blocks), stop_ids=tuple(self.spec.stop_ids),
+                    max_tokens=self.cache.n_pages * PAGE, max_batch=self.cache.n_slots,
+                    max_seq_len=self.cache.alloc.max_seq_len, cache_bytes=self.cache.bytes(),
+                    summary=self.config.summary() if hasattr(self.config, "summary") else "")

@@ -1,0 +1,69 @@
+"""The decoder as data: blocks built from a ``ModelSpec`` through the part
+registries, run in the order of the spec's schedule.  Nothing here names an
+architecture.
+
+Forward of one step, in the reference's order
+(crates/model/src/qwen35/cpu.rs:129-136,138-400,406-416): embedding gather
+without scale; the scheduled layer calls on the float32 residual stream;
+final norm and head on the wanted rows only (the reference takes the last
+row, cpu.rs:410-414)."""
+
+from __future__ import annotations
+
+import torch
+
+from .. import kernels
+from ..cache import Cache
+from ..config.spec import ModelSpec
+from ..parts import Linear, Runtime, build_block
+from ..parts.block import build_part
+from ..parts.registry import NORMS
+
+
+class DecoderModel:
+    def __init__(self, spec: ModelSpec, weights: dict, rt: Runtime):
+        """``weights``: name -> device tensor; the parts take theirs out of it."""
+        self.spec, self.rt = spec, rt
+        self.embedding = weights[spec.embedding.name]
+        head = weights.pop(spec.head.name) if spec.head is not None else self.embedding
+        self.blocks = [build_block(b, weights, rt) for b in spec.blocks]
+        self.final_norm = build_part(NORMS, "norm", spec.final_norm, weights, rt)
+        self.head = Linear(head, rt)
+        weights.pop(spec.embedding.name, None)
+        self._check_schedule()
+
+    def _check_schedule(self):
+        writers = {}
+        for call in self.spec.schedule:
+            if not (0 <= call.layer < len(self.blocks)):
+                raise ValueError(f"the schedule names layer {call.layer}; there are {len(self.blocks)}")
+            if call.writes_cache:
+                writers.setdefault(call.cache, call.layer)
+        for call in self.spec.schedule:
+            if call.cache not in writers:
+                raise ValueError(f"cache entry {call.cache} is read but no scheduled call writes it")
+            if self.blocks[call.layer].cache_need() != self.blocks[writers[call.cache]].cache_need():
+                raise ValueError(f"layer {call.layer} reads cache entry {call.cache} whose writer has other needs")
+        self._writers = writers
+
+    def cache_needs(self) -> list:
+        """Per cache entry: (KVNeed | None, StateNeed | None), from the entry's writer."""
+        n = self.spec.n_cache_entries()
+        missing = [e for e in range(n) if e not in self._writers]
+        if missing:
+            raise ValueError(f"cache entries {missing} are never written")
+        return [self.blocks[self._writers[e]].cache_need() for e in range(n)]
+
+    def forward(self, ctx, cache: Cache) -> torch.Tensor:
+        """float32 logits [n_want, vocab] at ``ctx.want_rows``."""
+        d = self.spec.hidden_size
+        h = torch.empty((ctx.n_tokens, d), dtype=torch.float32, device=self.rt.device)
+        kernels.embed(self.embedding, ctx.tokens, h)
+        pending = None
+        for call in self.spec.schedule:
+            pending = self.blocks[call.layer].forward(h, pending, ctx, cache.view(call.cache), call.writes_cache)
+        n_want = ctx.want_rows.numel()
+        if n_want == 0:
+            return torch.empty((0, self.spec.vocab_size), dtype=torch.float32, device=self.rt.device)
+        x = self.final_norm.add_forward(h, pending, rows=ctx.want_rows, write_h=False)
+        return self.head(x, out_dtype=torch.float32)

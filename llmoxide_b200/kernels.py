@@ -1,0 +1,229 @@
+"""Typed Python faces of the ``extern "C"`` kernel launchers.
+
+Each function checks what the kernel cannot check for itself (device, dtype,
+contiguity, shapes), passes raw pointers and the current CUDA stream, and
+turns a refusal or a launch error into an exception.  Nothing here computes
+on the host and nothing falls back to another implementation.
+"""
+
+from __future__ import annotations
+
+import ctypes
+from ctypes import c_float, c_int, c_longlong, c_void_p
+
+import torch
+
+from .csrc.build import load_library
+from .errors import ExtensionMissing, KernelError, Unsupported
+
+F32, BF16 = 0, 1
+PAGE = 64  # tokens per cache page; the same constant as LLMX_PAGE in common.cuh
+_DTYPE_TAG = {torch.float32: F32, torch.bfloat16: BF16}
+
+_REFUSALS = {
+    1: "a size or stride is out of range",
+    2: "unsupported combination of dtypes",
+    3: "a size exceeds what this kernel's shared memory or grid allows",
+    4: "a required table is missing",
+}
+
+
+def require_gpu() -> None:
+    if not torch.cuda.is_available():
+        raise ExtensionMissing("no CUDA device is available; llmoxide_b200 has no CPU path")
+
+
+def _tag(t: torch.Tensor) -> int:
+    try:
+        return _DTYPE_TAG[t.dtype]
+    except KeyError:
+        raise Unsupported(f"dtype {t.dtype} is not supported by the kernels (float32 and bfloat16 are)") from None
+
+
+def _ptr(t):
+    return c_void_p(0) if t is None else c_void_p(t.data_ptr())
+
+
+def _stream():
+    return c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def _check(code: int, what: str) -> None:
+    if code == 0:
+        return
+    if code < 0:
+        raise Unsupported(f"{what}: refused, {_REFUSALS.get(-code, f'code {-code}')}")
+    raise KernelError(f"{what}: CUDA error {code} at launch")
+
+
+def _dev(*tensors):
+    for t in tensors:
+        if t is not None and not t.is_cuda:
+            raise KernelError("a kernel was handed a tensor that is not on the GPU")
+
+
+def _contig(name, t):
+    if not t.is_contiguous():
+        raise KernelError(f"{name} must be contiguous")
+
+
+_fn_cache: dict = {}
+
+
+def _fn(lib_name: str, fn_name: str, argtypes):
+    key = (lib_name, fn_name)
+    f = _fn_cache.get(key)
+    if f is None:
+        f = getattr(load_library(lib_name), fn_name)
+        f.argtypes = argtypes
+        f.restype = c_int
+        _fn_cache[key] = f
+    return f
+
+
+# ---------------------------------------------------------------------------
+
+
+def embed(table: torch.Tensor, tokens: torch.Tensor, out: torch.Tensor) -> None:
+    """out[t,:] = float32(table[tokens[t],:]).  tokens int32 [T]; out float32 [T,d]."""
+    _dev(table, tokens, out)
+    _contig("table", table), _contig("out", out)
+    assert tokens.dtype == torch.int32 and out.dtype == torch.float32
+    f = _fn("elementwise", "llmx_embed",
+            [c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p])
+    _check(f(_ptr(table), _tag(table), _ptr(tokens), _ptr(out), tokens.numel(), table.shape[1],
+             table.shape[0], _stream()), "embed")
+
+
+def add_rms_norm(h: torch.Tensor, delta, gain: torch.Tensor, eps: float, out, rows=None,
+                 write_h: bool = True) -> None:
+    """h float32 [T,d] is the residual stream.  ``delta`` is None or [S,T,d]
+    (split partials, summed in order).  v = h + sum(delta); h = v when
+    ``write_h``; out[r] = rmsnorm(v[rows[r]]) * gain, or for every row without
+    ``rows``.  ``out`` may be None when only the sum is wanted."""
+    _dev(h, delta, gain, out, rows)
+    assert h.dtype == torch.float32 and gain.dtype == torch.float32
+    _contig("h", h)
+    d = h.shape[-1]
+    n_split, stride, dtag = 1, 0, F32
+    if delta is not None:
+        _contig("delta", delta)
+        if delta.dim() == 2:
+            delta = delta.unsqueeze(0)
+        assert delta.shape[1:] == h.shape, (delta.shape, h.shape)
+        n_split, stride, dtag = delta.shape[0], delta.stride(0), _tag(delta)
+    n_rows = h.shape[0] if rows is None else rows.numel()
+    if out is not None:
+        _contig("out", out)
+        assert out.shape[0] >= n_rows and out.shape[-1] == d
+    f = _fn("elementwise", "llmx_add_rms_norm",
+            [c_void_p, c_void_p, c_int, c_int, c_longlong, c_void_p, c_int, c_void_p, c_float, c_void_p,
+             c_int, c_int, c_int, c_void_p])
+    _check(f(_ptr(h), _ptr(delta), dtag, n_split, stride, _ptr(rows), n_rows, _ptr(gain), eps, _ptr(out),
+             _tag(out) if out is not None else F32, d, int(write_h), _stream()), "add_rms_norm")
+
+
+def qk_norm_rope_cache(qkv, q_out, k_cache, v_cache, block_table, token_seq, token_pos, q_gain, k_gain,
+                       eps: float, cos, sin, n_rot: int, n_heads: int, n_kv_heads: int, head_dim: int,
+                       write_cache: bool = True) -> None:
+    """qkv [T,(H+2G)*D] -> q_out [T,H*D] (normed, rotated) and, when
+    ``write_cache``, k (normed, rotated) and v into the paged cache entry
+    ``k_cache``/``v_cache`` [n_pages,G,PAGE,D] at each token's position."""
+    _dev(qkv, q_out, k_cache, v_cache, block_table, token_seq, token_pos)
+    _contig("qkv", qkv), _contig("q_out", q_out), _contig("block_table", block_table)
+    T = qkv.shape[0]
+    assert qkv.shape[1] == (n_heads + 2 * n_kv_heads) * head_dim
+    assert q_out.dtype == qkv.dtype and k_cache.dtype == v_cache.dtype
+    assert k_cache.is_contiguous() and v_cache.is_contiguous()
+    if head_dim > 256 or head_dim % 2:
+        raise Unsupported(f"head_dim {head_dim}: the q/k norm and rotation kernel takes even sizes up to 256")
+    f = _fn("elementwise", "llmx_qk_norm_rope_cache",
+            [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p,
+             c_void_p, c_void_p, c_float, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p])
+    _check(f(_ptr(qkv), _ptr(q_out), _tag(qkv), _ptr(k_cache), _ptr(v_cache), _tag(k_cache), _ptr(block_table),
+             block_table.shape[1], _ptr(token_seq), _ptr(token_pos), _ptr(q_gain), _ptr(k_gain), eps,
+             _ptr(cos), _ptr(sin), n_rot, T, n_heads, n_kv_heads, head_dim, int(write_cache), _stream()),
+           "qk_norm_rope_cache")
+
+
+def silu_gate(gu: torch.Tensor, out: torch.Tensor) -> None:
+    """gu [S,T,2F] or [T,2F] (gate columns, then up columns) -> out [T,F] = silu(gate) * up."""
+    _dev(gu, out)
+    _contig("gu", gu), _contig("out", out)
+    if gu.dim() == 2:
+        gu = gu.unsqueeze(0)
+    S, T, F2 = gu.shape
+    assert out.shape == (T, F2 // 2)
+    f = _fn("elementwise", "llmx_silu_gate",
+            [c_void_p, c_int, c_int, c_longlong, c_void_p, c_int, c_int, c_int, c_void_p])
+    _check(f(_ptr(gu), _tag(gu), S, gu.stride(0), _ptr(out), _tag(out), T, F2 // 2, _stream()), "silu_gate")
+
+
+def sum_splits(parts: torch.Tensor, out: torch.Tensor) -> None:
+    """out = parts.sum(0) with the partials added in order; parts [S, ...]."""
+    _dev(parts, out)
+    _contig("parts", parts), _contig("out", out)
+    assert parts.shape[1:] == out.shape
+    f = _fn("elementwise", "llmx_sum_splits",
+            [c_void_p, c_int, c_int, c_longlong, c_void_p, c_int, c_longlong, c_void_p])
+    _check(f(_ptr(parts), _tag(parts), parts.shape[0], parts.stride(0), _ptr(out), _tag(out), out.numel(),
+             _stream()), "sum_splits")
+
+
+def attention_paged(q, out, k_cache, v_cache, block_table, token_seq, token_pos, n_heads: int,
+                    n_kv_heads: int, head_dim: int, window, scale: float) -> None:
+    """General attention over the paged cache; q, out [T,H*D]."""
+    _dev(q, out, k_cache, v_cache, block_table, token_seq, token_pos)
+    _contig("q", q), _contig("out", out), _contig("block_table", block_table)
+    if head_dim > 256:
+        raise Unsupported(f"head_dim {head_dim}: the general attention kernel takes sizes up to 256")
+    if n_heads % n_kv_heads:
+        raise Unsupported(f"{n_heads} heads are not a multiple of {n_kv_heads} kv heads")
+    f = _fn("attention", "llmx_attention_paged",
+            [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p,
+             c_int, c_int, c_int, c_int, c_int, c_float, c_void_p])
+    _check(f(_ptr(q), _ptr(out), _tag(q), _ptr(k_cache), _ptr(v_cache), _tag(k_cache), _ptr(block_table),
+             block_table.shape[1], _ptr(token_seq), _ptr(token_pos), q.shape[0], n_heads, n_kv_heads, head_dim,
+             int(window or 0), scale, _stream()), "attention_paged")
+
+
+def gemm_fma(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> None:
+    """out[M,N] = x[M,K] @ w[N,K]^T on the FMA units, float32 accumulation in
+    the order k = 0..K-1.  Rows may be strided; the K axis must be dense."""
+    _dev(x, w, out)
+    M, K = x.shape
+    N = w.shape[0]
+    assert w.shape[1] == K and out.shape == (M, N)
+    assert x.stride(1) == 1 and w.stride(1) == 1 and out.stride(1) == 1
+    f = _fn("gemm_fma", "llmx_gemm_fma",
+            [c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_longlong, c_longlong,
+             c_longlong, c_void_p])
+    _check(f(_ptr(x), _tag(x), _ptr(w), _tag(w), _ptr(out), _tag(out), M, N, K, x.stride(0), w.stride(0),
+             out.stride(0), _stream()), "gemm_fma")
+
+
+def argmax(logits: torch.Tensor, out_tokens: torch.Tensor) -> None:
+    """out_tokens[b] = the last index among the maxima of logits[b,:]."""
+    _dev(logits, out_tokens)
+    assert logits.dtype == torch.float32 and out_tokens.dtype == torch.int32 and logits.stride(1) == 1
+    f = _fn("sampling", "llmx_argmax", [c_void_p, c_longlong, c_int, c_int, c_void_p, c_void_p])
+    _check(f(_ptr(logits), logits.stride(0), logits.shape[0], logits.shape[1], _ptr(out_tokens), _stream()),
+           "argmax")
+
+
+def sample(logits, temperature, top_k, top_p, repeat_penalty, recent, uniform, out_tokens, status) -> None:
+    """One token per row of float32 ``logits`` [B,V] (changed in place by the
+    repetition penalty).  Per-row parameters are device tensors [B]; ``recent``
+    is int32 [B,W] with -1 for no token, or None.  ``status`` int32 [1] is set
+    non-zero when a row asked for what the kernel cannot do."""
+    _dev(logits, temperature, top_k, top_p, repeat_penalty, recent, uniform, out_tokens, status)
+    assert logits.dtype == torch.float32 and logits.stride(1) == 1
+    assert temperature.dtype == torch.float32 and top_p.dtype == torch.float32 and uniform.dtype == torch.float32
+    assert top_k.dtype == torch.int32 and out_tokens.dtype == torch.int32 and status.dtype == torch.int32
+    f = _fn("sampling", "llmx_sample",
+            [c_void_p, c_longlong, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
+             c_void_p, c_void_p, c_void_p, c_void_p])
+    width = 0 if recent is None else recent.shape[1]
+    _check(f(_ptr(logits), logits.stride(0), logits.shape[0], logits.shape[1], _ptr(temperature), _ptr(top_k),
+             _ptr(top_p), _ptr(repeat_penalty), _ptr(recent), width, _ptr(uniform), _ptr(out_tokens),
+             _ptr(status), _stream()), "sample")

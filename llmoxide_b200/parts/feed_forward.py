@@ -1,0 +1,33 @@
+"""Gated feed-forward: down(act(gate x) * (up x)), act = SiLU x/(1+exp(-x))
+(crates/model/src/qwen35/cpu.rs:386-395, crates/model/src/ops.rs:176-178).
+Gate and up are one matrix product over the rows [gate; up]."""
+
+from __future__ import annotations
+
+import torch
+
+from .. import kernels
+from ..errors import Unsupported
+from .linear import Linear
+from .registry import register_feed_forward
+
+
+@register_feed_forward("gated_mlp")
+class GatedMLP:
+    def __init__(self, spec, weights: dict, rt):
+        if spec.get("activation", "silu") != "silu":
+            raise Unsupported(f"gated_mlp activation {spec.get('activation')!r}: only 'silu' is built")
+        self.rt, self.F = rt, spec["intermediate_size"]
+        t = spec.tensors
+        wg, wu = weights.pop(t["gate"].name), weights.pop(t["up"].name)
+        if wg.dtype != wu.dtype:
+            wg, wu = wg.float(), wu.float()
+        self.gate_up = Linear(torch.cat([wg, wu], dim=0), rt)
+        del wg, wu
+        self.down = Linear(weights.pop(t["down"].name), rt)
+
+    def forward(self, x, ctx):
+        gu = self.gate_up(x, splits_ok=True)
+        act = torch.empty((x.shape[0], self.F), dtype=self.rt.act_dtype, device=x.device)
+        kernels.silu_gate(gu, act)
+        return self.down(act, splits_ok=True)

@@ -1,0 +1,33 @@
+"""y = x W^T for one weight matrix [out, in] (no bias: the architecture has
+none, crates/model/src/qwen35/weights.rs:78-126).  Picks the kernel from the
+weight's dtype and the runtime: float32 weights always go through the FMA
+kernel in true 32-bit; bfloat16 weights go to the tensor-core kernel when it
+takes the shape, else to the FMA kernel."""
+
+from __future__ import annotations
+
+import torch
+
+from .. import kernels
+from .runtime import Runtime
+
+
+class Linear:
+    def __init__(self, weight: torch.Tensor, rt: Runtime):
+        assert weight.dim() == 2 and weight.stride(1) == 1
+        self.weight, self.rt = weight, rt
+        self.out_features, self.in_features = weight.shape
+        self._tc = None
+        if rt.tensor_cores and weight.dtype == torch.bfloat16 and rt.dtype == "bfloat16":
+            from . import linear_tc
+            self._tc = linear_tc.plan_for(weight)
+
+    def __call__(self, x: torch.Tensor, out_dtype=None, splits_ok: bool = False) -> torch.Tensor:
+        """x [T, in] -> [T, out], or split partials [S, T, out] in float32 when
+        ``splits_ok`` and the kernel chose to split the reduction."""
+        out_dtype = out_dtype or self.rt.act_dtype
+        if self._tc is not None and x.dtype == torch.bfloat16:
+            return self._tc(x, out_dtype, splits_ok)
+        out = torch.empty((x.shape[0], self.out_features), dtype=out_dtype, device=x.device)
+        kernels.gemm_fma(x, self.weight, out)
+        return out

@@ -1,0 +1,52 @@
+"""Tiny configurations of the dense Qwen3 decoder that differ in every size
+and option: head counts and groups, head size, widths that are no power of
+two, layer count, vocabulary, eps, rotation base, tied or untied head, and
+the window."""
+
+import json
+from pathlib import Path
+
+TINY_A = dict(
+    architectures=["Qwen3ForCausalLM"], model_type="qwen3",
+    num_hidden_layers=2, hidden_size=64, num_attention_heads=4, num_key_value_heads=2, head_dim=16,
+    intermediate_size=128, vocab_size=256, rope_theta=10000.0, rms_norm_eps=1e-6,
+    tie_word_embeddings=True, max_position_embeddings=128, sliding_window=None, use_sliding_window=False,
+    torch_dtype="float32", eos_token_id=7,
+)
+TINY_B = dict(
+    architectures=["Qwen3ForCausalLM"], model_type="qwen3",
+    num_hidden_layers=3, hidden_size=96, num_attention_heads=6, num_key_value_heads=2, head_dim=32,
+    intermediate_size=160, vocab_size=384, rope_theta=1000000.0, rms_norm_eps=1e-5,
+    tie_word_embeddings=False, max_position_embeddings=256, use_sliding_window=False,
+    torch_dtype="float32", eos_token_id=[11, 12],
+)
+# Windowed layers between full ones, as many kv heads as heads, odd vocabulary.
+TINY_C = dict(
+    architectures=["Qwen3ForCausalLM"], model_type="qwen3",
+    num_hidden_layers=4, hidden_size=80, num_attention_heads=5, num_key_value_heads=5, head_dim=48,
+    intermediate_size=112, vocab_size=307, rope_theta=50000.0, rms_norm_eps=3e-6,
+    tie_word_embeddings=False, max_position_embeddings=512, sliding_window=24, use_sliding_window=True,
+    layer_types=["full_attention", "sliding_attention", "sliding_attention", "full_attention"],
+    torch_dtype="float32", eos_token_id=3,
+)
+ALL = {"A": TINY_A, "B": TINY_B, "C": TINY_C}
+
+
+def make_folder(tmp_path, name: str, dtype: str, seed: int = 1234) -> Path:
+    """Writes a model folder with the package's random-weights mode."""
+    from llmoxide_b200.config import read_config
+    from llmoxide_b200.weights import write_model_folder
+
+    cfg = dict(ALL[name])
+    cfg["torch_dtype"] = dtype
+    folder = Path(tmp_path) / f"tiny_{name}_{dtype}"
+    if not (folder / "model.safetensors").exists():
+        write_model_folder(folder, read_config(cfg), seed, dtype)
+    return folder
+
+
+def prompts(vocab: int, lengths, seed: int = 0):
+    import numpy as np
+
+    rng = np.random.default_rng(seed)
+    return [rng.integers(0, vocab, size=n).tolist() for n in lengths]
