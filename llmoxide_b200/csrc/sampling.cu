@@ -203,6 +203,7 @@ sample_kernel(float* __restrict__ logits, long long ld, int V, const float* __re
   const unsigned n_eq = sh_count;        // keys equal to the k-th in the row
 
   // ---- gather the candidates ---------------------------------------------
+  __syncthreads();  // every thread has read the select's results before they are reset
   if (tid == 0) { sh_count = 0u; sh_taken_eq = 0u; }
   __syncthreads();
   if (n_eq == need_eq) {

@@ -63,6 +63,7 @@ class Engine:
                            self.device, max_seq_len=max_seq)
         self.buffers = StepBuffers(self.device)
         self.n_steps = 0
+        self._sampler = None
 
     # ---- loading -------------------------------------------------------------
 
@@ -147,6 +148,15 @@ class Engine:
         page_rows = [[alloc.page_row(slot, g) for slot, _ in entries] for g in range(n_groups)]
         lay, buf, facts = build_host_arrays(entries, want, lengths, page_rows, n_groups)
         return self.buffers.upload(lay, buf, facts)
+
+    def step_sample(self, entries, samplings, recents, uniforms) -> list:
+        """One step, then one token per entry from the logits at its last
+        token, chosen on the device.  Returns the token ids as a host list."""
+        if self._sampler is None:
+            from ..sampling.device import DeviceSampler
+            self._sampler = DeviceSampler(self.device, self.spec.vocab_size)
+        logits = self.step(entries)
+        return self._sampler.sample(logits, samplings, recents, uniforms)
 
     # ---- facts -------------------------------------------------------------------
 

@@ -1,0 +1,243 @@
+"""CPU tests: the cache's bookkeeping (no slot or page lost, held twice or
+freed twice; windows give pages back) and the generation loop's decisions
+with a scripted backend."""
+
+import random
+
+import pytest
+
+from llmoxide_b200.cache import PAGE, CacheAllocator, pages_for
+from llmoxide_b200.engine.generate import (CANCELLED, LENGTH, STOP, GenerationLoop, Limits, Request,
+                                           max_new_tokens, plan_batches)
+from llmoxide_b200.errors import CacheExhausted, CacheMisuse, ContextOverflow
+from llmoxide_b200.sampling import Rng, Sampling
+
+import plain_qwen3 as plain
+
+
+# ---- cache ----------------------------------------------------------------------
+
+def test_slots_are_given_back_and_used_again():
+    a = CacheAllocator(n_slots=2, n_pages=4, windows=[None])
+    s0, s1 = a.acquire(), a.acquire()
+    assert {s0, s1} == {0, 1}
+    with pytest.raises(CacheExhausted):
+        a.acquire()
+    a.reserve(s0, 70), a.commit(s0, 70)
+    assert a.length(s0) == 70 and len(a.page_row(s0, 0)) == 2
+    a.release(s0)
+    s2 = a.acquire()
+    assert s2 == s0 and a.length(s2) == 0 and a.page_row(s2, 0) == []
+    a.check_consistent()
+
+
+def test_double_free_and_use_after_free_are_errors():
+    a = CacheAllocator(2, 4, [None])
+    s = a.acquire()
+    a.release(s)
+    with pytest.raises(CacheMisuse):
+        a.release(s)
+    with pytest.raises(CacheMisuse):
+        a.reserve(s, 1)
+    with pytest.raises(CacheMisuse):
+        a.length(5)
+    s = a.acquire()
+    a.reserve(s, 3)
+    with pytest.raises(CacheMisuse):
+        a.commit(s, 4)          # more than was reserved
+
+
+def test_pages_run_out_without_changing_anything():
+    a = CacheAllocator(2, 3, [None, 16])
+    s0, s1 = a.acquire(), a.acquire()
+    a.reserve(s0, 2 * PAGE), a.commit(s0, 2 * PAGE)
+    with pytest.raises(CacheExhausted):
+        a.reserve(s1, PAGE + 1)
+    assert a.page_row(s1, 0) == [] and a.page_row(s1, 1) == []
+    a.check_consistent()
+    a.reserve(s1, PAGE)
+    a.check_consistent()
+
+
+def test_longest_sequence_is_enforced():
+    a = CacheAllocator(1, 8, [None], max_seq_len=100)
+    s = a.acquire()
+    a.reserve(s, 100), a.commit(s, 100)
+    with pytest.raises(ContextOverflow):
+        a.reserve(s, 1)
+
+
+def test_window_group_gives_dead_pages_back():
+    w = 24
+    a = CacheAllocator(1, 8, [None, w])
+    s = a.acquire()
+    a.reserve(s, 150), a.commit(s, 150)
+    # next query at 150 sees keys from 127 on: pages 0 (0..63) is dead, page 1 (64..127) holds 127
+    assert a.page_row(s, 0) == [0, 1, 2]
+    assert a.page_row(s, 1)[0] == -1 and a.page_row(s, 1)[1] >= 0
+    assert a.pages_held(1) == 2
+    for _ in range(42):          # up to length 192: first visible 169 -> pages 0, 1 dead
+        a.reserve(s, 1), a.commit(s, 1)
+    assert a.page_row(s, 1)[:2] == [-1, -1] and a.pages_held(1) == 1
+    a.check_consistent()
+    a.release(s)
+    assert a.pages_held(0) == 0 and a.pages_held(1) == 0
+
+
+def test_random_traffic_never_loses_or_doubles_a_page():
+    rng = random.Random(3)
+    a = CacheAllocator(6, 40, [None, 50])
+    live = {}
+    for _ in range(3000):
+        op = rng.random()
+        if op < 0.15 and a.n_free_slots:
+            live[a.acquire()] = 0
+        elif op < 0.25 and live:
+            s = rng.choice(list(live))
+            a.release(s)
+            del live[s]
+        elif live:
+            s = rng.choice(list(live))
+            n = rng.choice([1, 1, 1, 7, 64, 130])
+            try:
+                a.reserve(s, n)
+            except (CacheExhausted, ContextOverflow):
+                continue
+            a.commit(s, n)
+            live[s] += n
+            assert a.length(s) == live[s]
+        a.check_consistent()
+    for s in list(live):
+        a.release(s)
+    a.check_consistent()
+    assert a.pages_held(0) == 0 and a.pages_held(1) == 0 and a.n_free_slots == 6
+
+
+# ---- the generation loop ------------------------------------------------------------
+
+class ScriptedBackend:
+    """Answers each sequence with its own scripted tokens and records every
+    step; checks that slots are acquired, used and released consistently."""
+
+    def __init__(self, scripts, n_slots):
+        self.scripts, self.n_slots = scripts, n_slots       # first prompt token -> list of tokens to emit
+        self.free = list(range(n_slots))
+        self.owner, self.fed, self.steps, self.released = {}, {}, [], []
+
+    def acquire(self):
+        slot = self.free.pop(0)
+        self.fed[slot] = []
+        return slot
+
+    def release(self, slot):
+        assert slot in self.fed, "released a slot that is not held"
+        self.released.append((slot, list(self.fed.pop(slot))))
+        self.free.append(slot)
+
+    def step_sample(self, entries, samplings, recents, uniforms):
+        self.steps.append([(slot, list(toks)) for slot, toks in entries])
+        out = []
+        for (slot, toks), recent in zip(entries, recents):
+            assert slot in self.fed, "stepped a slot that is not held"
+            self.fed[slot].extend(toks)
+            key = self.fed[slot][0]
+            out.append(self.scripts[key][len(recent)])
+        return out
+
+
+LIMITS = Limits(max_batch=3, max_tokens=64 * 8, max_step_tokens=100, max_seq_len=128)
+
+
+def _loop(scripts, limits=LIMITS, stop_ids=(99,)):
+    be = ScriptedBackend(scripts, limits.max_batch)
+    return be, GenerationLoop(be, limits, Sampling.greedy(), stop_ids)
+
+
+def test_stop_length_and_early_finishers():
+    scripts = {1: [5, 6, 99, 7], 2: [8] * 10, 3: [99]}
+    be, loop = _loop(scripts)
+    outs = loop.run([Request([1, 10, 11], max_tokens=8), Request([2], max_tokens=4), Request([3, 30], max_tokens=8)])
+    assert outs[0].tokens == [5, 6, 99] and outs[0].reason == STOP          # the stop token is recorded
+    assert outs[1].tokens == [8, 8, 8, 8] and outs[1].reason == LENGTH
+    assert outs[2].tokens == [99] and outs[2].reason == STOP and outs[2].prompt_tokens == 2
+    # one prompt step with all three, then decode steps with the live ones only
+    assert [len(s) for s in be.steps] == [3, 2, 2, 1]
+    assert be.steps[0] == [(0, [1, 10, 11]), (1, [2]), (2, [3, 30])]
+    assert be.steps[1] == [(0, [5]), (1, [8])]
+    # the stop token is never fed back, and the last token of a length-limited sequence is not either
+    fed = {f[0]: f for _, f in be.released}
+    assert fed[1] == [1, 10, 11, 5, 6] and fed[2] == [2, 8, 8, 8] and fed[3] == [3, 30]
+    assert sorted(be.free) == [0, 1, 2]
+
+
+def test_batches_follow_one_another_and_reuse_slots():
+    scripts = {i: [i] * 6 for i in range(1, 8)}
+    be, loop = _loop(scripts)
+    reqs = [Request([i], max_tokens=1 + i % 3) for i in range(1, 8)]
+    outs = loop.run(reqs)
+    assert [o.generated for o in outs] == [1 + i % 3 for i in range(1, 8)]
+    assert len(be.released) == 7 and sorted(be.free) == [0, 1, 2]
+    assert max(len(s) for s in be.steps) <= 3
+    # 7 requests, at most 3 at a time: three batches
+    assert plan_batches([1] * 7, [2] * 7, LIMITS) == [[0, 1, 2], [3, 4, 5], [6]]
+
+
+def test_callback_cancels_one_sequence_only():
+    scripts = {1: [5, 6, 7, 8], 2: [9, 9, 9, 9]}
+    be, loop = _loop(scripts)
+    seen = []
+
+    def on_token(i, tok):
+        seen.append((i, tok))
+        return not (i == 0 and tok == 6)
+
+    outs = loop.run([Request([1], max_tokens=4), Request([2], max_tokens=3)], on_token)
+    assert outs[0].reason == CANCELLED and outs[0].tokens == [5, 6]
+    assert outs[1].reason == LENGTH and outs[1].tokens == [9, 9, 9]
+    assert (0, 5) in seen and (1, 9) in seen
+
+
+def test_plan_batches_respects_pages_and_step_tokens():
+    lim = Limits(max_batch=8, max_tokens=64 * 4, max_step_tokens=100, max_seq_len=512)
+    assert plan_batches([60, 60, 60], [1, 1, 1], lim) == [[0], [1], [2]]           # step tokens
+    assert plan_batches([10, 10, 10], [120, 120, 10], lim) == [[0], [1, 2]]        # pages: 3 + 3 > 4, 3 + 1 fit
+    assert plan_batches([300], [1], lim) == [[0]]                                  # alone, fed in chunks
+
+
+def test_long_prompt_is_fed_in_chunks_and_sampled_once():
+    scripts = {1: [7, 7, 7]}
+    lim = Limits(max_batch=2, max_tokens=64 * 8, max_step_tokens=4, max_seq_len=256)
+    be, loop = _loop(scripts, lim)
+    prompt = [1] + list(range(20, 29))
+    out = loop.run([Request(prompt, max_tokens=2)])[0]
+    assert out.tokens == [7, 7]
+    assert [t for s in be.steps[:3] for _, t in s] == [prompt[0:4], prompt[4:8], prompt[8:10]]
+    assert be.steps[3] == [(0, [7])]
+
+
+def test_limits_and_context_overflow():
+    lim = Limits(2, 1024, 1024, 16)
+    assert max_new_tokens(10, 512, lim) == 6
+    with pytest.raises(ContextOverflow):
+        max_new_tokens(16, 4, lim)
+    with pytest.raises(ValueError):
+        max_new_tokens(0, 4, lim)
+    be, loop = _loop({1: [4] * 20}, lim)
+    out = loop.run([Request([1] * 12, max_tokens=50)])[0]
+    assert out.generated == 4 and out.reason == LENGTH
+    assert len(be.released[0][1]) == 15            # 12 prompt + 3 fed back: position 15 is the last
+
+
+def test_rng_matches_the_plain_implementation_and_is_per_sequence():
+    a, b = Rng(42), plain.Rng(42)
+    assert [a.next_f32() for _ in range(100)] == [b.next_f32() for _ in range(100)]
+    scripts = {1: [5] * 5, 2: [6] * 5}
+    be, loop = _loop(scripts)
+    draws = []
+    orig = be.step_sample
+    be.step_sample = lambda e, s, r, u: (draws.append(list(u)), orig(e, s, r, u))[1]
+    samp = Sampling(temperature=0.7, seed=9)
+    loop.run([Request([1], 3, samp), Request([2], 3, samp.with_(seed=10))])
+    r9, r10 = plain.Rng(9), plain.Rng(10)
+    assert [d[0] for d in draws] == [r9.next_f32() for _ in range(3)]
+    assert [d[1] for d in draws] == [r10.next_f32() for _ in range(3)]

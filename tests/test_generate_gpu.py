@@ -1,0 +1,171 @@
+"""GPU: generation through the entry point -- greedy against the plain
+implementation, long decoding, the first tokens of a sequence, unequal
+batches with early finishers and slots used again, temperature sampling that
+is reproducible and independent of the batch, and the command line."""
+
+import subprocess
+import sys
+
+import numpy as np
+import pytest
+import torch
+
+import plain_qwen3 as plain
+import replay_util as ru
+from tiny_configs import ALL, make_folder, prompts
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def folders(tmp_path_factory):
+    base = tmp_path_factory.mktemp("models")
+    return {(n, d): make_folder(base, n, d) for n in ALL for d in ("float32", "bfloat16")}
+
+
+def _session(folder, dtype, **kw):
+    from llmoxide_b200 import LoadOptions, Session
+
+    opts = dict(dtype=dtype, max_tokens=2048, max_batch=4)
+    opts.update(kw)
+    return Session.load(folder, LoadOptions(**opts))
+
+
+@pytest.mark.parametrize("name", ["A", "B", "C"])
+def test_greedy_generation_matches_the_plain_implementation(folders, name):
+    from llmoxide_b200 import Request, Sampling
+
+    folder = folders[(name, "float32")]
+    cfg, w = plain.read_model(folder)
+    ps = prompts(cfg["vocab_size"], [3, 17, 1, 40, 9, 66, 5], seed=3)
+    n_new = [12, 5, 20, 8, 1, 10, 30]
+    stops = tuple(cfg["eos_token_id"]) if isinstance(cfg["eos_token_id"], list) else (cfg["eos_token_id"],)
+    want = [plain.greedy_generate(cfg, w, p, n, stops) for p, n in zip(ps, n_new)]
+    s = _session(folder, "float32", max_batch=3)           # 7 requests over 3 slots: slots are used again
+    outs = s.generate([Request(p, max_tokens=n, sampling=Sampling.greedy()) for p, n in zip(ps, n_new)])
+    for o, wt, n in zip(outs, want, n_new):
+        assert o.tokens == wt
+        assert o.reason == ("stop" if wt[-1] in stops else "length")
+        assert o.generated == len(wt)
+    s.engine.cache.alloc.check_consistent()
+    assert s.engine.cache.alloc.pages_held() == 0 and s.engine.cache.alloc.n_free_slots == 3
+
+
+def test_greedy_bfloat16_follows_float32_logits(folders):
+    """bfloat16 may pick another token only where the float32 logits nearly tie."""
+    from llmoxide_b200 import Request, Sampling
+
+    folder = folders[("B", "bfloat16")]
+    cfg, w = plain.read_model(folder)
+    p = prompts(cfg["vocab_size"], [23], seed=4)[0]
+    out = _session(folder, "bfloat16").generate([Request(p, 24, Sampling.greedy(), stop_ids=())])[0]
+    ids = list(p)
+    for tok in out.tokens:
+        logits = plain.forward(cfg, w, ids)[-1].numpy()
+        assert logits.max() - logits[tok] <= 2e-2 * np.abs(logits).max()
+        ids.append(tok)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_long_decoding_and_first_tokens(folders, dtype):
+    """One token at a time from the very first position, across several pages
+    and, in configuration C, far beyond the window."""
+    for name in ("A", "C"):
+        folder = folders[(name, dtype)]
+        vocab = ALL[name]["vocab_size"]
+        toks = prompts(vocab, [ALL[name]["max_position_embeddings"] // 2 if name == "A" else 230], seed=8)[0]
+        from llmoxide_b200.engine.engine import Engine, LoadOptions
+        eng = Engine.load(folder, LoadOptions(dtype=dtype, max_tokens=512, max_batch=2))
+        slot = eng.acquire()
+        rows = [eng.step([(slot, [t])])[0].cpu().numpy() for t in toks]
+        eng.release(slot)
+        got = np.stack(rows)
+        want = ru.expected_logits(folder, {"x": toks})["x"]
+        for lo, hi in ((0, 4), (0, len(toks))):            # the first tokens, then all of them
+            assert ru.rel_err(got[lo:hi], want[lo:hi]) <= ru.TOL[dtype], (name, lo, hi)
+        if name == "C":
+            assert eng.cache.alloc.pages_held(0) == 0 and eng.cache.alloc.pages_held(1) == 0
+
+
+def test_temperature_sampling_is_seeded_and_batch_independent(folders):
+    from llmoxide_b200 import Request, Sampling
+
+    folder = folders[("B", "float32")]
+    ps = prompts(ALL["B"]["vocab_size"], [9, 30, 2], seed=5)
+    samp = Sampling(temperature=0.9, top_k=40, top_p=0.9, repeat_penalty=1.1, seed=21)
+    s = _session(folder, "float32")
+    reqs = [Request(p, 16, samp.with_(seed=21 + i), stop_ids=()) for i, p in enumerate(ps)]
+    together = s.generate(reqs)
+    alone = [s.generate([r])[0] for r in reqs]
+    again = s.generate(reqs)
+    for a, b, c in zip(together, alone, again):
+        assert a.tokens == b.tokens == c.tokens
+    other = s.generate([Request(ps[0], 16, samp.with_(seed=99), stop_ids=())])[0]
+    assert other.tokens != together[0].tokens
+    # against the plain sampler on the plain implementation's logits
+    cfg, w = plain.read_model(folder)
+    rng, ids, out = plain.Rng(21), list(ps[0]), []
+    for _ in range(16):
+        logits = plain.forward(cfg, w, ids)[-1].numpy()
+        tok = plain.sample(logits, out, temperature=0.9, top_k=40, top_p=0.9, repeat_penalty=1.1,
+                           repeat_window=64, u=rng.next_f32())
+        out.append(tok)
+        ids.append(tok)
+    same = sum(a == b for a, b in zip(out, together[0].tokens))
+    assert out[:4] == together[0].tokens[:4] and same >= 12, (out, together[0].tokens)
+
+
+def test_forward_and_wipe(folders):
+    folder = folders[("A", "float32")]
+    s = _session(folder, "float32")
+    toks = prompts(ALL["A"]["vocab_size"], [11], seed=6)[0]
+    want = ru.expected_logits(folder, {"x": toks})["x"]
+    a = s.forward(toks[:6]).cpu().numpy()
+    b = s.forward(toks[6:]).cpu().numpy()
+    assert ru.rel_err(a[None], want[5:6]) <= ru.TOL["float32"]
+    assert ru.rel_err(b[None], want[10:11]) <= ru.TOL["float32"]
+    s.wipe()
+    c = s.forward(toks[:6]).cpu().numpy()
+    assert np.array_equal(a, c)
+    assert s.info()["architecture"] == "Qwen3ForCausalLM"
+
+
+def test_errors_before_any_launch(folders):
+    from llmoxide_b200 import CacheExhausted, ContextOverflow, LoadOptions, Request, Session
+    from llmoxide_b200.engine.engine import Engine
+
+    folder = folders[("A", "float32")]
+    eng = Engine.load(folder, LoadOptions(dtype="float32", max_tokens=128, max_batch=2, max_step_tokens=64))
+    slot = eng.acquire()
+    with pytest.raises(ValueError, match="vocabulary"):
+        eng.step([(slot, [1, 256])])
+    with pytest.raises(ContextOverflow):
+        eng.step([(slot, [1] * 65)])                      # step limit
+    with pytest.raises(ContextOverflow):
+        eng.step([(slot, [1] * 60)]), eng.step([(slot, [1] * 60)]), eng.step([(slot, [1] * 60)])
+    other = eng.acquire()
+    with pytest.raises(CacheExhausted):
+        eng.acquire()
+    with pytest.raises(CacheExhausted):
+        eng.step([(other, [1] * 10)])                     # the pages are held by the first sequence
+    eng.release(slot), eng.release(other)
+    eng.cache.alloc.check_consistent()
+    with pytest.raises(ContextOverflow):
+        Session(eng).generate([Request([1] * 128, 4)])
+
+
+def test_command_line(folders):
+    folder = folders[("A", "float32")]
+    cfg, w = plain.read_model(folder)
+    ps = prompts(cfg["vocab_size"], [4, 9], seed=7)
+    text = ";".join(",".join(map(str, p)) for p in ps)
+    p = subprocess.run([sys.executable, str(ru.ROOT / "bin" / "llmoxide"), str(folder), text, "6",
+                        "--dtype", "float32", "--ignore-stop"], capture_output=True, text=True, timeout=600)
+    assert p.returncode == 0, p.stderr[-3000:]
+    lines = [l for l in p.stdout.splitlines() if l.startswith("ids: ")]
+    want = [plain.greedy_generate(cfg, w, q, 6) for q in ps]
+    assert [l.split("  (")[0] for l in lines] == [f"ids: {t}" for t in want]
+    assert "prefill" in p.stderr and "tok/s" in p.stderr
+    q = subprocess.run([sys.executable, str(ru.ROOT / "bin" / "llmoxide"), str(folder), "1,2", "--cpu"],
+                       capture_output=True, text=True, timeout=600)
+    assert q.returncode == 2 and "no CPU path" in q.stderr

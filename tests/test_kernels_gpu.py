@@ -1,0 +1,302 @@
+"""GPU: each kernel alone against its plain float32 reference, at sizes other
+than the engine's, with inputs made so that a fault shows (a far key among
+hundreds, a window's edge, a page boundary)."""
+
+import math
+
+import numpy as np
+import pytest
+import torch
+
+import plain_qwen3 as plain
+
+pytestmark = pytest.mark.gpu
+
+DEV = "cuda"
+PAGE = 64
+
+
+def rel(got, want):
+    got, want = got.float().cpu(), want.float().cpu()
+    return float((got - want).abs().max() / want.abs().max())
+
+
+def tol(dtype):
+    return 2e-6 if dtype == torch.float32 else 6e-3   # one bfloat16 rounding is 2^-9 = 2e-3
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_embed(dtype):
+    from llmoxide_b200 import kernels
+    table = torch.randn(1000, 200).to(dtype)
+    toks = torch.tensor([0, 999, 17, 17, 500], dtype=torch.int32)
+    out = torch.empty(5, 200, dtype=torch.float32, device=DEV)
+    kernels.embed(table.to(DEV), toks.to(DEV), out)
+    assert torch.equal(out.cpu(), plain.embed(table.float(), toks.tolist()))
+
+
+@pytest.mark.parametrize("delta_dtype, out_dtype", [(torch.float32, torch.float32), (torch.float32, torch.bfloat16),
+                                                    (torch.bfloat16, torch.bfloat16)])
+def test_add_rms_norm(delta_dtype, out_dtype):
+    from llmoxide_b200 import kernels
+    T, d, S = 7, 200, 3
+    h = torch.randn(T, d)
+    delta = torch.randn(S, T, d).to(delta_dtype)
+    gain = 1 + 0.1 * torch.randn(d)
+    eps = 1e-5
+    want_h = h + delta.float().sum(0)
+    want = plain.rms_norm(want_h, gain, eps)
+    hd = h.to(DEV)
+    out = torch.empty(T, d, dtype=out_dtype, device=DEV)
+    kernels.add_rms_norm(hd, delta.to(DEV), gain.to(DEV), eps, out)
+    assert rel(hd, want_h) < 2e-6
+    assert rel(out, want) < tol(out_dtype)
+    # gathered rows, residual left alone
+    rows = torch.tensor([5, 0, 5], dtype=torch.int32, device=DEV)
+    hd2 = h.to(DEV)
+    out2 = torch.empty(3, d, dtype=out_dtype, device=DEV)
+    kernels.add_rms_norm(hd2, delta.to(DEV), gain.to(DEV), eps, out2, rows=rows, write_h=False)
+    assert torch.equal(hd2.cpu(), h)
+    assert rel(out2, want[[5, 0, 5]]) < tol(out_dtype)
+    # no delta at all: a plain norm
+    out3 = torch.empty(T, d, dtype=out_dtype, device=DEV)
+    kernels.add_rms_norm(hd2, None, gain.to(DEV), eps, out3)
+    assert rel(out3, plain.rms_norm(h, gain, eps)) < tol(out_dtype)
+
+
+def _paged(seqs_kv, G, D, dtype, n_pages=32, shuffle=True):
+    """Scatter per-sequence k, v [L,G,D] into a paged cache with a shuffled
+    page order; returns k_cache, v_cache, block table."""
+    rng = np.random.default_rng(5)
+    order = rng.permutation(n_pages) if shuffle else np.arange(n_pages)
+    k_cache = torch.full((n_pages, G, PAGE, D), float("nan"), dtype=dtype)
+    v_cache = torch.full((n_pages, G, PAGE, D), float("nan"), dtype=dtype)
+    width = max((len(k) + PAGE - 1) // PAGE for k, _ in seqs_kv)
+    table = torch.full((len(seqs_kv), width), -1, dtype=torch.int32)
+    nxt = 0
+    for i, (k, v) in enumerate(seqs_kv):
+        for lp in range((len(k) + PAGE - 1) // PAGE):
+            page = int(order[nxt]); nxt += 1
+            table[i, lp] = page
+            chunk = slice(lp * PAGE, min(len(k), (lp + 1) * PAGE))
+            n = chunk.stop - chunk.start
+            k_cache[page, :, :n] = k[chunk].transpose(0, 1).to(dtype)
+            v_cache[page, :, :n] = v[chunk].transpose(0, 1).to(dtype)
+    return k_cache, v_cache, table
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("window", [None, 37])
+def test_attention_paged_whole_and_single_tokens(dtype, window):
+    from llmoxide_b200 import kernels
+    H, G, D = 6, 3, 48
+    lens = [1, 100, 300]
+    torch.manual_seed(0)
+    qs = [torch.randn(L, H, D).to(dtype).float() for L in lens]
+    ks = [torch.randn(L, G, D).to(dtype).float() for L in lens]
+    vs = [torch.randn(L, G, D).to(dtype).float() for L in lens]
+    # a far key among hundreds: key 3 of the last sequence answers query 290 of head 4 loudly
+    ks[2][3, 2] = 0.0
+    ks[2][3, 2, :8] = 4.0
+    qs[2][290, 4] = 0.0
+    qs[2][290, 4, :8] = 4.0
+    want = [plain.causal_attention(q, k, v, G, window) for q, k, v in zip(qs, ks, vs)]
+    if window is None:
+        assert torch.allclose(want[2][290, 4], vs[2][3, 2], atol=1e-3)   # the far key dominates
+    kc, vc, table = _paged(list(zip(ks, vs)), G, D, dtype)
+    scale = 1 / math.sqrt(D)
+    # (a) all tokens of all sequences in one launch
+    q_all = torch.cat(qs).reshape(-1, H * D).to(dtype)
+    seq = torch.cat([torch.full((L,), i, dtype=torch.int32) for i, L in enumerate(lens)])
+    pos = torch.cat([torch.arange(L, dtype=torch.int32) for L in lens])
+    out = torch.empty_like(q_all, device=DEV)
+    kernels.attention_paged(q_all.to(DEV), out, kc.to(DEV), vc.to(DEV), table.to(DEV), seq.to(DEV), pos.to(DEV),
+                            H, G, D, window, scale)
+    want_all = torch.cat(want).reshape(-1, H * D)
+    assert rel(out, want_all) < tol(dtype)
+    # (b) only the last token of each sequence, as a decode step does
+    last = torch.tensor([sum(lens[: i + 1]) - 1 for i in range(3)])
+    out2 = torch.empty(3, H * D, dtype=dtype, device=DEV)
+    kernels.attention_paged(q_all[last].to(DEV), out2, kc.to(DEV), vc.to(DEV), table.to(DEV),
+                            torch.arange(3, dtype=torch.int32, device=DEV),
+                            torch.tensor([L - 1 for L in lens], dtype=torch.int32, device=DEV),
+                            H, G, D, window, scale)
+    assert rel(out2, want_all[last]) < tol(dtype)
+    if dtype == torch.float32:
+        assert torch.equal(out2.cpu(), out.cpu()[last])     # bit-equal however the tokens are batched
+
+
+def test_attention_window_edge_is_exact():
+    """The key just outside the window must not be seen, the one just inside must."""
+    from llmoxide_b200 import kernels
+    H = G = 1
+    D, L, w = 16, 200, 70
+    k = torch.zeros(L, G, D)
+    v = torch.zeros(L, G, D)
+    q = torch.zeros(L, H, D)
+    p = 199
+    q[p, 0, 0] = 8.0
+    inside, outside = p - (w - 1), p - w
+    k[outside, 0, 0], v[outside, 0, 1] = 50.0, 1.0     # would dominate if seen
+    k[inside, 0, 0], v[inside, 0, 2] = 5.0, 1.0
+    kc, vc, table = _paged([(k, v)], G, D, torch.float32)
+    out = torch.empty(1, D, device=DEV)
+    args = (kc.to(DEV), vc.to(DEV), table.to(DEV), torch.zeros(1, dtype=torch.int32, device=DEV),
+            torch.tensor([p], dtype=torch.int32, device=DEV), H, G, D)
+    kernels.attention_paged(q[p].reshape(1, D).to(DEV), out, *args, w, 0.25)
+    want = plain.causal_attention(q, k, v, G, w)[p, 0]
+    assert want[1] == 0 and want[2] > 0.99
+    assert rel(out[0], want) < 2e-6
+    kernels.attention_paged(q[p].reshape(1, D).to(DEV), out, *args, w + 1, 0.25)
+    assert out[0, 1].item() > 0.99
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_qk_norm_rope_cache(dtype):
+    from llmoxide_b200 import kernels
+    H, G, D, n_rot = 3, 1, 80, 32
+    lens, past = [5, 70], [60, 0]             # the first sequence crosses a page boundary
+    T = sum(lens)
+    torch.manual_seed(1)
+    qkv = torch.randn(T, (H + 2 * G) * D).to(dtype)
+    qg, kg = 1 + 0.1 * torch.randn(D), 1 + 0.1 * torch.randn(D)
+    eps, base = 1e-5, 5000.0
+    pos = torch.cat([torch.arange(p, p + L) for p, L in zip(past, lens)]).to(torch.int32)
+    seq = torch.cat([torch.full((L,), i) for i, L in enumerate(lens)]).to(torch.int32)
+    cos, sin = plain.rope_angles(list(range(256)), n_rot, base)
+    table = torch.tensor([[3, 1], [0, 2]], dtype=torch.int32)
+    kc = torch.zeros(4, G, PAGE, D, dtype=dtype, device=DEV)
+    vc = torch.zeros_like(kc)
+    q_out = torch.empty(T, H * D, dtype=dtype, device=DEV)
+    kernels.qk_norm_rope_cache(qkv.to(DEV), q_out, kc, vc, table.to(DEV), seq.to(DEV), pos.to(DEV),
+                               qg.to(DEV), kg.to(DEV), eps, cos.to(DEV), sin.to(DEV), n_rot, H, G, D, True)
+    x = qkv.float()
+    q = x[:, : H * D].view(T, H, D)
+    k = x[:, H * D : (H + G) * D].view(T, G, D)
+    v = x[:, (H + G) * D :].view(T, G, D)
+    want_q = plain.rope_neox(plain.rms_norm(q, qg, eps), pos.tolist(), base, n_rot)
+    want_k = plain.rope_neox(plain.rms_norm(k, kg, eps), pos.tolist(), base, n_rot)
+    assert rel(q_out.view(T, H, D), want_q) < tol(dtype)
+    for t in range(T):
+        page = table[seq[t], pos[t] // PAGE]
+        assert rel(kc[page, :, pos[t] % PAGE], want_k[t]) < tol(dtype), t
+        assert torch.equal(vc[page, :, pos[t] % PAGE].float().cpu(), v[t].to(dtype).float()), t
+    # without the cache write nothing is stored and q is the same
+    kc2 = torch.zeros_like(kc)
+    q2 = torch.empty_like(q_out)
+    kernels.qk_norm_rope_cache(qkv.to(DEV), q2, kc2, kc2, table.to(DEV), seq.to(DEV), pos.to(DEV),
+                               qg.to(DEV), kg.to(DEV), eps, cos.to(DEV), sin.to(DEV), n_rot, H, G, D, False)
+    assert torch.equal(q2, q_out) and not kc2.any()
+
+
+@pytest.mark.parametrize("xd, wd, yd", [(torch.float32,) * 3, (torch.bfloat16,) * 3,
+                                         (torch.bfloat16, torch.float32, torch.bfloat16),
+                                         (torch.bfloat16, torch.bfloat16, torch.float32)])
+def test_gemm_fma(xd, wd, yd):
+    from llmoxide_b200 import kernels
+    M, N, K = 37, 130, 75
+    x, w = torch.randn(M, K).to(xd), torch.randn(N, K).to(wd)
+    out = torch.empty(M, N, dtype=yd, device=DEV)
+    kernels.gemm_fma(x.to(DEV), w.to(DEV), out)
+    want = plain.linear(x.double(), w.double()).float()
+    assert rel(out, want) < (2e-6 if yd == torch.float32 else 6e-3)
+    if xd == torch.float32:
+        one = torch.empty(1, N, device=DEV)
+        kernels.gemm_fma(x[11:12].to(DEV), w.to(DEV), one)
+        assert torch.equal(one[0], out[11])        # a row does not depend on the rows around it
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_silu_gate_and_sum_splits(dtype):
+    from llmoxide_b200 import kernels
+    S, T, F = 2, 9, 70
+    gu = torch.randn(S, T, 2 * F).to(dtype)
+    act = torch.empty(T, F, dtype=dtype, device=DEV)
+    kernels.silu_gate(gu.to(DEV), act)
+    g = gu.float().sum(0)
+    assert rel(act, plain.silu(g[:, :F]) * g[:, F:]) < tol(dtype)
+    out = torch.empty(T, 2 * F, dtype=torch.float32, device=DEV)
+    kernels.sum_splits(gu.to(DEV), out)
+    assert rel(out, g) < 2e-6
+
+
+def test_argmax_takes_the_last_of_equal_maxima():
+    from llmoxide_b200 import kernels
+    V = 5003
+    logits = torch.randn(4, V)
+    logits[0, [7, 4000]] = 9.0
+    logits[1, 0] = 9.0
+    logits[2, V - 1] = 9.0
+    logits[3, [10, 11, 12]] = float("inf")
+    out = torch.empty(4, dtype=torch.int32, device=DEV)
+    kernels.argmax(logits.to(DEV), out)
+    assert out.tolist() == [4000, 0, V - 1, 12]
+    assert out.tolist() == [plain.argmax(r.numpy()) for r in logits]
+
+
+@pytest.mark.parametrize("V, top_k, top_p, temp, pen", [
+    (307, 20, 0.8, 0.7, 1.0), (5003, 64, 0.95, 1.0, 1.3), (5003, 1, 1.0, 1.0, 1.0),
+    (5003, 1024, 1.0, 2.0, 1.0), (307, 0, 0.9, 1.5, 1.0), (151936, 20, 0.8, 0.7, 1.1),
+])
+def test_sample_matches_the_plain_sampler(V, top_k, top_p, temp, pen):
+    from llmoxide_b200 import kernels
+    B = 24
+    g = torch.Generator().manual_seed(V + top_k)
+    logits = (3 * torch.randn(B, V, generator=g)).float()
+    logits[:, 5] = logits[:, 9]                      # equal logits: the lower id goes first
+    logits[3, :50] = float("-inf")
+    recent = torch.full((B, 8), -1, dtype=torch.int32)
+    for b in range(B):
+        top = torch.topk(logits[b], 3).indices
+        recent[b, :3] = top.to(torch.int32)
+        recent[b, 3] = top[0]                        # a token twice in the window is penalised twice
+    u = torch.rand(B, generator=g)
+    u[0], u[1] = 0.0, 0.9999999
+    dev = lambda t: t.to(DEV)
+    out = torch.empty(B, dtype=torch.int32, device=DEV)
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    work = dev(logits.clone())
+    kernels.sample(work, dev(torch.full((B,), temp)), dev(torch.full((B,), top_k, dtype=torch.int32)),
+                   dev(torch.full((B,), top_p)), dev(torch.full((B,), pen)), dev(recent), dev(u), out, status)
+    assert status.item() == 0
+    got = out.tolist()
+    mismatches = []
+    for b in range(B):
+        rec = [t for t in recent[b].tolist() if t >= 0]
+        want = plain.sample(logits[b].numpy(), rec, temperature=temp, top_k=top_k, top_p=top_p,
+                            repeat_penalty=pen, repeat_window=64, u=float(u[b]))
+        if got[b] != want:
+            mismatches.append((b, got[b], want))
+    # expf on the device and exp on the host may differ in the last bit, which can
+    # move a draw that sits on the edge between two tokens; more than one in 24 is a fault
+    assert len(mismatches) <= 1, mismatches
+
+
+def test_sample_whole_vocabulary_follows_the_distribution():
+    from llmoxide_b200 import kernels
+    V, B = 3000, 4096
+    base = torch.zeros(V)
+    base[[10, 2000, 2999]] = torch.tensor([2.0, 1.0, 0.0])
+    base[[0, 1, 2]] = -30.0
+    base[3:10] = -40.0
+    base[11:2000] = -50.0
+    base[2001:2999] = -50.0
+    logits = base.repeat(B, 1).clone()
+    g = torch.Generator().manual_seed(1)
+    u = torch.rand(B, generator=g)
+    out = torch.empty(B, dtype=torch.int32, device=DEV)
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    dev = lambda t: t.to(DEV)
+    kernels.sample(dev(logits), dev(torch.ones(B)), dev(torch.zeros(B, dtype=torch.int32)), dev(torch.ones(B)),
+                   None, None, dev(u), out, status)
+    assert status.item() == 0
+    counts = torch.bincount(out.cpu().long(), minlength=V).float() / B
+    p = torch.softmax(base, 0)
+    for t in (10, 2000, 2999):
+        assert abs(counts[t] - p[t]) < 0.03, (t, counts[t], p[t])
+    # the walk is in id order: small u lands on the lowest ids with mass
+    assert out[u.argmin()].item() <= 10
+    # top_p < 1 over a whole large vocabulary is refused, not approximated
+    kernels.sample(dev(logits), dev(torch.ones(B)), dev(torch.zeros(B, dtype=torch.int32)),
+                   dev(torch.full((B,), 0.5)), None, None, dev(u), out, status)
+    assert status.item() != 0

@@ -1,0 +1,87 @@
+"""GPU: the same requests replayed whole, with the last 32 tokens one by one,
+and in batches of unequal lengths with slots used again -- in true 32-bit and
+in bfloat16, each compared with the plain implementation."""
+
+import os
+
+import numpy as np
+import pytest
+import torch
+
+import replay_util as ru
+from tiny_configs import ALL, make_folder, prompts
+
+pytestmark = pytest.mark.gpu
+
+LENGTHS = {"A": [5, 9, 13, 70, 1, 41], "B": [1, 7, 16, 31, 130, 66], "C": [3, 90, 25, 64, 150, 49]}
+
+
+@pytest.fixture(scope="module")
+def folders(tmp_path_factory):
+    base = tmp_path_factory.mktemp("models")
+    return {(n, d): make_folder(base, n, d) for n in ALL for d in ("float32", "bfloat16")}
+
+
+def _engine(folder, dtype, max_tokens=1024):
+    from llmoxide_b200.engine.engine import Engine, LoadOptions
+
+    return Engine.load(folder, LoadOptions(dtype=dtype, max_tokens=max_tokens, max_batch=8))
+
+
+def _requests(name):
+    toks = prompts(ALL[name]["vocab_size"], LENGTHS[name], seed=11)
+    return {f"r{i}": t for i, t in enumerate(toks)}
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["A", "B", "C"])
+def test_three_cuttings_match_the_plain_implementation(folders, tmp_path, name, dtype):
+    folder = folders[(name, dtype)]
+    reqs = _requests(name)
+    want = ru.expected_logits(folder, reqs)
+    vocab = ALL[name]["vocab_size"]
+    eng = _engine(folder, dtype)
+    results = {}
+    for what, steps in (("whole", ru.trace_whole(reqs)),
+                        ("last 32 one by one", ru.trace_tail_decode(reqs, 32)),
+                        ("unequal batches", ru.trace_batches(reqs, 4)),
+                        ("unequal batches of 3, short prompts", ru.trace_batches(reqs, 3, 0.2))):
+        out = tmp_path / what.replace(" ", "_").replace(",", "")
+        ru.run_in_process(eng, steps, out)
+        got = ru.collect(steps, out, vocab)
+        ru.assert_matches(got, want, dtype, f"{name}/{dtype}/{what}")
+        results[what] = got
+    if dtype == "float32":
+        # In 32-bit the cuttings agree with one another far below the tolerance
+        # against the plain implementation.
+        for what, got in results.items():
+            for rid in reqs:
+                assert ru.rel_err(got[rid], results["whole"][rid]) <= 2e-6, (what, rid)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_trace_run_program(folders, tmp_path, dtype):
+    """The program itself, as a user runs it: fewer pages than all requests
+    together would need, so pages and slots are used again."""
+    name = "B"
+    folder = folders[(name, dtype)]
+    reqs = _requests(name)
+    want = ru.expected_logits(folder, reqs)
+    steps = ru.trace_batches(reqs, 2)
+    # two live requests at a time: the two longest are 130 and 66 tokens
+    max_tokens = 192 + 128
+    ru.run_trace_run(folder, dtype, steps, tmp_path / "out", max_tokens)
+    got = ru.collect(steps, tmp_path / "out", ALL[name]["vocab_size"])
+    ru.assert_matches(got, want, dtype, f"trace_run/{dtype}")
+
+
+def test_steps_without_wanted_logits_write_no_file(folders, tmp_path):
+    folder = folders[("A", "float32")]
+    steps = [dict(step=0, entries=[dict(id="a", tokens=[1, 2, 3], want=[])], end=[]),
+             dict(step=1, entries=[dict(id="a", tokens=[4], want=[0])], end=["a"])]
+    eng = _engine(folder, "float32")
+    ru.run_in_process(eng, steps, tmp_path)
+    assert not (tmp_path / "0.f32").exists() and (tmp_path / "1.f32").exists()
+    want = ru.expected_logits(folder, {"a": [1, 2, 3, 4]})["a"][3:]
+    got = np.fromfile(tmp_path / "1.f32", dtype="<f4").reshape(1, -1)
+    assert ru.rel_err(got, want) <= ru.TOL["float32"]
