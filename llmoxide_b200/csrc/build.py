@@ -37,6 +37,7 @@ LIBRARIES = {
     "elementwise": (["elementwise.cu"], []),
     "attention": (["attention.cu"], []),
     "gemm_fma": (["gemm_fma.cu"], []),
+    "gemm_tc": (["gemm_tc.cu"], []),
     "sampling": (["sampling.cu"], []),
 }
 HEADERS = ["common.cuh"]

@@ -1,0 +1,359 @@
+// bfloat16 matrix product on the 5th-generation tensor cores (tcgen05) of
+// sm_100a:  Y[T,N] = X[T,K] * W[N,K]^T, float32 accumulation in tensor memory.
+//
+// The weight matrix is the MMA's M operand: a CTA owns 128 rows of W (128
+// output features) and a tile of BN tokens, so the same kernel serves decode
+// (BN = 16..64 tokens, the weights streamed once at full HBM rate) and prefill
+// (BN = 256 tokens).  Both operands are K-major in global memory, so neither
+// needs a transpose.  Per CTA:
+//   warp 0      producer: TMA (cp.async.bulk.tensor, 128-byte swizzle) loads of
+//               the W tile [128 x 64] and the X tile [BN x 64] per stage
+//   warp 1      allocates tensor memory; one lane issues tcgen05.mma
+//               (M = 128, N = BN, K = 16, four per stage) and commits each
+//               stage back to the producer through an mbarrier
+//   warps 2..5  epilogue: tcgen05.ld the accumulator (lane = output feature,
+//               column = token), convert, store; or store float32 partials
+//               of a split reduction; or, with two accumulators (gate and up
+//               rows of the same features), silu(gate) * up
+// Every wait on an mbarrier is bounded; when one runs out the CTA records it
+// in a status word, stops issuing work, frees its tensor memory and returns.
+//
+// y[t,o] = sum_i W[o,i] x[t,i] (crates/model/src/ops.rs:83-101); the gated
+// epilogue is crates/model/src/qwen35/cpu.rs:386-392.
+#include <cuda.h>
+
+#include "common.cuh"
+
+#define TC_BM 128        // rows of W per CTA = MMA M
+#define TC_BK 64         // bf16 elements per stage along K = one 128-byte swizzle row
+#define TC_UMMA_K 16
+#define TC_THREADS 192
+#define TC_WAIT_CYCLES 4000000000ll   // about two seconds: far beyond any legitimate wait
+
+__device__ int g_tc_status = 0;   // 0, or 1 + the role whose bounded wait ran out
+
+// ---------------------------------------------------------------------------
+// PTX wrappers
+// ---------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n.reg .pred p;\n"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+      "selp.u32 %0, 1, 0, p;\n}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+// Bounded wait: false when the limit ran out.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
+  if (mbar_try_wait(bar, parity)) return true;
+  const long long t0 = clock64();
+  while (!mbar_try_wait(bar, parity)) {
+    if (clock64() - t0 > TC_WAIT_CYCLES) return false;
+  }
+  return true;
+}
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int x, int y, uint32_t bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+      ::"r"(dst), "l"(map), "r"(x), "r"(y), "r"(bar)
+      : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+
+// 64-bit shared-memory matrix descriptor: K-major tile of 128-byte rows with
+// the 128-byte swizzle; 8-row groups are 1024 bytes apart.
+__device__ __forceinline__ uint64_t umma_desc(uint32_t smem_addr) {
+  uint64_t d = 0;
+  d |= (uint64_t)((smem_addr & 0x3FFFFu) >> 4);        // start address
+  d |= (uint64_t)1 << 16;                               // leading byte offset (unused with swizzle)
+  d |= (uint64_t)(1024 >> 4) << 32;                     // stride byte offset
+  d |= (uint64_t)1 << 46;                               // descriptor version of sm_100
+  d |= (uint64_t)2 << 61;                               // SWIZZLE_128B
+  return d;
+}
+// Instruction descriptor: bf16 x bf16 -> f32, both operands K-major, M = 128.
+__host__ __device__ constexpr uint32_t umma_idesc(int n) {
+  return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(TC_BM >> 4) << 24);
+}
+__device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t a, uint64_t b, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\n"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}"
+      ::"r"(tmem_d), "l"(a), "l"(b), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, float* v) {
+  uint32_t r[16];
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+      : "r"(taddr));
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+  for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[i]);
+}
+
+// ---------------------------------------------------------------------------
+// The kernel.  grid = (ceil(rows/128), ceil(T/BN), n_split).
+// MODE 0: Y (bf16 or f32) [T, N] or split partials f32 [n_split][T, N].
+// MODE 1: two accumulators, rows n and n + F of W; act[T, F] = silu(g) * u.
+// ---------------------------------------------------------------------------
+template <int BN, int MODE, typename TY>
+__global__ void __launch_bounds__(TC_THREADS, 1)
+gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
+               TY* __restrict__ Y, int T, int N, int K, long long ldy, int k_blocks_per_split,
+               long long split_stride, int F, int n_stages) {
+  extern __shared__ uint8_t smem_raw[];
+  constexpr int N_ACC = MODE == 1 ? 2 : 1;
+  constexpr uint32_t A_BYTES = TC_BM * TC_BK * 2;
+  constexpr uint32_t B_BYTES = BN * TC_BK * 2;
+  constexpr uint32_t STAGE_BYTES = N_ACC * A_BYTES + B_BYTES;
+  constexpr uint32_t TMEM_COLS = (N_ACC * BN) < 32 ? 32 : (N_ACC * BN);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int n0 = blockIdx.x * TC_BM, t0 = blockIdx.y * BN;
+  const int total_kb = (K + TC_BK - 1) / TC_BK;
+  const int kb_begin = blockIdx.z * k_blocks_per_split;
+  const int kb_end = min(total_kb, kb_begin + k_blocks_per_split);
+  const int n_kb = kb_end - kb_begin;
+
+  // 1024-byte aligned stage buffers, then the barriers
+  const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  uint8_t* base_ptr = smem_raw + (base - smem_u32(smem_raw));
+  uint64_t* bars = reinterpret_cast<uint64_t*>(base_ptr + (size_t)n_stages * STAGE_BYTES);
+  const uint32_t full0 = smem_u32(bars), empty0 = full0 + 8u * n_stages, acc_full = empty0 + 8u * n_stages;
+  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(bars + 2 * n_stages + 1);
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < n_stages; ++s) {
+      mbar_init(full0 + 8u * s, 1);
+      mbar_init(empty0 + 8u * s, 1);
+    }
+    mbar_init(acc_full, 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("prefetch.tensormap [%0];" ::"l"(&map_w) : "memory");
+    asm volatile("prefetch.tensormap [%0];" ::"l"(&map_x) : "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_holder)),
+                 "r"(TMEM_COLS)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_holder;
+
+  if (warp == 0) {
+    // ---------------- producer ----------------
+    if (lane == 0) {
+      for (int i = 0; i < n_kb; ++i) {
+        const int s = i % n_stages;
+        const uint32_t parity = ((i / n_stages) & 1) ^ 1;
+        if (!mbar_wait(empty0 + 8u * s, parity)) { atomicExch(&g_tc_status, 1); break; }
+        const uint32_t stage = base + (uint32_t)s * STAGE_BYTES;
+        const uint32_t bar = full0 + 8u * s;
+        mbar_expect_tx(bar, STAGE_BYTES);
+        const int k = (kb_begin + i) * TC_BK;
+        tma_load_2d(stage, &map_w, k, n0, bar);
+        if (MODE == 1) tma_load_2d(stage + A_BYTES, &map_w, k, n0 + F, bar);
+        tma_load_2d(stage + N_ACC * A_BYTES, &map_x, k, t0, bar);
+      }
+    }
+  } else if (warp == 1) {
+    // ---------------- MMA issuer ----------------
+    if (lane == 0) {
+      constexpr uint32_t idesc = umma_idesc(BN);
+      bool ok = true;
+      for (int i = 0; i < n_kb && ok; ++i) {
+        const int s = i % n_stages;
+        const uint32_t parity = (i / n_stages) & 1;
+        if (!mbar_wait(full0 + 8u * s, parity)) { atomicExch(&g_tc_status, 2); ok = false; break; }
+        tc_fence_after();
+        const uint32_t stage = base + (uint32_t)s * STAGE_BYTES;
+#pragma unroll
+        for (int j = 0; j < TC_BK / TC_UMMA_K; ++j) {
+          const uint64_t db = umma_desc(stage + N_ACC * A_BYTES + j * (TC_UMMA_K * 2));
+          const uint32_t acc = (i > 0 || j > 0) ? 1u : 0u;
+          umma_bf16(tmem_base, umma_desc(stage + j * (TC_UMMA_K * 2)), db, idesc, acc);
+          if (MODE == 1) umma_bf16(tmem_base + BN, umma_desc(stage + A_BYTES + j * (TC_UMMA_K * 2)), db, idesc, acc);
+        }
+        umma_commit(empty0 + 8u * s);   // the stage is free once these MMAs have read it
+      }
+      umma_commit(acc_full);            // the accumulator is complete once every MMA has finished
+    }
+  } else {
+    // ---------------- epilogue ----------------
+    const int quad = warp & 3;          // the quarter of tensor memory this warp may read
+    const int row = quad * 32 + lane;   // row of the tile = lane of tensor memory
+    const int n = n0 + row;
+    const int n_limit = MODE == 1 ? F : N;
+    bool ok = true;
+    if (n_kb > 0) {
+      ok = mbar_wait(acc_full, 0);
+      if (!ok && lane == 0) atomicExch(&g_tc_status, 3);
+    }
+    ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+    tc_fence_after();
+    if (ok) {
+      TY* out = Y + (MODE == 0 ? (size_t)blockIdx.z * split_stride : 0);
+#pragma unroll 1
+      for (int c = 0; c < BN; c += 16) {
+        if (t0 + c >= T) break;
+        float v[16], u[16];
+        const uint32_t taddr = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)c;
+        if (n_kb > 0) {
+          tmem_ld16(taddr, v);
+          if (MODE == 1) tmem_ld16(taddr + BN, u);
+        } else {
+#pragma unroll
+          for (int j = 0; j < 16; ++j) v[j] = u[j] = 0.f;
+        }
+        if (n < n_limit) {
+#pragma unroll
+          for (int j = 0; j < 16; ++j) {
+            const int t = t0 + c + j;
+            if (t < T) {
+              float r = v[j];
+              if (MODE == 1) r = (r / (1.0f + __expf(-r))) * u[j];
+              out[(size_t)t * ldy + n] = from_f32<TY>(r);
+            }
+          }
+        }
+      }
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
+  }
+}
+
+// ---------------------------------------------------------------------------
+// Host side
+// ---------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  if (!fn) {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = (EncodeTiledFn)p;
+  }
+  return fn;
+}
+
+// A bf16 matrix [rows, K] with row stride `ld` elements, boxes of [box_rows x 64].
+static int make_map(CUtensorMap* map, const void* ptr, uint64_t rows, uint64_t K, uint64_t ld, uint32_t box_rows,
+                    bool weights) {
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) return 1;
+  cuuint64_t dims[2] = {K, rows};
+  cuuint64_t strides[1] = {ld * 2};
+  cuuint32_t box[2] = {TC_BK, box_rows};
+  cuuint32_t elem[2] = {1, 1};
+  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, elem,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                  weights ? CU_TENSOR_MAP_L2_PROMOTION_L2_256B : CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? 0 : 2;
+}
+
+template <int BN, int MODE, typename TY>
+static int launch(const CUtensorMap& mw, const CUtensorMap& mx, void* Y, int T, int N, int K, long long ldy,
+                  int n_split, long long split_stride, int F, cudaStream_t stream) {
+  constexpr int N_ACC = MODE == 1 ? 2 : 1;
+  constexpr size_t STAGE = (size_t)N_ACC * TC_BM * TC_BK * 2 + (size_t)BN * TC_BK * 2;
+  const int total_kb = (K + TC_BK - 1) / TC_BK;
+  const int per_split = (total_kb + n_split - 1) / n_split;
+  int stages = (int)((200 * 1024) / STAGE);
+  if (stages > 12) stages = 12;
+  if (stages > per_split) stages = per_split < 2 ? 2 : per_split;
+  const size_t smem = 1024 + (size_t)stages * STAGE + (2 * stages + 1) * 8 + 16;
+  auto kernel = gemm_tc_kernel<BN, MODE, TY>;
+  static bool attr_set = false;
+  if (!attr_set) {
+    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+    if (e != cudaSuccess) return (int)e;
+    attr_set = true;
+  }
+  const int rows = MODE == 1 ? F : N;
+  dim3 grid((rows + TC_BM - 1) / TC_BM, (T + BN - 1) / BN, n_split);
+  kernel<<<grid, TC_THREADS, smem, stream>>>(mw, mx, (TY*)Y, T, N, K, ldy, per_split, split_stride, F, stages);
+  return LLMX_LAUNCH_STATUS();
+}
+
+// X [T,K] bf16 (row stride ldx), W [N,K] bf16 (row stride ldw).
+// mode 0: Y [T,N] of y_dtype, or with n_split > 1 float32 partials [n_split][T,N] (split_stride elements apart).
+// mode 1: W = [gate rows; up rows] with N = 2F; Y = act [T,F] of y_dtype.
+LLMX_API int llmx_gemm_tc(const void* X, const void* W, void* Y, int y_dtype, int T, int N, int K, long long ldx,
+                          long long ldw, long long ldy, int n_split, long long split_stride, int mode,
+                          cudaStream_t stream) {
+  if (T <= 0 || N <= 0) return 0;
+  if (K <= 0 || (K % 8) || (ldx % 8) || (ldw % 8) || ((uintptr_t)X & 15) || ((uintptr_t)W & 15)) return LLMX_REFUSED(1);
+  if (n_split < 1 || (n_split > 1 && (mode != 0 || y_dtype != LLMX_F32))) return LLMX_REFUSED(1);
+  if (mode == 1 && (N % 2)) return LLMX_REFUSED(1);
+  const int F = mode == 1 ? N / 2 : 0;
+  int bn = 16;
+  while (bn < T && bn < (mode == 1 ? 128 : 256)) bn <<= 1;
+  CUtensorMap mw, mx;
+  if (make_map(&mw, W, (uint64_t)N, (uint64_t)K, (uint64_t)ldw, TC_BM, true)) return LLMX_REFUSED(4);
+  if (make_map(&mx, X, (uint64_t)T, (uint64_t)K, (uint64_t)ldx, (uint32_t)bn, false)) return LLMX_REFUSED(4);
+#define GO(BN, MODE, TY) return launch<BN, MODE, TY>(mw, mx, Y, T, N, K, ldy, n_split, split_stride, F, stream)
+#define BY_BN(MODE, TY)                    \
+  switch (bn) {                            \
+    case 16: GO(16, MODE, TY);             \
+    case 32: GO(32, MODE, TY);             \
+    case 64: GO(64, MODE, TY);             \
+    case 128: GO(128, MODE, TY);           \
+    default: GO(256, MODE, TY);            \
+  }
+  if (mode == 0 && y_dtype == LLMX_BF16) { BY_BN(0, bf16) }
+  if (mode == 0 && y_dtype == LLMX_F32) { BY_BN(0, float) }
+  if (mode == 1 && y_dtype == LLMX_BF16) {
+    switch (bn) {
+      case 16: GO(16, 1, bf16);
+      case 32: GO(32, 1, bf16);
+      case 64: GO(64, 1, bf16);
+      default: GO(128, 1, bf16);
+    }
+  }
+#undef BY_BN
+#undef GO
+  return LLMX_REFUSED(2);
+}
+
+// The status word of the bounded waits: 0, or which role gave up.  Reading it synchronises the device.
+LLMX_API int llmx_gemm_tc_status(int reset) {
+  int v = 0;
+  if (cudaMemcpyFromSymbol(&v, g_tc_status, sizeof(int)) != cudaSuccess) return -1;
+  if (reset && v) {
+    int z = 0;
+    cudaMemcpyToSymbol(g_tc_status, &z, sizeof(int));
+  }
+  return v;
+}

@@ -64,6 +64,8 @@ class Engine:
         self.buffers = StepBuffers(self.device)
         self.n_steps = 0
         self._sampler = None
+        self._graphs: dict = {}
+        self._graph_pool = torch.cuda.graph_pool_handle() if options.cuda_graphs else None
 
     # ---- loading -------------------------------------------------------------
 
@@ -106,12 +108,21 @@ class Engine:
         among its tokens whose logits are asked for (default: the last).
         Returns float32 logits [wanted, vocab] on the device, in the order of
         the entries and of ``want``."""
-        ctx = self._prepare(entries, want)
-        logits = self.model.forward(ctx, self.cache)
+        logits, replayed = self._step(entries, want)
+        # A replayed graph writes its logits to the same memory every time.
+        return logits.clone() if replayed else logits
+
+    def _step(self, entries, want=None):
+        lay, ctx = self._prepare(entries, want)
+        replayed = bool(self.options.cuda_graphs and ctx.is_decode and self.model.graph_safe)
+        if replayed:
+            logits = self._graphed_forward(lay, ctx)
+        else:
+            logits = self.model.forward(ctx, self.cache)
         for slot, toks in entries:
             self.cache.alloc.commit(slot, len(toks))
         self.n_steps += 1
-        return logits
+        return logits, replayed
 
     def _prepare(self, entries, want):
         if not entries:
@@ -147,7 +158,41 @@ class Engine:
         n_groups = max(1, self.cache.n_groups())
         page_rows = [[alloc.page_row(slot, g) for slot, _ in entries] for g in range(n_groups)]
         lay, buf, facts = build_host_arrays(entries, want, lengths, page_rows, n_groups)
-        return self.buffers.upload(lay, buf, facts)
+        return lay, self.buffers.upload(lay, buf, facts)
+
+    def _graphed_forward(self, lay, ctx):
+        """Decode steps are launch-bound, so the whole forward of a decode
+        step is captured once per batch shape as a CUDA graph and replayed.
+        The step's inputs live in the step buffer at offsets that depend on
+        the shape alone, so a replay reads the new step's data.  Running the
+        same step again is harmless (it rewrites the same cache rows), which
+        lets the first occurrence run eagerly, then under capture, then as a
+        replay."""
+        key = (lay.key(), self.buffers.dev.data_ptr())
+        entry = self._graphs.get(key)
+        if entry is None:
+            self.model.forward(ctx, self.cache)            # warm-up: loads libraries, sizes workspaces
+            torch.cuda.current_stream().synchronize()
+            before = kernels.launch_count
+            graph = torch.cuda.CUDAGraph()
+            try:
+                with torch.cuda.graph(graph, pool=self._graph_pool):
+                    logits = self.model.forward(ctx, self.cache)
+            except RuntimeError as e:
+                # A part that reads device data on the host cannot be captured:
+                # from here on this engine runs every step eagerly.
+                print(f"[llmoxide_b200] decode steps are not captured as CUDA graphs: {e}", file=sys.stderr)
+                self.options.cuda_graphs = False
+                torch.cuda.synchronize()
+                return self.model.forward(ctx, self.cache)
+            entry = (graph, logits, kernels.launch_count - before)
+            if len(self._graphs) >= 64:
+                self._graphs.pop(next(iter(self._graphs)))
+            self._graphs[key] = entry
+        graph, logits, n_kernels = entry
+        graph.replay()
+        kernels.launch_count += n_kernels
+        return logits
 
     def step_sample(self, entries, samplings, recents, uniforms) -> list:
         """One step, then one token per entry from the logits at its last
@@ -155,7 +200,7 @@ class Engine:
         if self._sampler is None:
             from ..sampling.device import DeviceSampler
             self._sampler = DeviceSampler(self.device, self.spec.vocab_size)
-        logits = self.step(entries)
+        logits, _ = self._step(entries)
         return self._sampler.sample(logits, samplings, recents, uniforms)
 
     # ---- facts -------------------------------------------------------------------

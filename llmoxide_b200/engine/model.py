@@ -31,6 +31,10 @@ class DecoderModel:
         self.head = Linear(head, rt)
         weights.pop(spec.embedding.name, None)
         self._check_schedule()
+        # A part that reads device data on the host during its forward (it says
+        # so with ``graph_safe = False``) keeps decode steps out of CUDA graphs.
+        self.graph_safe = all(getattr(p, "graph_safe", True)
+                              for b in self.blocks for p in vars(b).values())
 
     def _check_schedule(self):
         writers = {}

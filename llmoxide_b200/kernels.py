@@ -48,8 +48,13 @@ def _stream():
     return c_void_p(torch.cuda.current_stream().cuda_stream)
 
 
+launch_count = 0  # kernels of this package launched (or replayed from a graph) so far
+
+
 def _check(code: int, what: str) -> None:
+    global launch_count
     if code == 0:
+        launch_count += 1
         return
     if code < 0:
         raise Unsupported(f"{what}: refused, {_REFUSALS.get(-code, f'code {-code}')}")
@@ -200,6 +205,45 @@ def gemm_fma(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> None:
              c_longlong, c_void_p])
     _check(f(_ptr(x), _tag(x), _ptr(w), _tag(w), _ptr(out), _tag(out), M, N, K, x.stride(0), w.stride(0),
              out.stride(0), _stream()), "gemm_fma")
+
+
+def gemm_tc_supports(x: torch.Tensor, w: torch.Tensor) -> bool:
+    """Shapes the tensor-core kernel takes: bfloat16, dense K axis, K and the
+    row strides multiples of 8 elements (TMA wants 16-byte strides and starts)."""
+    return (x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and x.stride(1) == 1 and w.stride(1) == 1
+            and x.shape[1] % 8 == 0 and x.stride(0) % 8 == 0 and w.stride(0) % 8 == 0
+            and x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0)
+
+
+def gemm_tc(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, n_split: int = 1, gated: bool = False) -> None:
+    """bfloat16 x [T,K] times w [N,K]^T on tcgen05.  ``out`` is [T,N] (bfloat16
+    or float32), or float32 partials [n_split,T,N] of a split reduction, or,
+    with ``gated`` (w = [gate rows; up rows]), [T,N/2] = silu(gate) * up."""
+    _dev(x, w, out)
+    T, K = x.shape
+    N = w.shape[0]
+    assert w.shape[1] == K and out.is_contiguous()
+    if gated:
+        assert n_split == 1 and out.shape == (T, N // 2)
+        ldy, stride = N // 2, 0
+    elif n_split > 1:
+        assert out.shape == (n_split, T, N) and out.dtype == torch.float32
+        ldy, stride = N, out.stride(0)
+    else:
+        assert out.shape == (T, N)
+        ldy, stride = N, 0
+    f = _fn("gemm_tc", "llmx_gemm_tc",
+            [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_longlong, c_longlong, c_longlong, c_int,
+             c_longlong, c_int, c_void_p])
+    _check(f(_ptr(x), _ptr(w), _ptr(out), _tag(out), T, N, K, x.stride(0), w.stride(0), ldy, n_split, stride,
+             1 if gated else 0, _stream()), "gemm_tc")
+
+
+def gemm_tc_status(reset: bool = True) -> int:
+    """0, or which role of the tensor-core kernel ran out of its bounded wait
+    since the last reset.  Synchronises the device."""
+    f = _fn("gemm_tc", "llmx_gemm_tc_status", [c_int])
+    return f(int(reset))
 
 
 def argmax(logits: torch.Tensor, out_tokens: torch.Tensor) -> None:

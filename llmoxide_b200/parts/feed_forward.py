@@ -27,7 +27,12 @@ class GatedMLP:
         self.down = Linear(weights.pop(t["down"].name), rt)
 
     def forward(self, x, ctx):
-        gu = self.gate_up(x, splits_ok=True)
-        act = torch.empty((x.shape[0], self.F), dtype=self.rt.act_dtype, device=x.device)
-        kernels.silu_gate(gu, act)
+        tc = self.gate_up._tc
+        if tc is not None and x.dtype == torch.bfloat16 and x.shape[0] > 64 and kernels.gemm_tc_supports(x, tc.weight):
+            # prefill: the activation is the epilogue of the gate/up product
+            act = tc.gated(x, self.rt.act_dtype)
+        else:
+            gu = self.gate_up(x, splits_ok=True)
+            act = torch.empty((x.shape[0], self.F), dtype=self.rt.act_dtype, device=x.device)
+            kernels.silu_gate(gu, act)
         return self.down(act, splits_ok=True)

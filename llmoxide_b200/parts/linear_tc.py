@@ -1,5 +1,61 @@
-"""Plans for the tensor-core matrix product (filled in by the tcgen05 kernel)."""
+"""Plans for the tensor-core matrix product: which launches a weight matrix
+takes at a given number of tokens.
+
+Decode is bound by reading the weights once, so a matrix with few 128-row
+tiles splits its reduction over K until about one CTA per SM streams; the
+float32 partials are summed by the kernel that consumes them (the residual
+add + norm, or the gated activation).  Prefill has tiles enough and does not
+split."""
+
+from __future__ import annotations
+
+import torch
+
+from .. import kernels
+
+N_SM = 148
+TILE_ROWS = 128
+MIN_KBLOCKS_PER_SPLIT = 8     # 64-element blocks of K per split, at least
 
 
-def plan_for(weight):
-    return None
+def choose_splits(n_rows: int, k: int, n_tokens: int, max_splits: int = 16) -> int:
+    if n_tokens > 64:
+        return 1
+    tiles = (n_rows + TILE_ROWS - 1) // TILE_ROWS
+    k_blocks = (k + 63) // 64
+    s = max(1, N_SM // tiles)
+    s = min(s, max(1, k_blocks // MIN_KBLOCKS_PER_SPLIT), max_splits)
+    return s
+
+
+class TensorCoreLinear:
+    def __init__(self, weight: torch.Tensor):
+        self.weight = weight
+        self.N, self.K = weight.shape
+
+    def __call__(self, x, out_dtype, splits_ok):
+        T = x.shape[0]
+        if not kernels.gemm_tc_supports(x, self.weight):
+            out = torch.empty((T, self.N), dtype=out_dtype, device=x.device)
+            kernels.gemm_fma(x, self.weight, out)
+            return out
+        s = choose_splits(self.N, self.K, T) if splits_ok else 1
+        if s > 1:
+            out = torch.empty((s, T, self.N), dtype=torch.float32, device=x.device)
+            kernels.gemm_tc(x, self.weight, out, n_split=s)
+            return out
+        out = torch.empty((T, self.N), dtype=out_dtype, device=x.device)
+        kernels.gemm_tc(x, self.weight, out)
+        return out
+
+    def gated(self, x, out_dtype):
+        """weight = [gate rows; up rows] -> silu(gate x) * (up x), [T, N/2]."""
+        out = torch.empty((x.shape[0], self.N // 2), dtype=out_dtype, device=x.device)
+        kernels.gemm_tc(x, self.weight, out, gated=True)
+        return out
+
+
+def plan_for(weight: torch.Tensor):
+    if weight.dtype != torch.bfloat16 or weight.stride(1) != 1 or weight.shape[1] % 8 or weight.stride(0) % 8:
+        return None
+    return TensorCoreLinear(weight)

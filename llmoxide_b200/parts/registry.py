@@ -16,6 +16,8 @@ Interfaces (``rt`` is the ``Runtime``: device, compute dtype, limits):
     ``forward(x, ctx, view, writes_cache) -> delta`` with x [T,d] in the
     compute dtype, ``ctx`` the step's ``StepContext``, ``view`` the
     ``CacheEntryView`` of the call's cache entry; returns [T,d] or [S,T,d].
+    A part whose forward reads device data on the host sets the class
+    attribute ``graph_safe = False``; decode steps then run eagerly.
 ``FeedForward(spec, weights, rt)``
     ``forward(x, ctx) -> delta``.
 ``Arrangement(block_spec, weights, rt)``

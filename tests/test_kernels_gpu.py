@@ -300,3 +300,43 @@ def test_sample_whole_vocabulary_follows_the_distribution():
     kernels.sample(dev(logits), dev(torch.ones(B)), dev(torch.zeros(B, dtype=torch.int32)),
                    dev(torch.full((B,), 0.5)), None, None, dev(u), out, status)
     assert status.item() != 0
+
+
+@pytest.mark.parametrize("T, N, K", [(1, 256, 64), (8, 384, 512), (64, 200, 1000), (130, 520, 320),
+                                     (300, 128, 4096), (5, 1000, 72)])
+def test_gemm_tc(T, N, K):
+    """The tcgen05 kernel against float64, plain, split and gated."""
+    from llmoxide_b200 import kernels
+    g = torch.Generator().manual_seed(T * N)
+    x = torch.randn(T, K, generator=g).bfloat16()
+    w = (torch.randn(N, K, generator=g) / math.sqrt(K)).bfloat16()
+    x[:, K // 3] *= 30                     # one loud column: a misplaced K block shows
+    want = x.double() @ w.double().t()
+    xd, wd = x.to(DEV), w.to(DEV)
+    assert kernels.gemm_tc_supports(xd, wd)
+    out32 = torch.empty(T, N, dtype=torch.float32, device=DEV)
+    kernels.gemm_tc(xd, wd, out32)
+    assert rel(out32, want) < 1e-5
+    out16 = torch.empty(T, N, dtype=torch.bfloat16, device=DEV)
+    kernels.gemm_tc(xd, wd, out16)
+    assert rel(out16, want) < 6e-3
+    for s in (2, 3):
+        parts = torch.full((s, T, N), float("nan"), dtype=torch.float32, device=DEV)
+        kernels.gemm_tc(xd, wd, parts, n_split=s)
+        assert rel(parts.sum(0), want) < 1e-5
+    if N % 2 == 0:
+        F = N // 2
+        act = torch.empty(T, F, dtype=torch.bfloat16, device=DEV)
+        kernels.gemm_tc(xd, wd, act, gated=True)
+        gate, up = want[:, :F].float(), want[:, F:].float()
+        assert rel(act, plain.silu(gate) * up) < 8e-3
+    assert kernels.gemm_tc_status() == 0
+
+
+def test_gemm_tc_refuses_what_it_cannot_do():
+    from llmoxide_b200 import kernels
+    x = torch.randn(4, 76).bfloat16().to(DEV)       # K not a multiple of 8
+    w = torch.randn(16, 76).bfloat16().to(DEV)
+    assert not kernels.gemm_tc_supports(x, w)
+    with pytest.raises(Exception):
+        kernels.gemm_tc(x, w, torch.empty(4, 16, dtype=torch.bfloat16, device=DEV))

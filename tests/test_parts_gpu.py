@@ -223,6 +223,8 @@ def _register_toys():
         """y_t = W * mean(x_0..x_t): its state is the running sum and the count,
         per sequence, of fixed size, kept in the cache's state area."""
 
+        graph_safe = False      # forward reads the batch's layout on the host
+
         def __init__(self, spec, position, weights, rt):
             self.d = spec["hidden_size"]
             self.w = weights.pop(spec.tensors["w"].name).float()
