@@ -36,6 +36,8 @@ NVCC_FLAGS = ["-O3", "-std=c++17", "-lineinfo", "-Xcompiler", "-fPIC,-fvisibilit
 LIBRARIES = {
     "elementwise": (["elementwise.cu"], []),
     "attention": (["attention.cu"], []),
+    "attention_decode": (["attention_decode.cu"], []),
+    "attention_prefill": (["attention_prefill.cu"], []),
     "gemm_fma": (["gemm_fma.cu"], []),
     "gemm_tc": (["gemm_tc.cu"], []),
     "sampling": (["sampling.cu"], []),

@@ -192,6 +192,66 @@ def attention_paged(q, out, k_cache, v_cache, block_table, token_seq, token_pos,
              int(window or 0), scale, _stream()), "attention_paged")
 
 
+N_SM = 148
+
+
+def decode_split(n_seqs: int, n_kv_heads: int, group: int, n_pages: int) -> tuple:
+    """(pages_per_warp, n_chunks) for the decode attention kernel: enough CTAs
+    to fill the GPU about four times over, each warp walking whole pages.  It
+    depends on the batch's shape only (not on its lengths), so a captured
+    graph stays valid while the shape does."""
+    base = n_seqs * n_kv_heads * ((group + 3) // 4)
+    chunks_wanted = max(1, -(-4 * N_SM // base))
+    ppw = max(1, n_pages // (4 * chunks_wanted))
+    return ppw, -(-n_pages // (4 * ppw))
+
+
+def attention_decode(q, out, k_cache, v_cache, block_table, seq_past, n_heads: int, n_kv_heads: int,
+                     head_dim: int, window, scale: float) -> None:
+    """One new token per sequence, bfloat16: q, out [B,H*D] in batch order;
+    seq_past[b] is the token's position.  The key range is split over CTAs and
+    merged through a float32 workspace."""
+    _dev(q, out, k_cache, v_cache, block_table, seq_past)
+    _contig("q", q), _contig("out", out), _contig("block_table", block_table)
+    assert q.dtype == torch.bfloat16 and k_cache.dtype == torch.bfloat16 and out.dtype == torch.bfloat16
+    if head_dim % 16 or head_dim > 256:
+        raise Unsupported(f"head_dim {head_dim}: the decode attention kernel takes multiples of 16 up to 256")
+    B = q.shape[0]
+    n_pages = block_table.shape[1]
+    if window:
+        n_pages = min(n_pages, (window + PAGE - 2) // PAGE + 1)
+    ppw, n_chunks = decode_split(B, n_kv_heads, n_heads // n_kv_heads, n_pages)
+    ws = torch.empty(B * n_heads * n_chunks * (head_dim + 2), dtype=torch.float32, device=q.device)
+    f = _fn("attention_decode", "llmx_attention_decode",
+            [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int,
+             c_int, c_int, c_float, c_int, c_int, c_void_p])
+    _check(f(_ptr(q), _ptr(out), _ptr(k_cache), _ptr(v_cache), _ptr(block_table), block_table.shape[1],
+             _ptr(seq_past), _ptr(ws), B, n_heads, n_kv_heads, head_dim, int(window or 0), scale, ppw, n_chunks,
+             _stream()), "attention_decode")
+    global launch_count
+    launch_count += 1   # the merge kernel
+
+
+def attention_prefill_supports(q, k_cache, head_dim: int) -> bool:
+    return q.dtype == torch.bfloat16 and k_cache.dtype == torch.bfloat16 and head_dim in (64, 128)
+
+
+def attention_prefill(q, out, k_cache, v_cache, block_table, seq_start, seq_past, n_seqs: int, max_new: int,
+                      n_heads: int, n_kv_heads: int, head_dim: int, window, scale: float) -> None:
+    """Prompt attention on the tensor cores, bfloat16, head sizes 64 and 128:
+    q, out [T,H*D] packed sequence after sequence."""
+    _dev(q, out, k_cache, v_cache, block_table, seq_start, seq_past)
+    _contig("q", q), _contig("out", out), _contig("block_table", block_table)
+    if not attention_prefill_supports(q, k_cache, head_dim):
+        raise Unsupported(f"the tiled prompt attention takes bfloat16 and head sizes 64 or 128, not {head_dim}")
+    f = _fn("attention_prefill", "llmx_attention_prefill",
+            [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int,
+             c_int, c_int, c_int, c_float, c_void_p])
+    _check(f(_ptr(q), _ptr(out), _ptr(k_cache), _ptr(v_cache), _ptr(block_table), block_table.shape[1],
+             _ptr(seq_start), _ptr(seq_past), n_seqs, max_new, n_heads, n_kv_heads, head_dim, int(window or 0),
+             scale, _stream()), "attention_prefill")
+
+
 def gemm_fma(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> None:
     """out[M,N] = x[M,K] @ w[N,K]^T on the FMA units, float32 accumulation in
     the order k = 0..K-1.  Rows may be strided; the K axis must be dense."""

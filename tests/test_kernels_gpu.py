@@ -340,3 +340,64 @@ def test_gemm_tc_refuses_what_it_cannot_do():
     assert not kernels.gemm_tc_supports(x, w)
     with pytest.raises(Exception):
         kernels.gemm_tc(x, w, torch.empty(4, 16, dtype=torch.bfloat16, device=DEV))
+
+
+def _attention_case(H, G, D, lens, pasts, window, seed=0):
+    """Sequences with ``pasts[i]`` cached positions and ``lens[i]`` new tokens;
+    returns everything the bfloat16 attention kernels need and the plain result
+    for the new tokens."""
+    torch.manual_seed(seed)
+    qs, ks, vs, want = [], [], [], []
+    for L, P in zip(lens, pasts):
+        n = P + L
+        q = torch.randn(n, H, D).bfloat16().float()
+        k = torch.randn(n, G, D).bfloat16().float()
+        v = torch.randn(n, G, D).bfloat16().float()
+        if n > 40:      # a far key among many answers one late query loudly
+            k[2, G - 1] = 0.0
+            k[2, G - 1, :8] = 3.0
+            q[n - 1, H - 1] = 0.0
+            q[n - 1, H - 1, :8] = 3.0
+        full = plain.causal_attention(q, k, v, G, window)
+        qs.append(q[P:]), ks.append(k), vs.append(v), want.append(full[P:])
+    kc, vc, table = _paged(list(zip(ks, vs)), G, D, torch.bfloat16, n_pages=64)
+    starts = torch.tensor([0] + list(np.cumsum(lens)), dtype=torch.int32)
+    q_all = torch.cat(qs).reshape(-1, H * D).bfloat16()
+    return q_all, kc, vc, table, starts, torch.tensor(pasts, dtype=torch.int32), torch.cat(want).reshape(-1, H * D)
+
+
+@pytest.mark.parametrize("H, G, D", [(8, 2, 128), (6, 6, 64), (5, 1, 128)])
+@pytest.mark.parametrize("window", [None, 100])
+def test_attention_prefill_tiled(H, G, D, window):
+    from llmoxide_b200 import kernels
+    lens, pasts = [1, 64, 200, 65, 130], [0, 0, 0, 70, 300]     # whole prompts and later chunks of prompts
+    q, kc, vc, table, starts, past, want = _attention_case(H, G, D, lens, pasts, window)
+    out = torch.full_like(q, float("nan"), device=DEV)
+    kernels.attention_prefill(q.to(DEV), out, kc.to(DEV), vc.to(DEV), table.to(DEV), starts.to(DEV), past.to(DEV),
+                              len(lens), max(lens), H, G, D, window, 1 / math.sqrt(D))
+    assert not out.isnan().any()
+    for i in range(len(lens)):
+        lo, hi = starts[i], starts[i + 1]
+        assert rel(out[lo:hi], want[lo:hi]) < 1.2e-2, (i, lens[i], pasts[i])
+
+
+@pytest.mark.parametrize("H, G, D", [(8, 2, 128), (6, 6, 64), (5, 1, 48), (16, 2, 80), (4, 4, 256)])
+@pytest.mark.parametrize("window", [None, 100])
+def test_attention_decode_split(H, G, D, window):
+    from llmoxide_b200 import kernels
+    pasts = [0, 63, 64, 500, 1500, 129]
+    lens = [1] * len(pasts)
+    q, kc, vc, table, starts, past, want = _attention_case(H, G, D, lens, pasts, window)
+    out = torch.full_like(q, float("nan"), device=DEV)
+    kernels.attention_decode(q.to(DEV), out, kc.to(DEV), vc.to(DEV), table.to(DEV), past.to(DEV), H, G, D, window,
+                             1 / math.sqrt(D))
+    assert not out.isnan().any()
+    for i in range(len(pasts)):
+        assert rel(out[i], want[i]) < 1.2e-2, (i, pasts[i])
+    # a wider block table (another split of the keys) gives the same result up to rounding
+    wide = torch.full((len(pasts), 64), -1, dtype=torch.int32)
+    wide[:, : table.shape[1]] = table
+    out2 = torch.empty_like(out)
+    kernels.attention_decode(q.to(DEV), out2, kc.to(DEV), vc.to(DEV), wide.to(DEV), past.to(DEV), H, G, D, window,
+                             1 / math.sqrt(D))
+    assert rel(out2, out) < 1e-2
