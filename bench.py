@@ -121,6 +121,8 @@ def main() -> int:
     ap.add_argument("--prefill-tokens", type=int, default=2048)
     ap.add_argument("--no-points", action="store_true", help="skip the batch 1 and batch 64 points")
     ap.add_argument("--no-graphs", action="store_true")
+    ap.add_argument("--cuda-profiler", choices=["decode", "prefill"], default=None,
+                    help="bracket that region with cudaProfilerStart/Stop (for ncu --profile-from-start off)")
     args = ap.parse_args()
 
     if args.impl == "reference":
@@ -175,6 +177,11 @@ def main() -> int:
 
     for _ in range(3):
         one_prefill()
+    if args.cuda_profiler == "prefill":
+        torch.cuda.profiler.start()
+        one_prefill()
+        torch.cuda.synchronize()
+        torch.cuda.profiler.stop()
     prefill_ms = statistics.median(event_time(one_prefill) for _ in range(5))
     prefill = dict(value=T / prefill_ms * 1e3, tokens=T, ms=prefill_ms,
                    frac=prefill_flops(T) / (prefill_ms * 1e-3) / (pk["bf16_tflops"] * 1e12),
@@ -197,7 +204,11 @@ def main() -> int:
             for i in range(warmup, warmup + steps):
                 eng.step([(s, [t]) for s, t in zip(slots, toks[i])])
 
+        if sampler and args.cuda_profiler == "decode":
+            torch.cuda.profiler.start()
         ms = event_time(run)
+        if sampler and args.cuda_profiler == "decode":
+            torch.cuda.profiler.stop()
         clocks = sampler.stop() if sampler else None
         launches = kernels.launch_count - launches
         for s in slots:

@@ -26,6 +26,8 @@ __global__ void attention_paged_kernel(const TA* __restrict__ q, TA* __restrict_
                                        const int* __restrict__ token_seq, const int* __restrict__ token_pos,
                                        int H, int G, int D, int window, float scale) {
   extern __shared__ float q_buf[];  // [ATT_WARPS][D]
+  pdl_launch_dependents();
+  pdl_wait();
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int t = blockIdx.y;
   const int hq = blockIdx.x * ATT_WARPS + warp;
@@ -93,7 +95,7 @@ LLMX_API int llmx_attention_paged(const void* q, void* out, int act_dtype, const
   dim3 grid((H + ATT_WARPS - 1) / ATT_WARPS, n_tokens);
   const size_t smem = (size_t)ATT_WARPS * D * sizeof(float);
 #define CASE(TA, TC)                                                                                      \
-  attention_paged_kernel<TA, TC><<<grid, ATT_WARPS * 32, smem, stream>>>(                                 \
+  launch_pdl(attention_paged_kernel<TA, TC>, grid, dim3(ATT_WARPS * 32), smem, stream,                    \
       (const TA*)q, (TA*)out, (const TC*)k_cache, (const TC*)v_cache, block_table, table_width, token_seq, \
       token_pos, H, G, D, window, scale)
   if (act_dtype == LLMX_F32 && cache_dtype == LLMX_F32) CASE(float, float);

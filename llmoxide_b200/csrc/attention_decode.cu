@@ -66,6 +66,8 @@ attention_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_c
   __shared__ float merge_acc[DEC_WARPS][DEC_MAX_HEADS][D];
   __shared__ float merge_ml[DEC_WARPS][DEC_MAX_HEADS][2];
 
+  pdl_launch_dependents();
+  pdl_wait();
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int sub = lane >> 3;            // which of the 4 keys of an iteration
   const int part = lane & 7;            // which slice of the head's dims
@@ -229,6 +231,8 @@ attention_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_c
 // Merges the chunk partials of each (sequence, head): out = sum_c e^(m_c - m) acc_c / sum_c e^(m_c - m) l_c.
 __global__ void attention_decode_merge_kernel(const float* __restrict__ ws, bf16* __restrict__ out, int H, int D,
                                               int n_chunks) {
+  pdl_launch_dependents();
+  pdl_wait();
   const int bh = blockIdx.x;
   const float* base = ws + (size_t)bh * n_chunks * (D + 2);
   float mx = -INFINITY;
@@ -254,12 +258,13 @@ static int launch_decode(const void* q, void* out, const void* k_cache, const vo
   const int R = H / G;
   const int head_groups = (R + DEC_MAX_HEADS - 1) / DEC_MAX_HEADS;
   dim3 grid(n_chunks, G * head_groups, B);
-  attention_decode_kernel<D><<<grid, DEC_WARPS * 32, 0, stream>>>(
+  launch_pdl(attention_decode_kernel<D>, grid, dim3(DEC_WARPS * 32), 0, stream,
       (const bf16*)q, (const bf16*)k_cache, (const bf16*)v_cache, block_table, table_width, seq_past, ws, H, G,
       window, scale, pages_per_warp, n_chunks);
   int rc = LLMX_LAUNCH_STATUS();
   if (rc) return rc;
-  attention_decode_merge_kernel<<<B * H, D <= 64 ? 64 : 128, 0, stream>>>(ws, (bf16*)out, H, D, n_chunks);
+  launch_pdl(attention_decode_merge_kernel, dim3(B * H), dim3(D <= 64 ? 64 : 128), 0, stream, (const float*)ws,
+             (bf16*)out, H, D, n_chunks);
   return LLMX_LAUNCH_STATUS();
 }
 

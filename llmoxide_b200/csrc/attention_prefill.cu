@@ -68,6 +68,8 @@ attention_prefill_kernel(const bf16* __restrict__ q, bf16* __restrict__ out, con
   const uint32_t sQ = (uint32_t)__cvta_generic_to_shared(smem);
   const uint32_t sKV = sQ + PF_BQ * D * 2;   // stage s: K at sKV + s*2*TILE_BYTES, V after it
 
+  pdl_launch_dependents();
+  pdl_wait();
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int b = blockIdx.z, hq = blockIdx.y;
   const int g = hq / (H / G);
@@ -255,7 +257,7 @@ static int launch_prefill(const void* q, void* out, const void* k_cache, const v
     attr_set = true;
   }
   dim3 grid((max_new + PF_BQ - 1) / PF_BQ, H, B);
-  kernel<<<grid, PF_THREADS, smem, stream>>>((const bf16*)q, (bf16*)out, (const bf16*)k_cache, (const bf16*)v_cache,
+  launch_pdl(kernel, grid, dim3(PF_THREADS), smem, stream, (const bf16*)q, (bf16*)out, (const bf16*)k_cache, (const bf16*)v_cache,
                                              block_table, table_width, seq_start, seq_past, H, G, window,
                                              scale * 1.4426950408889634f);
   return LLMX_LAUNCH_STATUS();

@@ -149,6 +149,9 @@ def compile_library(name: str, verbose=True) -> Path:
                 tmp.unlink(missing_ok=True)
                 raise ExtensionMissing(f"nvcc failed on {name}:\n{' '.join(cmd)}\n{out}")
             os.replace(tmp, target)
+            for old in target.parent.glob(f"libllmx_{name}-*.so"):   # earlier versions of this library
+                if old != target:
+                    old.unlink(missing_ok=True)
             if verbose:
                 _say(f"built {target.name} in {time.time() - t0:.1f} s")
             return target

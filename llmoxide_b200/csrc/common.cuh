@@ -19,6 +19,36 @@ typedef __nv_bfloat16 bf16;
 // dtype tags passed through the C interface
 enum { LLMX_F32 = 0, LLMX_BF16 = 1 };
 
+// ---------------------------------------------------------------------------
+// Programmatic dependent launch.  Every kernel of this library is launched
+// with the stream-serialization attribute and begins with
+// pdl_launch_dependents() (the next kernel's CTAs may be scheduled as soon as
+// all of this kernel's have started) and pdl_wait() (block until the kernel
+// before has finished and its writes are visible) ahead of its first read or
+// write of anything another kernel touches.  Decode steps are chains of short
+// kernels; this overlaps each launch and prologue with the kernel before.
+// ---------------------------------------------------------------------------
+#ifdef __CUDACC__
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+template <typename... KArgs, typename... Args>
+static inline cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem,
+                                     cudaStream_t stream, Args... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  return cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
+}
+#endif
+
 // Tokens per cache page.  A sequence's position p lives in its logical page
 // p / PAGE at row p % PAGE; the block table maps logical to physical pages.
 #define LLMX_PAGE 64

@@ -15,6 +15,8 @@
 template <typename TW>
 __global__ void embed_kernel(const TW* __restrict__ table, const int* __restrict__ tokens,
                              float* __restrict__ h, int d, int vocab) {
+  pdl_launch_dependents();
+  pdl_wait();
   const int t = blockIdx.x;
   int tok = tokens[t];
   tok = tok < 0 ? 0 : (tok >= vocab ? vocab - 1 : tok);  // never read outside the table
@@ -29,9 +31,9 @@ LLMX_API int llmx_embed(const void* table, int table_dtype, const int* tokens, f
   if (d <= 0 || vocab <= 0) return LLMX_REFUSED(1);
   const int threads = d >= 1024 ? 256 : 128;
   if (table_dtype == LLMX_F32)
-    embed_kernel<float><<<n_tokens, threads, 0, stream>>>((const float*)table, tokens, h, d, vocab);
+    launch_pdl(embed_kernel<float>, dim3(n_tokens), dim3(threads), 0, stream, (const float*)table, tokens, h, d, vocab);
   else if (table_dtype == LLMX_BF16)
-    embed_kernel<bf16><<<n_tokens, threads, 0, stream>>>((const bf16*)table, tokens, h, d, vocab);
+    launch_pdl(embed_kernel<bf16>, dim3(n_tokens), dim3(threads), 0, stream, (const bf16*)table, tokens, h, d, vocab);
   else
     return LLMX_REFUSED(2);
   return LLMX_LAUNCH_STATUS();
@@ -44,8 +46,8 @@ LLMX_API int llmx_embed(const void* table, int table_dtype, const int* tokens, f
 //   out[r,:] = v * (1/sqrt(mean(v^2)+eps)) * gain
 // One block per row; the row is staged in shared memory as float32.
 // ---------------------------------------------------------------------------
-#define NORM_THREADS 256
-
+// Threads per row are fixed by d alone (so the reduction order does not depend on the batch):
+// a thread takes 4 consecutive elements per pass, and rows up to 4096 wide finish in one pass.
 template <typename TD, typename TO>
 __global__ void add_rms_norm_kernel(float* __restrict__ h, const TD* __restrict__ delta, int n_split,
                                     size_t split_stride, const int* __restrict__ rows,
@@ -53,26 +55,56 @@ __global__ void add_rms_norm_kernel(float* __restrict__ h, const TD* __restrict_
                                     int d, int write_h) {
   extern __shared__ float row_buf[];
   __shared__ float red[32];
+  pdl_launch_dependents();
+  pdl_wait();
   const int r = blockIdx.x;
   const int t = rows ? rows[r] : r;
   float* hrow = h + (size_t)t * d;
+  const int nthreads = blockDim.x;
   float ss = 0.f;
-  for (int i = threadIdx.x; i < d; i += NORM_THREADS) {
-    float v = hrow[i];
-    if (delta) {
-      const TD* p = delta + (size_t)t * d + i;
-      for (int s = 0; s < n_split; ++s) v += to_f32(p[s * split_stride]);
-      if (write_h) hrow[i] = v;
+  if ((d & 3) == 0) {
+    for (int i = threadIdx.x * 4; i < d; i += nthreads * 4) {
+      float4 v = *reinterpret_cast<const float4*>(hrow + i);
+      if (delta) {
+        const TD* p = delta + (size_t)t * d + i;
+        for (int s = 0; s < n_split; ++s) {
+          const TD* ps = p + s * split_stride;
+          v.x += to_f32(ps[0]);
+          v.y += to_f32(ps[1]);
+          v.z += to_f32(ps[2]);
+          v.w += to_f32(ps[3]);
+        }
+        if (write_h) *reinterpret_cast<float4*>(hrow + i) = v;
+      }
+      *reinterpret_cast<float4*>(row_buf + i) = v;
+      ss += v.x * v.x;
+      ss += v.y * v.y;
+      ss += v.z * v.z;
+      ss += v.w * v.w;
     }
-    row_buf[i] = v;
-    ss += v * v;
+  } else {
+    for (int i = threadIdx.x; i < d; i += nthreads) {
+      float v = hrow[i];
+      if (delta) {
+        const TD* p = delta + (size_t)t * d + i;
+        for (int s = 0; s < n_split; ++s) v += to_f32(p[s * split_stride]);
+        if (write_h) hrow[i] = v;
+      }
+      row_buf[i] = v;
+      ss += v * v;
+    }
   }
   const float total = block_sum(ss, red);
   const float scale = 1.0f / sqrtf(total / (float)d + eps);
   if (out) {
     TO* orow = out + (size_t)r * d;
-    for (int i = threadIdx.x; i < d; i += NORM_THREADS) orow[i] = from_f32<TO>((row_buf[i] * scale) * gain[i]);
+    for (int i = threadIdx.x; i < d; i += nthreads) orow[i] = from_f32<TO>((row_buf[i] * scale) * gain[i]);
   }
+}
+
+static int norm_threads(int d) {
+  int t = (d / 4 + 31) / 32 * 32;
+  return t < 64 ? 64 : (t > 1024 ? 1024 : t);
 }
 
 template <typename TD, typename TO>
@@ -86,8 +118,8 @@ static int launch_add_rms_norm(float* h, const void* delta, int n_split, size_t 
     cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
   }
-  kernel<<<n_rows, NORM_THREADS, smem, stream>>>(h, (const TD*)delta, n_split, split_stride, rows, gain, eps,
-                                                 (TO*)out, d, write_h);
+  launch_pdl(kernel, dim3(n_rows), dim3(norm_threads(d)), smem, stream, h, (const TD*)delta, n_split, split_stride, rows, gain, eps,
+                                                    (TO*)out, d, write_h);
   return LLMX_LAUNCH_STATUS();
 }
 
@@ -115,8 +147,9 @@ LLMX_API int llmx_add_rms_norm(float* h, const void* delta, int delta_dtype, int
 // ---------------------------------------------------------------------------
 #define QKV_WARPS 4
 
-template <typename TA, typename TC>
-__global__ void qk_norm_rope_cache_kernel(const TA* __restrict__ qkv, TA* __restrict__ q_out,
+template <typename TIN, typename TA, typename TC>
+__global__ void qk_norm_rope_cache_kernel(const TIN* __restrict__ qkv, int n_split, size_t split_stride,
+                                          TA* __restrict__ q_out,
                                           TC* __restrict__ k_cache, TC* __restrict__ v_cache,
                                           const int* __restrict__ block_table, int table_width,
                                           const int* __restrict__ token_seq, const int* __restrict__ token_pos,
@@ -125,14 +158,22 @@ __global__ void qk_norm_rope_cache_kernel(const TA* __restrict__ qkv, TA* __rest
                                           const float* __restrict__ sin_t, int n_rot, int H, int G, int D,
                                           int write_cache) {
   extern __shared__ float head_buf[];
+  pdl_launch_dependents();
+  pdl_wait();
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int t = blockIdx.y;
   const int slot = blockIdx.x * QKV_WARPS + warp;  // which head of the fused row
   const int n_slots = write_cache ? H + 2 * G : H;
   if (slot >= n_slots) return;
   float* buf = head_buf + warp * D;
-  const TA* src = qkv + (size_t)t * (H + 2 * G) * D + (size_t)slot * D;
+  const TIN* src = qkv + (size_t)t * (H + 2 * G) * D + (size_t)slot * D;
   const int pos = token_pos[t];
+  // the head's values: one tensor, or split partials added in order
+  auto value = [&](int i) {
+    float v = to_f32(src[i]);
+    for (int s = 1; s < n_split; ++s) v += to_f32(src[s * split_stride + i]);
+    return v;
+  };
   const bool is_q = slot < H, is_k = !is_q && slot < H + G;
 
   TC* cache_row = nullptr;
@@ -142,13 +183,13 @@ __global__ void qk_norm_rope_cache_kernel(const TA* __restrict__ qkv, TA* __rest
     cache_row = (is_k ? k_cache : v_cache) + cache_row_offset(page, g, pos % LLMX_PAGE, G, D);
   }
   if (!is_q && !is_k) {  // v: stored as it is
-    for (int i = lane; i < D; i += 32) cache_row[i] = from_f32<TC>(to_f32(src[i]));
+    for (int i = lane; i < D; i += 32) cache_row[i] = from_f32<TC>(value(i));
     return;
   }
   const float* gain = is_q ? q_gain : k_gain;
   float ss = 0.f;
   for (int i = lane; i < D; i += 32) {
-    const float v = to_f32(src[i]);
+    const float v = value(i);
     buf[i] = v;
     ss += v * v;
   }
@@ -173,28 +214,33 @@ __global__ void qk_norm_rope_cache_kernel(const TA* __restrict__ qkv, TA* __rest
   }
 }
 
-LLMX_API int llmx_qk_norm_rope_cache(const void* qkv, void* q_out, int act_dtype, void* k_cache, void* v_cache,
-                                     int cache_dtype, const int* block_table, int table_width,
-                                     const int* token_seq, const int* token_pos, const float* q_gain,
-                                     const float* k_gain, float eps, const float* cos_t, const float* sin_t,
-                                     int n_rot, int n_tokens, int H, int G, int D, int write_cache,
-                                     cudaStream_t stream) {
+LLMX_API int llmx_qk_norm_rope_cache(const void* qkv, int in_dtype, int n_split, long long split_stride, void* q_out,
+                                     int act_dtype, void* k_cache, void* v_cache, int cache_dtype,
+                                     const int* block_table, int table_width, const int* token_seq,
+                                     const int* token_pos, const float* q_gain, const float* k_gain, float eps,
+                                     const float* cos_t, const float* sin_t, int n_rot, int n_tokens, int H, int G,
+                                     int D, int write_cache, cudaStream_t stream) {
   if (n_tokens <= 0) return 0;
-  if (H <= 0 || G <= 0 || D <= 0 || n_rot < 0 || n_rot > D || (n_rot & 1)) return LLMX_REFUSED(1);
+  if (H <= 0 || G <= 0 || D <= 0 || n_rot < 0 || n_rot > D || (n_rot & 1) || n_split < 1) return LLMX_REFUSED(1);
   if (n_rot > 0 && (!cos_t || !sin_t)) return LLMX_REFUSED(4);
   const int n_slots = write_cache ? H + 2 * G : H;
   dim3 grid((n_slots + QKV_WARPS - 1) / QKV_WARPS, n_tokens);
   const size_t smem = (size_t)QKV_WARPS * D * sizeof(float);
   if (smem > 48 * 1024) return LLMX_REFUSED(3);
-#define CASE(TA, TC)                                                                                           \
-  qk_norm_rope_cache_kernel<TA, TC><<<grid, QKV_WARPS * 32, smem, stream>>>(                                   \
-      (const TA*)qkv, (TA*)q_out, (TC*)k_cache, (TC*)v_cache, block_table, table_width, token_seq, token_pos, \
-      q_gain, k_gain, eps, cos_t, sin_t, n_rot, H, G, D, write_cache)
-  if (act_dtype == LLMX_F32 && cache_dtype == LLMX_F32) CASE(float, float);
-  else if (act_dtype == LLMX_BF16 && cache_dtype == LLMX_BF16) CASE(bf16, bf16);
-  else if (act_dtype == LLMX_F32 && cache_dtype == LLMX_BF16) CASE(float, bf16);
-  else if (act_dtype == LLMX_BF16 && cache_dtype == LLMX_F32) CASE(bf16, float);
-  else return LLMX_REFUSED(2);
+#define CASE(TIN, TA, TC)                                                                                          \
+  launch_pdl(qk_norm_rope_cache_kernel<TIN, TA, TC>, grid, dim3(QKV_WARPS * 32), smem, stream,                     \
+      (const TIN*)qkv, n_split, (size_t)split_stride, (TA*)q_out, (TC*)k_cache, (TC*)v_cache, block_table,          \
+      table_width, token_seq, token_pos, q_gain, k_gain, eps, cos_t, sin_t, n_rot, H, G, D, write_cache)
+  const int key = in_dtype * 4 + act_dtype * 2 + cache_dtype;
+  switch (key) {
+    case 0: CASE(float, float, float); break;
+    case 1: CASE(float, float, bf16); break;
+    case 2: CASE(float, bf16, float); break;
+    case 3: CASE(float, bf16, bf16); break;
+    case 6: CASE(bf16, bf16, float); break;
+    case 7: CASE(bf16, bf16, bf16); break;
+    default: return LLMX_REFUSED(2);
+  }
 #undef CASE
   return LLMX_LAUNCH_STATUS();
 }
@@ -206,6 +252,8 @@ LLMX_API int llmx_qk_norm_rope_cache(const void* qkv, void* q_out, int act_dtype
 template <typename TI, typename TO>
 __global__ void silu_gate_kernel(const TI* __restrict__ gu, int n_split, size_t split_stride,
                                  TO* __restrict__ act, int n_tokens, int F) {
+  pdl_launch_dependents();
+  pdl_wait();
   const size_t n = (size_t)n_tokens * F;
   for (size_t idx = blockIdx.x * (size_t)blockDim.x + threadIdx.x; idx < n; idx += (size_t)gridDim.x * blockDim.x) {
     const size_t t = idx / F, f = idx - t * F;
@@ -227,7 +275,7 @@ LLMX_API int llmx_silu_gate(const void* gu, int in_dtype, int n_split, long long
   const int threads = 256;
   const int blocks = (int)((n + threads - 1) / threads < 148 * 16 ? (n + threads - 1) / threads : 148 * 16);
 #define CASE(TI, TO) \
-  silu_gate_kernel<TI, TO><<<blocks, threads, 0, stream>>>((const TI*)gu, n_split, (size_t)split_stride, (TO*)act, n_tokens, F)
+  launch_pdl(silu_gate_kernel<TI, TO>, dim3(blocks), dim3(threads), 0, stream, (const TI*)gu, n_split, (size_t)split_stride, (TO*)act, n_tokens, F)
   if (in_dtype == LLMX_F32 && out_dtype == LLMX_F32) CASE(float, float);
   else if (in_dtype == LLMX_F32 && out_dtype == LLMX_BF16) CASE(float, bf16);
   else if (in_dtype == LLMX_BF16 && out_dtype == LLMX_BF16) CASE(bf16, bf16);
@@ -243,6 +291,8 @@ LLMX_API int llmx_silu_gate(const void* gu, int in_dtype, int n_split, long long
 template <typename TI, typename TO>
 __global__ void sum_splits_kernel(const TI* __restrict__ in, int n_split, size_t split_stride, TO* __restrict__ out,
                                   size_t n) {
+  pdl_launch_dependents();
+  pdl_wait();
   for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
     float v = 0.f;
     for (int s = 0; s < n_split; ++s) v += to_f32(in[s * split_stride + i]);
@@ -258,7 +308,7 @@ LLMX_API int llmx_sum_splits(const void* in, int in_dtype, int n_split, long lon
   const long long want = (n + threads - 1) / threads;
   const int blocks = (int)(want < 148 * 16 ? want : 148 * 16);
 #define CASE(TI, TO) \
-  sum_splits_kernel<TI, TO><<<blocks, threads, 0, stream>>>((const TI*)in, n_split, (size_t)split_stride, (TO*)out, (size_t)n)
+  launch_pdl(sum_splits_kernel<TI, TO>, dim3(blocks), dim3(threads), 0, stream, (const TI*)in, n_split, (size_t)split_stride, (TO*)out, (size_t)n)
   if (in_dtype == LLMX_F32 && out_dtype == LLMX_F32) CASE(float, float);
   else if (in_dtype == LLMX_F32 && out_dtype == LLMX_BF16) CASE(float, bf16);
   else if (in_dtype == LLMX_BF16 && out_dtype == LLMX_BF16) CASE(bf16, bf16);

@@ -20,6 +20,8 @@ gemm_fma_kernel(const TX* __restrict__ X, const TW* __restrict__ W, TY* __restri
                 long long ldx, long long ldw, long long ldy) {
   __shared__ float Xs[FMA_BK][FMA_BM + 4];
   __shared__ float Ws[FMA_BK][FMA_BN + 4];
+  pdl_launch_dependents();
+  pdl_wait();
   const int tid = threadIdx.x;
   const int tx = tid & 15, ty = tid >> 4;
   const int m0 = blockIdx.y * FMA_BM, n0 = blockIdx.x * FMA_BN;
@@ -75,7 +77,7 @@ LLMX_API int llmx_gemm_fma(const void* X, int x_dtype, const void* W, int w_dtyp
   dim3 grid((N + FMA_BN - 1) / FMA_BN, (M + FMA_BM - 1) / FMA_BM);
   if (grid.y > 65535) return LLMX_REFUSED(3);
 #define CASE(TX, TW, TY) \
-  gemm_fma_kernel<TX, TW, TY><<<grid, 256, 0, stream>>>((const TX*)X, (const TW*)W, (TY*)Y, M, N, K, ldx, ldw, ldy)
+  launch_pdl(gemm_fma_kernel<TX, TW, TY>, grid, dim3(256), 0, stream, (const TX*)X, (const TW*)W, (TY*)Y, M, N, K, ldx, ldw, ldy)
   const int key = x_dtype * 4 + w_dtype * 2 + y_dtype;
   switch (key) {
     case 0: CASE(float, float, float); break;

@@ -115,7 +115,7 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, float* v) {
 // MODE 1: two accumulators, rows n and n + F of W; act[T, F] = silu(g) * u.
 // ---------------------------------------------------------------------------
 template <int BN, int MODE, typename TY>
-__global__ void __launch_bounds__(TC_THREADS, 1)
+__global__ void __launch_bounds__(TC_THREADS)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
                TY* __restrict__ Y, int T, int N, int K, long long ldy, int k_blocks_per_split,
                long long split_stride, int F, int n_stages) {
@@ -140,6 +140,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
   const uint32_t full0 = smem_u32(bars), empty0 = full0 + 8u * n_stages, acc_full = empty0 + 8u * n_stages;
   uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(bars + 2 * n_stages + 1);
 
+  pdl_launch_dependents();
   if (threadIdx.x == 0) {
     for (int s = 0; s < n_stages; ++s) {
       mbar_init(full0 + 8u * s, 1);
@@ -164,7 +165,21 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
   if (warp == 0) {
     // ---------------- producer ----------------
     if (lane == 0) {
-      for (int i = 0; i < n_kb; ++i) {
+      // The weights do not depend on the kernel before this one: the first stages' weight tiles are
+      // requested at once, and only the activation tiles wait for that kernel to finish.
+      const int pre = n_kb < n_stages ? n_kb : n_stages;
+      for (int i = 0; i < pre; ++i) {
+        const uint32_t stage = base + (uint32_t)i * STAGE_BYTES, bar = full0 + 8u * i;
+        mbar_expect_tx(bar, STAGE_BYTES);
+        const int k = (kb_begin + i) * TC_BK;
+        tma_load_2d(stage, &map_w, k, n0, bar);
+        if (MODE == 1) tma_load_2d(stage + A_BYTES, &map_w, k, n0 + F, bar);
+      }
+      pdl_wait();
+      for (int i = 0; i < pre; ++i)
+        tma_load_2d(base + (uint32_t)i * STAGE_BYTES + N_ACC * A_BYTES, &map_x, (kb_begin + i) * TC_BK, t0,
+                    full0 + 8u * i);
+      for (int i = pre; i < n_kb; ++i) {
         const int s = i % n_stages;
         const uint32_t parity = ((i / n_stages) & 1) ^ 1;
         if (!mbar_wait(empty0 + 8u * s, parity)) { atomicExch(&g_tc_status, 1); break; }
@@ -206,6 +221,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
     const int n = n0 + row;
     const int n_limit = MODE == 1 ? F : N;
     bool ok = true;
+    if (n_kb == 0) pdl_wait();      // nothing to wait for below: order the stores after the kernel before
     if (n_kb > 0) {
       ok = mbar_wait(acc_full, 0);
       if (!ok && lane == 0) atomicExch(&g_tc_status, 3);
@@ -290,7 +306,10 @@ static int launch(const CUtensorMap& mw, const CUtensorMap& mx, void* Y, int T, 
   constexpr size_t STAGE = (size_t)N_ACC * TC_BM * TC_BK * 2 + (size_t)BN * TC_BK * 2;
   const int total_kb = (K + TC_BK - 1) / TC_BK;
   const int per_split = (total_kb + n_split - 1) / n_split;
-  int stages = (int)((200 * 1024) / STAGE);
+  // Decode tiles (few tokens) stream weights: two CTAs per SM, so that one CTA's prologue and epilogue
+  // overlap the other's main loop.  Prompt tiles take the whole SM.
+  const size_t budget = BN <= 64 ? 100 * 1024 : 200 * 1024;
+  int stages = (int)(budget / STAGE);
   if (stages > 12) stages = 12;
   if (stages > per_split) stages = per_split < 2 ? 2 : per_split;
   const size_t smem = 1024 + (size_t)stages * STAGE + (2 * stages + 1) * 8 + 16;
@@ -303,7 +322,7 @@ static int launch(const CUtensorMap& mw, const CUtensorMap& mx, void* Y, int T, 
   }
   const int rows = MODE == 1 ? F : N;
   dim3 grid((rows + TC_BM - 1) / TC_BM, (T + BN - 1) / BN, n_split);
-  kernel<<<grid, TC_THREADS, smem, stream>>>(mw, mx, (TY*)Y, T, N, K, ldy, per_split, split_stride, F, stages);
+  launch_pdl(kernel, grid, dim3(TC_THREADS), smem, stream, mw, mx, (TY*)Y, T, N, K, ldy, per_split, split_stride, F, stages);
   return LLMX_LAUNCH_STATUS();
 }
 

@@ -45,6 +45,8 @@ sample_kernel(float* __restrict__ logits, long long ld, int V, const float* __re
   __shared__ int sh_result;
   __shared__ float sh_f;
 
+  pdl_launch_dependents();
+  pdl_wait();
   const int b = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   float* row = logits + (size_t)b * ld;
 
@@ -303,7 +305,7 @@ LLMX_API int llmx_sample(float* logits, long long ld, int n_rows, int V, const f
   if (n_rows <= 0) return 0;
   if (V <= 0 || ld < V || !temperature || !top_k || !top_p || !uniform || !out_tokens || !status)
     return LLMX_REFUSED(1);
-  sample_kernel<<<n_rows, SMP_THREADS, 0, stream>>>(logits, ld, V, temperature, top_k, top_p, repeat_penalty,
+  launch_pdl(sample_kernel, dim3(n_rows), dim3(SMP_THREADS), 0, stream, logits, ld, V, temperature, top_k, top_p, repeat_penalty,
                                                      recent, recent_width, uniform, out_tokens, status);
   return LLMX_LAUNCH_STATUS();
 }
@@ -313,6 +315,8 @@ __global__ void __launch_bounds__(SMP_THREADS)
 argmax_kernel(const float* __restrict__ logits, long long ld, int V, int* __restrict__ out_tokens) {
   __shared__ float red_v[32];
   __shared__ int red_i[32];
+  pdl_launch_dependents();
+  pdl_wait();
   const int b = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const float* row = logits + (size_t)b * ld;
   float best = -INFINITY;
@@ -344,6 +348,6 @@ LLMX_API int llmx_argmax(const float* logits, long long ld, int n_rows, int V, i
                          cudaStream_t stream) {
   if (n_rows <= 0) return 0;
   if (V <= 0 || ld < V) return LLMX_REFUSED(1);
-  argmax_kernel<<<n_rows, SMP_THREADS, 0, stream>>>(logits, ld, V, out_tokens);
+  launch_pdl(argmax_kernel, dim3(n_rows), dim3(SMP_THREADS), 0, stream, logits, ld, V, out_tokens);
   return LLMX_LAUNCH_STATUS();
 }

@@ -70,4 +70,8 @@ class DecoderModel:
         if n_want == 0:
             return torch.empty((0, self.spec.vocab_size), dtype=torch.float32, device=self.rt.device)
         x = self.final_norm.add_forward(h, pending, rows=ctx.want_rows, write_h=False)
-        return self.head(x, out_dtype=torch.float32)
+        logits = self.head(x, out_dtype=torch.float32, splits_ok=True)
+        if logits.dim() == 3:       # split partials of the reduction
+            parts, logits = logits, torch.empty(logits.shape[1:], dtype=torch.float32, device=self.rt.device)
+            kernels.sum_splits(parts, logits)
+        return logits

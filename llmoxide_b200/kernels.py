@@ -131,24 +131,28 @@ def add_rms_norm(h: torch.Tensor, delta, gain: torch.Tensor, eps: float, out, ro
 def qk_norm_rope_cache(qkv, q_out, k_cache, v_cache, block_table, token_seq, token_pos, q_gain, k_gain,
                        eps: float, cos, sin, n_rot: int, n_heads: int, n_kv_heads: int, head_dim: int,
                        write_cache: bool = True) -> None:
-    """qkv [T,(H+2G)*D] -> q_out [T,H*D] (normed, rotated) and, when
-    ``write_cache``, k (normed, rotated) and v into the paged cache entry
-    ``k_cache``/``v_cache`` [n_pages,G,PAGE,D] at each token's position."""
+    """qkv [T,(H+2G)*D], or float32 split partials [S,T,(H+2G)*D] summed in
+    order -> q_out [T,H*D] (normed, rotated) and, when ``write_cache``, k
+    (normed, rotated) and v into the paged cache entry ``k_cache``/``v_cache``
+    [n_pages,G,PAGE,D] at each token's position."""
     _dev(qkv, q_out, k_cache, v_cache, block_table, token_seq, token_pos)
     _contig("qkv", qkv), _contig("q_out", q_out), _contig("block_table", block_table)
-    T = qkv.shape[0]
-    assert qkv.shape[1] == (n_heads + 2 * n_kv_heads) * head_dim
-    assert q_out.dtype == qkv.dtype and k_cache.dtype == v_cache.dtype
-    assert k_cache.is_contiguous() and v_cache.is_contiguous()
+    n_split, stride = 1, 0
+    if qkv.dim() == 3:
+        n_split, stride = qkv.shape[0], qkv.stride(0)
+    T = qkv.shape[-2]
+    assert qkv.shape[-1] == (n_heads + 2 * n_kv_heads) * head_dim
+    assert k_cache.dtype == v_cache.dtype and k_cache.is_contiguous() and v_cache.is_contiguous()
     if head_dim > 256 or head_dim % 2:
         raise Unsupported(f"head_dim {head_dim}: the q/k norm and rotation kernel takes even sizes up to 256")
     f = _fn("elementwise", "llmx_qk_norm_rope_cache",
-            [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p,
-             c_void_p, c_void_p, c_float, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p])
-    _check(f(_ptr(qkv), _ptr(q_out), _tag(qkv), _ptr(k_cache), _ptr(v_cache), _tag(k_cache), _ptr(block_table),
-             block_table.shape[1], _ptr(token_seq), _ptr(token_pos), _ptr(q_gain), _ptr(k_gain), eps,
-             _ptr(cos), _ptr(sin), n_rot, T, n_heads, n_kv_heads, head_dim, int(write_cache), _stream()),
-           "qk_norm_rope_cache")
+            [c_void_p, c_int, c_int, c_longlong, c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, c_int,
+             c_void_p, c_void_p, c_void_p, c_void_p, c_float, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
+             c_int, c_int, c_void_p])
+    _check(f(_ptr(qkv), _tag(qkv), n_split, stride, _ptr(q_out), _tag(q_out), _ptr(k_cache), _ptr(v_cache),
+             _tag(k_cache), _ptr(block_table), block_table.shape[1], _ptr(token_seq), _ptr(token_pos),
+             _ptr(q_gain), _ptr(k_gain), eps, _ptr(cos), _ptr(sin), n_rot, T, n_heads, n_kv_heads, head_dim,
+             int(write_cache), _stream()), "qk_norm_rope_cache")
 
 
 def silu_gate(gu: torch.Tensor, out: torch.Tensor) -> None:

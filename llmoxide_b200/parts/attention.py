@@ -59,13 +59,13 @@ class GQAttention:
         cos, sin, n_rot = tables if tables is not None else (None, None, 0)
         block_table = ctx.block_tables[view.group]
         if writes_cache:
-            qkv = self.qkv(x)
+            qkv = self.qkv(x, splits_ok=True)
         else:
             # A call that reads another call's cache entry makes only queries.
             q_part = self.q_only(x)
             qkv = torch.empty((T, (H + 2 * G) * D), dtype=q_part.dtype, device=x.device)
             qkv[:, : H * D] = q_part
-        q = torch.empty((T, H * D), dtype=qkv.dtype, device=x.device)
+        q = torch.empty((T, H * D), dtype=self.rt.act_dtype, device=x.device)
         kernels.qk_norm_rope_cache(qkv, q, view.k, view.v, block_table, ctx.token_seq, ctx.token_pos,
                                    self.q_gain, self.k_gain, self.eps, cos, sin, n_rot, H, G, D, writes_cache)
         out = torch.empty_like(q)

@@ -15,17 +15,28 @@ from .. import kernels
 
 N_SM = 148
 TILE_ROWS = 128
-MIN_KBLOCKS_PER_SPLIT = 8     # 64-element blocks of K per split, at least
+CTAS_PER_SM = 2               # what the kernel fits per SM at decode tile sizes
+MIN_KBLOCKS_PER_SPLIT = 4     # 64-element blocks of K per split, at least
 
 
 def choose_splits(n_rows: int, k: int, n_tokens: int, max_splits: int = 16) -> int:
+    """How many ways to split the reduction over K at ``n_tokens`` tokens.
+    The aim is whole rounds of N_SM * CTAS_PER_SM CTAs, bounded so that the
+    float32 partials (written once, read once) stay a few per cent of the
+    weight bytes."""
     if n_tokens > 64:
         return 1
     tiles = (n_rows + TILE_ROWS - 1) // TILE_ROWS
     k_blocks = (k + 63) // 64
-    s = max(1, N_SM // tiles)
-    s = min(s, max(1, k_blocks // MIN_KBLOCKS_PER_SPLIT), max_splits)
-    return s
+    slots = N_SM * CTAS_PER_SM
+    cap = min(max_splits, max(1, k_blocks // MIN_KBLOCKS_PER_SPLIT), max(1, int(0.05 * k / n_tokens)))
+    best, best_cost = 1, None
+    for s in range(1, cap + 1):
+        rounds = -(-tiles * s // slots)
+        cost = rounds * (-(-k_blocks // s) + 6)       # k-blocks per CTA plus a fixed prologue/epilogue cost
+        if best_cost is None or cost < best_cost:
+            best, best_cost = s, cost
+    return best
 
 
 class TensorCoreLinear:
