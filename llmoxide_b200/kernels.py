@@ -200,14 +200,15 @@ N_SM = 148
 
 
 def decode_split(n_seqs: int, n_kv_heads: int, group: int, n_pages: int) -> tuple:
-    """(pages_per_warp, n_chunks) for the decode attention kernel: enough CTAs
-    to fill the GPU about four times over, each warp walking whole pages.  It
+    """(pages_per_warp, n_chunks) for the decode attention kernel, whose CTA
+    has two warps and so covers 2 * pages_per_warp pages: about two rounds of
+    the CTAs that fit the GPU at once, each warp walking whole pages.  It
     depends on the batch's shape only (not on its lengths), so a captured
     graph stays valid while the shape does."""
-    base = n_seqs * n_kv_heads * ((group + 3) // 4)
+    base = n_seqs * n_kv_heads * ((group + 15) // 16)
     chunks_wanted = max(1, -(-4 * N_SM // base))
-    ppw = max(1, n_pages // (4 * chunks_wanted))
-    return ppw, -(-n_pages // (4 * ppw))
+    ppw = max(1, n_pages // (2 * chunks_wanted))
+    return ppw, -(-n_pages // (2 * ppw))
 
 
 def attention_decode(q, out, k_cache, v_cache, block_table, seq_past, n_heads: int, n_kv_heads: int,
