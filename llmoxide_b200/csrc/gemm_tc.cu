@@ -30,7 +30,7 @@
 #define TC_THREADS 192
 #define TC_WAIT_CYCLES 4000000000ll   // about two seconds: far beyond any legitimate wait
 
-__device__ int g_tc_status = 0;   // 0, or 1 + the role whose bounded wait ran out
+__device__ int g_tc_status = 0;   // 0, or which bounded wait ran out: 1 producer, 2 MMA, 3 epilogue, 4 MMA on the accumulator
 
 // ---------------------------------------------------------------------------
 // PTX wrappers
@@ -110,7 +110,12 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, float* v) {
 }
 
 // ---------------------------------------------------------------------------
-// The kernel.  grid = (ceil(rows/128), ceil(T/BN), n_split).
+// The kernel: persistent CTAs over work units.  A unit is (tile of 128 rows
+// of W, tile of BN tokens, one split of K); unit u = ((split * row_tiles +
+// row_tile) * token_tiles + token_tile), so CTAs that run side by side share
+// a W tile through L2.  CTA c takes units c, c + gridDim.x, ...  The TMA ring
+// runs on across unit boundaries, and tensor memory holds two accumulator
+// sets, so the epilogue of a unit overlaps the MMAs of the next.
 // MODE 0: Y (bf16 or f32) [T, N] or split partials f32 [n_split][T, N].
 // MODE 1: two accumulators, rows n and n + F of W; act[T, F] = silu(g) * u.
 // ---------------------------------------------------------------------------
@@ -118,27 +123,25 @@ template <int BN, int MODE, typename TY>
 __global__ void __launch_bounds__(TC_THREADS)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
                TY* __restrict__ Y, int T, int N, int K, long long ldy, int k_blocks_per_split,
-               long long split_stride, int F, int n_stages) {
+               long long split_stride, int F, int n_stages, int row_tiles, int token_tiles, int n_units) {
   extern __shared__ uint8_t smem_raw[];
   constexpr int N_ACC = MODE == 1 ? 2 : 1;
   constexpr uint32_t A_BYTES = TC_BM * TC_BK * 2;
   constexpr uint32_t B_BYTES = BN * TC_BK * 2;
   constexpr uint32_t STAGE_BYTES = N_ACC * A_BYTES + B_BYTES;
-  constexpr uint32_t TMEM_COLS = (N_ACC * BN) < 32 ? 32 : (N_ACC * BN);
+  constexpr uint32_t ACC_COLS = N_ACC * BN;                                  // columns of one accumulator set
+  constexpr uint32_t TMEM_COLS = (2 * ACC_COLS) < 32 ? 32 : (2 * ACC_COLS);  // two sets; a power of two >= 32
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int n0 = blockIdx.x * TC_BM, t0 = blockIdx.y * BN;
   const int total_kb = (K + TC_BK - 1) / TC_BK;
-  const int kb_begin = blockIdx.z * k_blocks_per_split;
-  const int kb_end = min(total_kb, kb_begin + k_blocks_per_split);
-  const int n_kb = kb_end - kb_begin;
 
   // 1024-byte aligned stage buffers, then the barriers
   const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t* base_ptr = smem_raw + (base - smem_u32(smem_raw));
   uint64_t* bars = reinterpret_cast<uint64_t*>(base_ptr + (size_t)n_stages * STAGE_BYTES);
-  const uint32_t full0 = smem_u32(bars), empty0 = full0 + 8u * n_stages, acc_full = empty0 + 8u * n_stages;
-  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(bars + 2 * n_stages + 1);
+  const uint32_t full0 = smem_u32(bars), empty0 = full0 + 8u * n_stages;
+  const uint32_t acc_full0 = empty0 + 8u * n_stages, acc_empty0 = acc_full0 + 16u;
+  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(bars + 2 * n_stages + 4);
 
   pdl_launch_dependents();
   if (threadIdx.x == 0) {
@@ -146,7 +149,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
       mbar_init(full0 + 8u * s, 1);
       mbar_init(empty0 + 8u * s, 1);
     }
-    mbar_init(acc_full, 1);
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(acc_full0 + 8u * i, 1);
+      mbar_init(acc_empty0 + 8u * i, 4);      // one arrival per epilogue warp
+    }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("prefetch.tensormap [%0];" ::"l"(&map_w) : "memory");
     asm volatile("prefetch.tensormap [%0];" ::"l"(&map_x) : "memory");
@@ -162,98 +168,143 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
   tc_fence_after();
   const uint32_t tmem_base = *tmem_holder;
 
+  // unit -> coordinates
+  auto unit_coords = [&](int u, int& n0, int& t0, int& kb_begin, int& n_kb, int& split) {
+    const int tt = u % token_tiles;
+    const int rest = u / token_tiles;
+    const int rt = rest % row_tiles;
+    split = rest / row_tiles;
+    n0 = rt * TC_BM;
+    t0 = tt * BN;
+    kb_begin = split * k_blocks_per_split;
+    const int kb_end = min(total_kb, kb_begin + k_blocks_per_split);
+    n_kb = max(0, kb_end - kb_begin);
+  };
+
   if (warp == 0) {
     // ---------------- producer ----------------
     if (lane == 0) {
-      // The weights do not depend on the kernel before this one: the first stages' weight tiles are
-      // requested at once, and only the activation tiles wait for that kernel to finish.
-      const int pre = n_kb < n_stages ? n_kb : n_stages;
-      for (int i = 0; i < pre; ++i) {
-        const uint32_t stage = base + (uint32_t)i * STAGE_BYTES, bar = full0 + 8u * i;
-        mbar_expect_tx(bar, STAGE_BYTES);
-        const int k = (kb_begin + i) * TC_BK;
-        tma_load_2d(stage, &map_w, k, n0, bar);
-        if (MODE == 1) tma_load_2d(stage + A_BYTES, &map_w, k, n0 + F, bar);
-      }
-      pdl_wait();
-      for (int i = 0; i < pre; ++i)
-        tma_load_2d(base + (uint32_t)i * STAGE_BYTES + N_ACC * A_BYTES, &map_x, (kb_begin + i) * TC_BK, t0,
-                    full0 + 8u * i);
-      for (int i = pre; i < n_kb; ++i) {
-        const int s = i % n_stages;
-        const uint32_t parity = ((i / n_stages) & 1) ^ 1;
-        if (!mbar_wait(empty0 + 8u * s, parity)) { atomicExch(&g_tc_status, 1); break; }
-        const uint32_t stage = base + (uint32_t)s * STAGE_BYTES;
-        const uint32_t bar = full0 + 8u * s;
-        mbar_expect_tx(bar, STAGE_BYTES);
-        const int k = (kb_begin + i) * TC_BK;
-        tma_load_2d(stage, &map_w, k, n0, bar);
-        if (MODE == 1) tma_load_2d(stage + A_BYTES, &map_w, k, n0 + F, bar);
-        tma_load_2d(stage + N_ACC * A_BYTES, &map_x, k, t0, bar);
+      int it = 0;                 // k-blocks issued so far by this CTA (ring position)
+      bool waited = false, ok = true;
+      for (int u = blockIdx.x; u < n_units && ok; u += gridDim.x) {
+        int n0, t0, kb_begin, n_kb, split;
+        unit_coords(u, n0, t0, kb_begin, n_kb, split);
+        int i = 0;
+        if (!waited) {
+          // The weights do not depend on the kernel before this one: the first stages' weight tiles are
+          // requested at once, and only the activation tiles wait for that kernel to finish.
+          const int pre = n_kb < n_stages ? n_kb : n_stages;
+          for (int j = 0; j < pre; ++j) {
+            const uint32_t stage = base + (uint32_t)j * STAGE_BYTES, bar = full0 + 8u * j;
+            mbar_expect_tx(bar, STAGE_BYTES);
+            const int k = (kb_begin + j) * TC_BK;
+            tma_load_2d(stage, &map_w, k, n0, bar);
+            if (MODE == 1) tma_load_2d(stage + A_BYTES, &map_w, k, n0 + F, bar);
+          }
+          pdl_wait();
+          waited = true;
+          for (int j = 0; j < pre; ++j)
+            tma_load_2d(base + (uint32_t)j * STAGE_BYTES + N_ACC * A_BYTES, &map_x, (kb_begin + j) * TC_BK, t0,
+                        full0 + 8u * j);
+          i = pre;
+          it = pre;
+        }
+        for (; i < n_kb; ++i, ++it) {
+          const int s = it % n_stages;
+          const uint32_t parity = ((it / n_stages) & 1) ^ 1;
+          if (!mbar_wait(empty0 + 8u * s, parity)) { atomicExch(&g_tc_status, 1); ok = false; break; }
+          const uint32_t stage = base + (uint32_t)s * STAGE_BYTES;
+          const uint32_t bar = full0 + 8u * s;
+          mbar_expect_tx(bar, STAGE_BYTES);
+          const int k = (kb_begin + i) * TC_BK;
+          tma_load_2d(stage, &map_w, k, n0, bar);
+          if (MODE == 1) tma_load_2d(stage + A_BYTES, &map_w, k, n0 + F, bar);
+          tma_load_2d(stage + N_ACC * A_BYTES, &map_x, k, t0, bar);
+        }
       }
     }
   } else if (warp == 1) {
     // ---------------- MMA issuer ----------------
     if (lane == 0) {
       constexpr uint32_t idesc = umma_idesc(BN);
+      int it = 0, j = 0;          // ring position; units done by this CTA
       bool ok = true;
-      for (int i = 0; i < n_kb && ok; ++i) {
-        const int s = i % n_stages;
-        const uint32_t parity = (i / n_stages) & 1;
-        if (!mbar_wait(full0 + 8u * s, parity)) { atomicExch(&g_tc_status, 2); ok = false; break; }
+      for (int u = blockIdx.x; u < n_units && ok; u += gridDim.x, ++j) {
+        int n0, t0, kb_begin, n_kb, split;
+        unit_coords(u, n0, t0, kb_begin, n_kb, split);
+        const int buf = j & 1;
+        const uint32_t acc_addr = tmem_base + (uint32_t)buf * ACC_COLS;
+        // the epilogue must have drained this accumulator set (two units ago)
+        if (!mbar_wait(acc_empty0 + 8u * buf, ((j >> 1) & 1) ^ 1)) { atomicExch(&g_tc_status, 4); ok = false; break; }
         tc_fence_after();
-        const uint32_t stage = base + (uint32_t)s * STAGE_BYTES;
+        for (int i = 0; i < n_kb; ++i, ++it) {
+          const int s = it % n_stages;
+          const uint32_t parity = (it / n_stages) & 1;
+          if (!mbar_wait(full0 + 8u * s, parity)) { atomicExch(&g_tc_status, 2); ok = false; break; }
+          tc_fence_after();
+          const uint32_t stage = base + (uint32_t)s * STAGE_BYTES;
 #pragma unroll
-        for (int j = 0; j < TC_BK / TC_UMMA_K; ++j) {
-          const uint64_t db = umma_desc(stage + N_ACC * A_BYTES + j * (TC_UMMA_K * 2));
-          const uint32_t acc = (i > 0 || j > 0) ? 1u : 0u;
-          umma_bf16(tmem_base, umma_desc(stage + j * (TC_UMMA_K * 2)), db, idesc, acc);
-          if (MODE == 1) umma_bf16(tmem_base + BN, umma_desc(stage + A_BYTES + j * (TC_UMMA_K * 2)), db, idesc, acc);
+          for (int kk = 0; kk < TC_BK / TC_UMMA_K; ++kk) {
+            const uint64_t db = umma_desc(stage + N_ACC * A_BYTES + kk * (TC_UMMA_K * 2));
+            const uint32_t acc = (i > 0 || kk > 0) ? 1u : 0u;
+            umma_bf16(acc_addr, umma_desc(stage + kk * (TC_UMMA_K * 2)), db, idesc, acc);
+            if (MODE == 1) umma_bf16(acc_addr + BN, umma_desc(stage + A_BYTES + kk * (TC_UMMA_K * 2)), db, idesc, acc);
+          }
+          umma_commit(empty0 + 8u * s);   // the stage is free once these MMAs have read it
         }
-        umma_commit(empty0 + 8u * s);   // the stage is free once these MMAs have read it
+        umma_commit(acc_full0 + 8u * buf);  // this unit's accumulator is complete once every MMA has finished
       }
-      umma_commit(acc_full);            // the accumulator is complete once every MMA has finished
     }
   } else {
     // ---------------- epilogue ----------------
     const int quad = warp & 3;          // the quarter of tensor memory this warp may read
     const int row = quad * 32 + lane;   // row of the tile = lane of tensor memory
-    const int n = n0 + row;
     const int n_limit = MODE == 1 ? F : N;
-    bool ok = true;
-    if (n_kb == 0) pdl_wait();      // nothing to wait for below: order the stores after the kernel before
-    if (n_kb > 0) {
-      ok = mbar_wait(acc_full, 0);
+    bool waited = false;
+    int j = 0;
+    for (int u = blockIdx.x; u < n_units; u += gridDim.x, ++j) {
+      int n0, t0, kb_begin, n_kb, split;
+      unit_coords(u, n0, t0, kb_begin, n_kb, split);
+      const int n = n0 + row;
+      const int buf = j & 1;
+      bool ok = mbar_wait(acc_full0 + 8u * buf, (j >> 1) & 1);
       if (!ok && lane == 0) atomicExch(&g_tc_status, 3);
-    }
-    ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
-    tc_fence_after();
-    if (ok) {
-      TY* out = Y + (MODE == 0 ? (size_t)blockIdx.z * split_stride : 0);
+      ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+      if (!ok) break;
+      tc_fence_after();
+      if (n_kb == 0 && !waited) {       // no load ordered this unit after the kernel before: do it here
+        pdl_wait();
+        waited = true;
+      }
+      TY* out = Y + (MODE == 0 ? (size_t)split * split_stride : 0);
+      const uint32_t acc_addr = tmem_base + (uint32_t)buf * ACC_COLS + ((uint32_t)(quad * 32) << 16);
 #pragma unroll 1
       for (int c = 0; c < BN; c += 16) {
         if (t0 + c >= T) break;
-        float v[16], u[16];
-        const uint32_t taddr = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)c;
+        float v[16], g[16];
         if (n_kb > 0) {
-          tmem_ld16(taddr, v);
-          if (MODE == 1) tmem_ld16(taddr + BN, u);
+          tmem_ld16(acc_addr + (uint32_t)c, v);
+          if (MODE == 1) tmem_ld16(acc_addr + (uint32_t)(BN + c), g);
         } else {
 #pragma unroll
-          for (int j = 0; j < 16; ++j) v[j] = u[j] = 0.f;
+          for (int e = 0; e < 16; ++e) v[e] = g[e] = 0.f;
         }
         if (n < n_limit) {
 #pragma unroll
-          for (int j = 0; j < 16; ++j) {
-            const int t = t0 + c + j;
+          for (int e = 0; e < 16; ++e) {
+            const int t = t0 + c + e;
             if (t < T) {
-              float r = v[j];
-              if (MODE == 1) r = (r / (1.0f + __expf(-r))) * u[j];
+              float r = v[e];
+              if (MODE == 1) r = (r / (1.0f + __expf(-r))) * g[e];
               out[(size_t)t * ldy + n] = from_f32<TY>(r);
             }
           }
         }
       }
+      // hand the accumulator set back to the MMA warp
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(acc_empty0 + 8u * buf) : "memory");
     }
   }
   tc_fence_before();
@@ -299,6 +350,16 @@ static int make_map(CUtensorMap* map, const void* ptr, uint64_t rows, uint64_t K
   return r == CUDA_SUCCESS ? 0 : 2;
 }
 
+static int sm_count() {
+  static int n = 0;
+  if (!n) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
+  }
+  return n;
+}
+
 template <int BN, int MODE, typename TY>
 static int launch(const CUtensorMap& mw, const CUtensorMap& mx, void* Y, int T, int N, int K, long long ldy,
                   int n_split, long long split_stride, int F, cudaStream_t stream) {
@@ -306,13 +367,14 @@ static int launch(const CUtensorMap& mw, const CUtensorMap& mx, void* Y, int T, 
   constexpr size_t STAGE = (size_t)N_ACC * TC_BM * TC_BK * 2 + (size_t)BN * TC_BK * 2;
   const int total_kb = (K + TC_BK - 1) / TC_BK;
   const int per_split = (total_kb + n_split - 1) / n_split;
-  // Decode tiles (few tokens) stream weights: two CTAs per SM, so that one CTA's prologue and epilogue
-  // overlap the other's main loop.  Prompt tiles take the whole SM.
+  // Decode tiles (few tokens) stream weights: two CTAs per SM, so that more loads are in flight per SM.
+  // Prompt tiles take the whole SM.
+  const int ctas_per_sm = BN <= 64 ? 2 : 1;
   const size_t budget = BN <= 64 ? 100 * 1024 : 200 * 1024;
   int stages = (int)(budget / STAGE);
   if (stages > 12) stages = 12;
-  if (stages > per_split) stages = per_split < 2 ? 2 : per_split;
-  const size_t smem = 1024 + (size_t)stages * STAGE + (2 * stages + 1) * 8 + 16;
+  if (stages < 2) stages = 2;
+  const size_t smem = 1024 + (size_t)stages * STAGE + (2 * stages + 4) * 8 + 16;
   auto kernel = gemm_tc_kernel<BN, MODE, TY>;
   static bool attr_set = false;
   if (!attr_set) {
@@ -321,8 +383,13 @@ static int launch(const CUtensorMap& mw, const CUtensorMap& mx, void* Y, int T, 
     attr_set = true;
   }
   const int rows = MODE == 1 ? F : N;
-  dim3 grid((rows + TC_BM - 1) / TC_BM, (T + BN - 1) / BN, n_split);
-  launch_pdl(kernel, grid, dim3(TC_THREADS), smem, stream, mw, mx, (TY*)Y, T, N, K, ldy, per_split, split_stride, F, stages);
+  const int row_tiles = (rows + TC_BM - 1) / TC_BM, token_tiles = (T + BN - 1) / BN;
+  const long long n_units = (long long)row_tiles * token_tiles * n_split;
+  if (n_units > 0x7fffffff) return LLMX_REFUSED(3);
+  const int max_ctas = sm_count() * ctas_per_sm;
+  const int grid = n_units < max_ctas ? (int)n_units : max_ctas;
+  launch_pdl(kernel, dim3(grid), dim3(TC_THREADS), smem, stream, mw, mx, (TY*)Y, T, N, K, ldy, per_split,
+             split_stride, F, stages, row_tiles, token_tiles, (int)n_units);
   return LLMX_LAUNCH_STATUS();
 }
 

@@ -61,7 +61,11 @@ class Engine:
         n_slots = max(1, min(options.max_batch, (options.max_tokens + PAGE - 1) // PAGE))
         self.cache = Cache(self.model.cache_needs(), n_slots, options.max_tokens, self.rt.cache_dtype,
                            self.device, max_seq_len=max_seq)
-        self.buffers = StepBuffers(self.device)
+        # The step buffer is sized for the largest step up front (up to a bound), because growing it
+        # moves it, and a captured decode graph reads it at a fixed address.
+        width = (max_seq // PAGE + 8) * max(1, self.cache.n_groups())
+        want = 4 * min(options.max_step_tokens, options.max_tokens) + 4 * n_slots + min(n_slots, 256) * width + 64
+        self.buffers = StepBuffers(self.device, capacity=max(1 << 14, min(want, 1 << 22)))
         self.n_steps = 0
         self._sampler = None
         self._graphs: dict = {}

@@ -303,7 +303,9 @@ def test_sample_whole_vocabulary_follows_the_distribution():
 
 
 @pytest.mark.parametrize("T, N, K", [(1, 256, 64), (8, 384, 512), (64, 200, 1000), (130, 520, 320),
-                                     (300, 128, 4096), (5, 1000, 72)])
+                                     (300, 128, 4096), (5, 1000, 72),
+                                     # more work units than resident CTAs: a CTA walks several units
+                                     (8, 40000, 128), (600, 7680, 192), (300, 20480, 128), (40, 10240, 640)])
 def test_gemm_tc(T, N, K):
     """The tcgen05 kernel against float64, plain, split and gated."""
     from llmoxide_b200 import kernels
