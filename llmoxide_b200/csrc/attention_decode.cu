@@ -12,8 +12,8 @@
 // (the rows of one m16n8k16 tile; unused rows are zero), and a chunk of
 // 2 * pages_per_warp cache pages.  Each warp walks its pages in tiles of 32
 // keys: cp.async brings the tile's keys and values (contiguous in a page) to
-// the warp's own two-stage shared-memory ring, so the next tile is in flight
-// while this one is multiplied; scores and the weighted sum run on the tensor
+// the warp's own three-stage shared-memory ring, so the next two tiles are in
+// flight while this one is multiplied; scores and the weighted sum run on the tensor
 // cores.  Rows are padded by 16 bytes so that ldmatrix is free of bank
 // conflicts at every head size.  The two warps are merged through shared
 // memory and the CTA writes one unnormalised partial (acc, max, sum) per head
@@ -23,7 +23,7 @@
 #define DEC_WARPS 2
 #define DEC_ROWS 16                          // query heads per CTA = rows of the MMA tile
 #define DEC_TILE 32                          // keys per pipeline stage
-#define DEC_STAGES 2
+#define DEC_STAGES 3
 
 __device__ __forceinline__ void cp_async16(uint32_t dst, const void* src) {
   asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
@@ -68,8 +68,8 @@ template <int D>
 __global__ void __launch_bounds__(DEC_WARPS * 32)
 attention_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_cache, const bf16* __restrict__ v_cache,
                         const int* __restrict__ block_table, int table_width, const int* __restrict__ seq_past,
-                        float* __restrict__ ws, int H, int G, int window, float scale_log2, int pages_per_warp,
-                        int n_chunks) {
+                        float* __restrict__ ws, bf16* __restrict__ out, int H, int G, int window, float scale_log2,
+                        int pages_per_warp, int n_chunks) {
   using S = DecSmem<D>;
   constexpr int CHUNKS = D / 8;            // 16-byte chunks per row
   constexpr int KSTEPS = D / 16;
@@ -123,18 +123,18 @@ attention_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_c
       if (r < n_heads) cp_async16(sQ + r * S::ROW + c * 16, q + ((size_t)b * H + h0 + r) * D + c * 8);
       else *reinterpret_cast<uint4*>(wsm + r * S::ROW + c * 16) = make_uint4(0u, 0u, 0u, 0u);
     }
-    load_tile(tile_lo, 0);
-    cp_async_commit();
+    // ring of DEC_STAGES tiles: one commit group per tile slot (empty past the end), so that
+    // "all but the newest DEC_STAGES - 1 groups are done" always means "tile t has landed"
+    for (int i = 0; i < DEC_STAGES - 1; ++i) {
+      if (i < n_tiles) load_tile(tile_lo + i, i);
+      cp_async_commit();
+    }
 
     for (int t = 0; t < n_tiles; ++t) {
-      const int stage = t & 1;
-      if (t + 1 < n_tiles) {
-        load_tile(tile_lo + t + 1, stage ^ 1);
-        cp_async_commit();
-        cp_async_wait<1>();
-      } else {
-        cp_async_wait<0>();
-      }
+      const int stage = t % DEC_STAGES;
+      if (t + DEC_STAGES - 1 < n_tiles) load_tile(tile_lo + t + DEC_STAGES - 1, (t + DEC_STAGES - 1) % DEC_STAGES);
+      cp_async_commit();
+      cp_async_wait<DEC_STAGES - 1>();
       __syncwarp();
       const uint32_t sK = sKV + stage * 2 * S::TILE, sV = sK + S::TILE;
       const int key0 = (tile_lo + t) * DEC_TILE;
@@ -270,11 +270,15 @@ attention_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_c
       a += f * macc[((size_t)w * DEC_ROWS + h) * D + d];
       ls += f * mml[(w * DEC_ROWS + h) * 2 + 1];
     }
-    float* dst = ws + (((size_t)b * H + h0 + h) * n_chunks + chunk) * (D + 2);
-    dst[d] = a;
-    if (d == 0) {
-      dst[D] = mx;
-      dst[D + 1] = ls;
+    if (n_chunks == 1) {
+      out[((size_t)b * H + h0 + h) * D + d] = __float2bfloat16_rn(a / ls);   // nothing to merge with
+    } else {
+      float* dst = ws + (((size_t)b * H + h0 + h) * n_chunks + chunk) * (D + 2);
+      dst[d] = a;
+      if (d == 0) {
+        dst[D] = mx;
+        dst[D + 1] = ls;
+      }
     }
   }
 }
@@ -321,10 +325,10 @@ static int launch_decode(const void* q, void* out, const void* k_cache, const vo
     attr_set = true;
   }
   launch_pdl(kernel, grid, dim3(DEC_WARPS * 32), smem, stream, (const bf16*)q, (const bf16*)k_cache,
-             (const bf16*)v_cache, block_table, table_width, seq_past, ws, H, G, window,
+             (const bf16*)v_cache, block_table, table_width, seq_past, ws, (bf16*)out, H, G, window,
              scale * 1.4426950408889634f, pages_per_warp, n_chunks);
   int rc = LLMX_LAUNCH_STATUS();
-  if (rc) return rc;
+  if (rc || n_chunks == 1) return rc;
   launch_pdl(attention_decode_merge_kernel, dim3(B * H), dim3(D <= 64 ? 64 : 128), 0, stream, (const float*)ws,
              (bf16*)out, H, D, n_chunks);
   return LLMX_LAUNCH_STATUS();
@@ -338,7 +342,8 @@ LLMX_API int llmx_attention_decode(const void* q, void* out, const void* k_cache
                                    int H, int G, int D, int window, float scale, int pages_per_warp, int n_chunks,
                                    cudaStream_t stream) {
   if (B <= 0) return 0;
-  if (H <= 0 || G <= 0 || H % G || window < 0 || pages_per_warp < 1 || n_chunks < 1 || !ws) return LLMX_REFUSED(1);
+  if (H <= 0 || G <= 0 || H % G || window < 0 || pages_per_warp < 1 || n_chunks < 1 || (n_chunks > 1 && !ws))
+    return LLMX_REFUSED(1);
   if (B > 65535 || (long long)G * ((H / G + DEC_ROWS - 1) / DEC_ROWS) > 65535) return LLMX_REFUSED(3);
 #define CASE(DD)                                                                                               \
   case DD:                                                                                                     \

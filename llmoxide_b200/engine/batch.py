@@ -94,7 +94,7 @@ def build_host_arrays(entries, wants, lengths, page_rows, n_groups):
     for g in range(n_groups):
         width = max(1, max((f + PAGE - 1) // PAGE for f in final))
         # Round the width up so that a growing sequence changes the layout rarely.
-        width = _align(width, 8)
+        width = _align(width, 4)
         tab = np.full((n_seqs, width), -1, dtype=np.int32)
         for i in range(n_seqs):
             row = page_rows[g][i]

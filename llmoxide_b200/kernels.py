@@ -201,14 +201,21 @@ N_SM = 148
 
 def decode_split(n_seqs: int, n_kv_heads: int, group: int, n_pages: int) -> tuple:
     """(pages_per_warp, n_chunks) for the decode attention kernel, whose CTA
-    has two warps and so covers 2 * pages_per_warp pages: about two rounds of
-    the CTAs that fit the GPU at once, each warp walking whole pages.  It
-    depends on the batch's shape only (not on its lengths), so a captured
-    graph stays valid while the shape does."""
+    has two warps and so covers 2 * pages_per_warp pages.  Two CTAs fit an SM;
+    the choice minimises rounds of resident CTAs times the length of a warp's
+    walk (a page costs 1, starting and finishing a CTA about 1.5).  It depends
+    on the batch's shape only (not on its lengths), so a captured graph stays
+    valid while the shape does."""
     base = n_seqs * n_kv_heads * ((group + 15) // 16)
-    chunks_wanted = max(1, -(-4 * N_SM // base))
-    ppw = max(1, n_pages // (2 * chunks_wanted))
-    return ppw, -(-n_pages // (2 * ppw))
+    slots = 2 * N_SM
+    best = None
+    for ppw in range(1, max(1, -(-n_pages // 2)) + 1):
+        n_chunks = -(-n_pages // (2 * ppw))
+        rounds = -(-base * n_chunks // slots)
+        cost = rounds * (ppw + 1.5)
+        if best is None or cost < best[0]:
+            best = (cost, ppw, n_chunks)
+    return best[1], best[2]
 
 
 def attention_decode(q, out, k_cache, v_cache, block_table, seq_past, n_heads: int, n_kv_heads: int,
@@ -226,15 +233,17 @@ def attention_decode(q, out, k_cache, v_cache, block_table, seq_past, n_heads: i
     if window:
         n_pages = min(n_pages, (window + PAGE - 2) // PAGE + 1)
     ppw, n_chunks = decode_split(B, n_kv_heads, n_heads // n_kv_heads, n_pages)
-    ws = torch.empty(B * n_heads * n_chunks * (head_dim + 2), dtype=torch.float32, device=q.device)
+    ws = (torch.empty(B * n_heads * n_chunks * (head_dim + 2), dtype=torch.float32, device=q.device)
+          if n_chunks > 1 else None)
     f = _fn("attention_decode", "llmx_attention_decode",
             [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int,
              c_int, c_int, c_float, c_int, c_int, c_void_p])
     _check(f(_ptr(q), _ptr(out), _ptr(k_cache), _ptr(v_cache), _ptr(block_table), block_table.shape[1],
              _ptr(seq_past), _ptr(ws), B, n_heads, n_kv_heads, head_dim, int(window or 0), scale, ppw, n_chunks,
              _stream()), "attention_decode")
-    global launch_count
-    launch_count += 1   # the merge kernel
+    if n_chunks > 1:
+        global launch_count
+        launch_count += 1   # the merge kernel
 
 
 def attention_prefill_supports(q, k_cache, head_dim: int) -> bool:
