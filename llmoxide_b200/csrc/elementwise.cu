@@ -9,6 +9,23 @@
 // crates/model/src/qwen35/cpu.rs:295-323.
 #include "common.cuh"
 
+__device__ __forceinline__ float4 load4(const float* p) { return *reinterpret_cast<const float4*>(p); }
+__device__ __forceinline__ float4 load4(const bf16* p) {
+  const uint2 raw = *reinterpret_cast<const uint2*>(p);
+  const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.x));
+  const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.y));
+  return make_float4(a.x, a.y, b.x, b.y);
+}
+__device__ __forceinline__ void store4(float* p, float4 v) { *reinterpret_cast<float4*>(p) = v; }
+__device__ __forceinline__ void store4(bf16* p, float4 v) {
+  __nv_bfloat162 a = __floats2bfloat162_rn(v.x, v.y), b = __floats2bfloat162_rn(v.z, v.w);
+  uint2 raw;
+  raw.x = *reinterpret_cast<uint32_t*>(&a);
+  raw.y = *reinterpret_cast<uint32_t*>(&b);
+  *reinterpret_cast<uint2*>(p) = raw;
+}
+
+
 // ---------------------------------------------------------------------------
 // Embedding gather: h[t,:] = E[tok_t,:] widened to float32 (no scale).
 // ---------------------------------------------------------------------------
@@ -44,7 +61,7 @@ LLMX_API int llmx_embed(const void* table, int table_dtype, const int* tokens, f
 //   v = h[t,:] + sum_s delta[s][t,:]      (partials added in the order s = 0..S-1)
 //   if write_h: h[t,:] = v
 //   out[r,:] = v * (1/sqrt(mean(v^2)+eps)) * gain
-// One block per row; the row is staged in shared memory as float32.
+// One block per row; a row wider than one pass is staged in shared memory as float32.
 // ---------------------------------------------------------------------------
 // Threads per row are fixed by d alone (so the reduction order does not depend on the batch):
 // a thread takes 4 consecutive elements per pass, and rows up to 4096 wide finish in one pass.
@@ -62,21 +79,47 @@ __global__ void add_rms_norm_kernel(float* __restrict__ h, const TD* __restrict_
   float* hrow = h + (size_t)t * d;
   const int nthreads = blockDim.x;
   float ss = 0.f;
-  if ((d & 3) == 0) {
-    for (int i = threadIdx.x * 4; i < d; i += nthreads * 4) {
-      float4 v = *reinterpret_cast<const float4*>(hrow + i);
+  if ((d & 3) == 0 && d <= 4 * nthreads) {
+    // The row fits one pass: a thread keeps its four elements in registers from the sum to the store.
+    const int i = threadIdx.x * 4;
+    const bool live = i < d;
+    float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (live) {
+      v = load4(hrow + i);
       if (delta) {
         const TD* p = delta + (size_t)t * d + i;
         for (int s = 0; s < n_split; ++s) {
-          const TD* ps = p + s * split_stride;
-          v.x += to_f32(ps[0]);
-          v.y += to_f32(ps[1]);
-          v.z += to_f32(ps[2]);
-          v.w += to_f32(ps[3]);
+          const float4 y = load4(p + s * split_stride);
+          v.x += y.x; v.y += y.y; v.z += y.z; v.w += y.w;
         }
-        if (write_h) *reinterpret_cast<float4*>(hrow + i) = v;
+        if (write_h) store4(hrow + i, v);
       }
-      *reinterpret_cast<float4*>(row_buf + i) = v;
+      ss = v.x * v.x;
+      ss += v.y * v.y;
+      ss += v.z * v.z;
+      ss += v.w * v.w;
+    }
+    const float total = block_sum(ss, red);
+    const float scale = 1.0f / sqrtf(total / (float)d + eps);
+    if (out && live) {
+      const float4 g = load4(gain + i);
+      store4(out + (size_t)r * d + i,
+             make_float4((v.x * scale) * g.x, (v.y * scale) * g.y, (v.z * scale) * g.z, (v.w * scale) * g.w));
+    }
+    return;
+  }
+  if ((d & 3) == 0) {
+    for (int i = threadIdx.x * 4; i < d; i += nthreads * 4) {
+      float4 v = load4(hrow + i);
+      if (delta) {
+        const TD* p = delta + (size_t)t * d + i;
+        for (int s = 0; s < n_split; ++s) {
+          const float4 y = load4(p + s * split_stride);
+          v.x += y.x; v.y += y.y; v.z += y.z; v.w += y.w;
+        }
+        if (write_h) store4(hrow + i, v);
+      }
+      store4(row_buf + i, v);
       ss += v.x * v.x;
       ss += v.y * v.y;
       ss += v.z * v.z;
@@ -182,11 +225,47 @@ __global__ void qk_norm_rope_cache_kernel(const TIN* __restrict__ qkv, int n_spl
     const int page = block_table[(size_t)token_seq[t] * table_width + pos / LLMX_PAGE];
     cache_row = (is_k ? k_cache : v_cache) + cache_row_offset(page, g, pos % LLMX_PAGE, G, D);
   }
+  const float* gain = is_q ? q_gain : k_gain;
+  if (D == 128 && (n_rot == 128 || (!is_q && !is_k))) {
+    // Head size 128 with full rotation: a lane owns dims 4*lane..4*lane+3, read and written as one
+    // vector; the rotation partner (dim +-64) lives in lane +-16 and comes by shuffle.
+    const int d0 = 4 * lane;
+    float4 x = load4(src + d0);
+    for (int s = 1; s < n_split; ++s) {
+      const float4 y = load4(src + s * split_stride + d0);
+      x.x += y.x; x.y += y.y; x.z += y.z; x.w += y.w;
+    }
+    if (!is_q && !is_k) {  // v: stored as it is
+      store4(cache_row + d0, x);
+      return;
+    }
+    if (gain) {
+      const float ssq = warp_sum(x.x * x.x + x.y * x.y + x.z * x.z + x.w * x.w);
+      const float scale = 1.0f / sqrtf(ssq / 128.0f + eps);
+      const float4 gn = load4(gain + d0);
+      x.x = (x.x * scale) * gn.x; x.y = (x.y * scale) * gn.y; x.z = (x.z * scale) * gn.z; x.w = (x.w * scale) * gn.w;
+    }
+    float4 p;
+    p.x = __shfl_xor_sync(0xffffffffu, x.x, 16);
+    p.y = __shfl_xor_sync(0xffffffffu, x.y, 16);
+    p.z = __shfl_xor_sync(0xffffffffu, x.z, 16);
+    p.w = __shfl_xor_sync(0xffffffffu, x.w, 16);
+    const int ti = d0 & 63;
+    const float4 cs = load4(cos_t + (size_t)pos * 64 + ti), sn = load4(sin_t + (size_t)pos * 64 + ti);
+    float4 r;
+    if (lane < 16) {   // dims i < 64: x_i cos - x_{i+64} sin
+      r = make_float4(x.x * cs.x - p.x * sn.x, x.y * cs.y - p.y * sn.y, x.z * cs.z - p.z * sn.z, x.w * cs.w - p.w * sn.w);
+    } else {           // dims i + 64: x_i sin + x_{i+64} cos
+      r = make_float4(p.x * sn.x + x.x * cs.x, p.y * sn.y + x.y * cs.y, p.z * sn.z + x.z * cs.z, p.w * sn.w + x.w * cs.w);
+    }
+    if (is_q) store4(q_out + (size_t)t * H * D + (size_t)slot * D + d0, r);
+    else store4(cache_row + d0, r);
+    return;
+  }
   if (!is_q && !is_k) {  // v: stored as it is
     for (int i = lane; i < D; i += 32) cache_row[i] = from_f32<TC>(value(i));
     return;
   }
-  const float* gain = is_q ? q_gain : k_gain;
   float ss = 0.f;
   for (int i = lane; i < D; i += 32) {
     const float v = value(i);

@@ -152,13 +152,21 @@ def test_attention_window_edge_is_exact():
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-def test_qk_norm_rope_cache(dtype):
+@pytest.mark.parametrize("D, n_rot, n_split", [(80, 32, 1), (128, 128, 1), (128, 128, 3), (128, 64, 2), (16, 16, 1)])
+def test_qk_norm_rope_cache(dtype, D, n_rot, n_split):
     from llmoxide_b200 import kernels
-    H, G, D, n_rot = 3, 1, 80, 32
+    H, G = 3, 1
     lens, past = [5, 70], [60, 0]             # the first sequence crosses a page boundary
     T = sum(lens)
     torch.manual_seed(1)
-    qkv = torch.randn(T, (H + 2 * G) * D).to(dtype)
+    if n_split == 1:
+        qkv = torch.randn(T, (H + 2 * G) * D).to(dtype)
+        x = qkv.float()
+    else:                                     # float32 partials of a split reduction, summed in order
+        qkv = torch.randn(n_split, T, (H + 2 * G) * D)
+        x = qkv[0].clone()
+        for s_ in range(1, n_split):
+            x = x + qkv[s_]
     qg, kg = 1 + 0.1 * torch.randn(D), 1 + 0.1 * torch.randn(D)
     eps, base = 1e-5, 5000.0
     pos = torch.cat([torch.arange(p, p + L) for p, L in zip(past, lens)]).to(torch.int32)
@@ -170,7 +178,6 @@ def test_qk_norm_rope_cache(dtype):
     q_out = torch.empty(T, H * D, dtype=dtype, device=DEV)
     kernels.qk_norm_rope_cache(qkv.to(DEV), q_out, kc, vc, table.to(DEV), seq.to(DEV), pos.to(DEV),
                                qg.to(DEV), kg.to(DEV), eps, cos.to(DEV), sin.to(DEV), n_rot, H, G, D, True)
-    x = qkv.float()
     q = x[:, : H * D].view(T, H, D)
     k = x[:, H * D : (H + G) * D].view(T, G, D)
     v = x[:, (H + G) * D :].view(T, G, D)
