@@ -356,3 +356,39 @@ LLMX_API int llmx_attention_decode(const void* q, void* out, const void* k_cache
   }
 #undef CASE
 }
+
+// ---------------------------------------------------------------------------
+// The same kernels for callers that must not allocate: the workspace is a
+// file-scope device array.  See attention_decode_noalloc.h for who needs this
+// and for the rules (size limit, first call outside capture, shared array).
+// ---------------------------------------------------------------------------
+#include "attention_decode_noalloc.h"
+
+static __device__ __align__(256) float g_noalloc_workspace[LLMX_NOALLOC_WS_FLOATS];
+
+// In host code the array's name is only a handle for the runtime, not an address a kernel can use:
+// the device address is asked for once per device, with that device current, and kept.
+#define LLMX_NOALLOC_MAX_DEVICES 64
+static float* g_noalloc_ptr[LLMX_NOALLOC_MAX_DEVICES];
+
+LLMX_API int llmx_attention_decode_noalloc(const void* q, void* out, const void* k_cache, const void* v_cache,
+                                           const int* block_table, int table_width, const int* seq_past, int B,
+                                           int H, int G, int D, int window, float scale, int pages_per_warp,
+                                           int n_chunks, cudaStream_t stream) {
+  if (B <= 0) return 0;
+  if (H <= 0 || D <= 0 || n_chunks < 1) return LLMX_REFUSED(1);
+  const unsigned long long need = (unsigned long long)B * H * n_chunks * (unsigned long long)(D + 2);
+  if (need > LLMX_NOALLOC_WS_FLOATS) return LLMX_NOALLOC_TOO_LARGE;
+  int dev = -1;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return (int)e;
+  if (dev < 0 || dev >= LLMX_NOALLOC_MAX_DEVICES) return LLMX_REFUSED(3);
+  if (!g_noalloc_ptr[dev]) {
+    void* p = nullptr;
+    e = cudaGetSymbolAddress(&p, g_noalloc_workspace);
+    if (e != cudaSuccess) return (int)e;
+    g_noalloc_ptr[dev] = static_cast<float*>(p);
+  }
+  return llmx_attention_decode(q, out, k_cache, v_cache, block_table, table_width, seq_past, g_noalloc_ptr[dev], B,
+                               H, G, D, window, scale, pages_per_warp, n_chunks, stream);
+}

@@ -42,7 +42,7 @@ LIBRARIES = {
     "gemm_tc": (["gemm_tc.cu"], []),
     "sampling": (["sampling.cu"], []),
 }
-HEADERS = ["common.cuh"]
+HEADERS = ["common.cuh", "attention_decode_noalloc.h"]
 
 _loaded: dict = {}
 _lock = threading.Lock()
