@@ -130,7 +130,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
   constexpr uint32_t B_BYTES = BN * TC_BK * 2;
   constexpr uint32_t STAGE_BYTES = N_ACC * A_BYTES + B_BYTES;
   constexpr uint32_t ACC_COLS = N_ACC * BN;                                  // columns of one accumulator set
-  constexpr uint32_t TMEM_COLS = (2 * ACC_COLS) < 32 ? 32 : (2 * ACC_COLS);  // two sets; a power of two >= 32
+  constexpr int ACC_BUFS = (2 * ACC_COLS <= 512) ? 2 : 1;                    // two sets where tensor memory has room
+  constexpr uint32_t TMEM_COLS = (ACC_BUFS * ACC_COLS) < 32 ? 32 : (ACC_BUFS * ACC_COLS);   // a power of two >= 32
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int total_kb = (K + TC_BK - 1) / TC_BK;
@@ -232,10 +233,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
       for (int u = blockIdx.x; u < n_units && ok; u += gridDim.x, ++j) {
         int n0, t0, kb_begin, n_kb, split;
         unit_coords(u, n0, t0, kb_begin, n_kb, split);
-        const int buf = j & 1;
+        const int buf = j % ACC_BUFS, use = j / ACC_BUFS;
         const uint32_t acc_addr = tmem_base + (uint32_t)buf * ACC_COLS;
-        // the epilogue must have drained this accumulator set (two units ago)
-        if (!mbar_wait(acc_empty0 + 8u * buf, ((j >> 1) & 1) ^ 1)) { atomicExch(&g_tc_status, 4); ok = false; break; }
+        // the epilogue must have drained this accumulator set (ACC_BUFS units ago)
+        if (!mbar_wait(acc_empty0 + 8u * buf, (use & 1) ^ 1)) { atomicExch(&g_tc_status, 4); ok = false; break; }
         tc_fence_after();
         for (int i = 0; i < n_kb; ++i, ++it) {
           const int s = it % n_stages;
@@ -266,8 +267,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
       int n0, t0, kb_begin, n_kb, split;
       unit_coords(u, n0, t0, kb_begin, n_kb, split);
       const int n = n0 + row;
-      const int buf = j & 1;
-      bool ok = mbar_wait(acc_full0 + 8u * buf, (j >> 1) & 1);
+      const int buf = j % ACC_BUFS, use = j / ACC_BUFS;
+      bool ok = mbar_wait(acc_full0 + 8u * buf, use & 1);
       if (!ok && lane == 0) atomicExch(&g_tc_status, 3);
       ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
       if (!ok) break;
@@ -425,7 +426,8 @@ LLMX_API int llmx_gemm_tc(const void* X, const void* W, void* Y, int y_dtype, in
       case 16: GO(16, 1, bf16);
       case 32: GO(32, 1, bf16);
       case 64: GO(64, 1, bf16);
-      default: GO(128, 1, bf16);
+      case 128: GO(128, 1, bf16);
+      default: GO(256, 1, bf16);
     }
   }
 #undef BY_BN
