@@ -11,7 +11,7 @@ import pytest
 import torch
 
 import plain_qwen3 as plain
-from tiny_configs import ALL, TINY_A, TINY_B, TINY_C, make_folder, prompts
+from tiny_configs import ALL, TINY_A, TINY_B, TINY_C, TINY_D, make_folder, prompts
 
 from llmoxide_b200.config import Qwen3Config, read_config, register_architecture
 from llmoxide_b200.errors import (CheckpointFormatError, ConfigError, UnsupportedArch, WeightsError)
@@ -50,6 +50,7 @@ def test_window_layers():
     raw = dict(TINY_B, use_sliding_window=True, sliding_window=16, max_window_layers=1)
     assert read_config(raw).layer_windows() == [None, 16, 16]
     assert read_config(TINY_A).layer_windows() == [None, None]
+    assert read_config(TINY_D).layer_windows() == [None, 80]
 
 
 @pytest.mark.parametrize("change, needle", [

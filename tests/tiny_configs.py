@@ -29,7 +29,23 @@ TINY_C = dict(
     layer_types=["full_attention", "sliding_attention", "sliding_attention", "full_attention"],
     torch_dtype="float32", eos_token_id=3,
 )
-ALL = {"A": TINY_A, "B": TINY_B, "C": TINY_C}
+# The head sizes of the tiled tensor-core kernels (128 and 64), q width != hidden width,
+# one kv head for four heads, a window shorter than the sequences on one layer.
+TINY_D = dict(
+    architectures=["Qwen3ForCausalLM"], model_type="qwen3",
+    num_hidden_layers=2, hidden_size=192, num_attention_heads=4, num_key_value_heads=1, head_dim=128,
+    intermediate_size=320, vocab_size=509, rope_theta=1000000.0, rms_norm_eps=1e-6,
+    tie_word_embeddings=True, max_position_embeddings=1024, sliding_window=80, use_sliding_window=True,
+    max_window_layers=1, torch_dtype="float32", eos_token_id=[1, 2],
+)
+TINY_E = dict(
+    architectures=["Qwen3ForCausalLM"], model_type="qwen3",
+    num_hidden_layers=2, hidden_size=136, num_attention_heads=6, num_key_value_heads=3, head_dim=64,
+    intermediate_size=264, vocab_size=300, rope_theta=10000.0, rms_norm_eps=1e-5,
+    tie_word_embeddings=False, max_position_embeddings=1024, use_sliding_window=False,
+    torch_dtype="float32", eos_token_id=0,
+)
+ALL = {"A": TINY_A, "B": TINY_B, "C": TINY_C, "D": TINY_D, "E": TINY_E}
 
 
 def make_folder(tmp_path, name: str, dtype: str, seed: int = 1234) -> Path:
