@@ -330,31 +330,36 @@ LLMX_API int llmx_qk_norm_rope_cache(const void* qkv, int in_dtype, int n_split,
 // ---------------------------------------------------------------------------
 template <typename TI, typename TO>
 __global__ void silu_gate_kernel(const TI* __restrict__ gu, int n_split, size_t split_stride,
-                                 TO* __restrict__ act, int n_tokens, int F) {
+                                 TO* __restrict__ act, int n_tokens, int F, int block) {
   pdl_launch_dependents();
   pdl_wait();
   const size_t n = (size_t)n_tokens * F;
   for (size_t idx = blockIdx.x * (size_t)blockDim.x + threadIdx.x; idx < n; idx += (size_t)gridDim.x * blockDim.x) {
     const size_t t = idx / F, f = idx - t * F;
-    const TI* p = gu + t * 2 * (size_t)F + f;
+    // block == 0: columns [gate 0..F) [up 0..F).  block > 0: blocks of `block` gate columns followed by the
+    // `block` up columns of the same features.
+    const size_t gcol = block > 0 ? (f / block) * 2 * block + f % block : f;
+    const size_t ucol = block > 0 ? gcol + block : f + F;
+    const TI* p = gu + t * 2 * (size_t)F;
     float g = 0.f, u = 0.f;
     for (int s = 0; s < n_split; ++s) {
-      g += to_f32(p[s * split_stride]);
-      u += to_f32(p[s * split_stride + F]);
+      g += to_f32(p[s * split_stride + gcol]);
+      u += to_f32(p[s * split_stride + ucol]);
     }
     act[idx] = from_f32<TO>((g / (1.0f + expf(-g))) * u);
   }
 }
 
 LLMX_API int llmx_silu_gate(const void* gu, int in_dtype, int n_split, long long split_stride, void* act,
-                            int out_dtype, int n_tokens, int F, cudaStream_t stream) {
+                            int out_dtype, int n_tokens, int F, int block, cudaStream_t stream) {
   if (n_tokens <= 0) return 0;
-  if (F <= 0 || n_split < 1) return LLMX_REFUSED(1);
+  if (F <= 0 || n_split < 1 || block < 0 || (block > 0 && F % block)) return LLMX_REFUSED(1);
   const size_t n = (size_t)n_tokens * F;
   const int threads = 256;
   const int blocks = (int)((n + threads - 1) / threads < 148 * 16 ? (n + threads - 1) / threads : 148 * 16);
-#define CASE(TI, TO) \
-  launch_pdl(silu_gate_kernel<TI, TO>, dim3(blocks), dim3(threads), 0, stream, (const TI*)gu, n_split, (size_t)split_stride, (TO*)act, n_tokens, F)
+#define CASE(TI, TO)                                                                                        \
+  launch_pdl(silu_gate_kernel<TI, TO>, dim3(blocks), dim3(threads), 0, stream, (const TI*)gu, n_split,      \
+             (size_t)split_stride, (TO*)act, n_tokens, F, block)
   if (in_dtype == LLMX_F32 && out_dtype == LLMX_F32) CASE(float, float);
   else if (in_dtype == LLMX_F32 && out_dtype == LLMX_BF16) CASE(float, bf16);
   else if (in_dtype == LLMX_BF16 && out_dtype == LLMX_BF16) CASE(bf16, bf16);

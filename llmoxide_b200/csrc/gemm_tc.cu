@@ -29,6 +29,9 @@
 #define TC_UMMA_K 16
 #define TC_THREADS 192
 #define TC_WAIT_CYCLES 4000000000ll   // about two seconds: far beyond any legitimate wait
+// Prompt tiles: weight tiles this many k-blocks ahead of the load are prefetched into L2, so that the load
+// itself sees L2 latency, not DRAM latency (the shared-memory ring alone is too short to hide DRAM).
+#define TC_L2_AHEAD 12
 
 __device__ int g_tc_status = 0;   // 0, or which bounded wait ran out: 1 producer, 2 MMA, 3 epilogue, 4 MMA on the accumulator
 
@@ -68,6 +71,10 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map
       "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
       ::"r"(dst), "l"(map), "r"(x), "r"(y), "r"(bar)
       : "memory");
+}
+// Asks the TMA unit to bring a tile into L2 only (no shared memory, no barrier).
+__device__ __forceinline__ void tma_prefetch_l2_2d(const CUtensorMap* map, int x, int y) {
+  asm volatile("cp.async.bulk.prefetch.tensor.2d.L2.global [%0, {%1, %2}];" ::"l"(map), "r"(x), "r"(y) : "memory");
 }
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
@@ -110,6 +117,61 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, float* v) {
 }
 
 // ---------------------------------------------------------------------------
+// Epilogue of one accumulator tile: this warp's quarter (32 lanes = 32 rows of
+// W) of BN token columns, 16 columns at a time.
+// MODE 0: out[t, n] = acc.          MODE 1: two accumulators (gate, up): out[t, n] = silu(gate) * up.
+// MODE 2: W's rows come in blocks of 128 = 64 gate rows then the 64 up rows of the same features, so
+//         lanes 0..63 of the tile hold gate and lanes 64..127 hold up.  The two upper warps pass their
+//         values through shared memory (double-buffered, one named barrier per 16 columns) and the two
+//         lower warps write out[t, n0/2 + row] = silu(gate) * up.  All four warps run the same loop
+//         whatever happened before, so the barrier cannot be left waiting.
+// ---------------------------------------------------------------------------
+#define TC_XBUF_FLOATS (2 * 64 * 17)
+
+template <int BN, int MODE, typename TY>
+__device__ __forceinline__ void epilogue_tile(uint32_t acc_addr, bool have_acc, bool store, TY* __restrict__ out,
+                                              int n0, int t0, int T, int n_limit, long long ldy, int quad, int lane,
+                                              float* xbuf) {
+  const int row = quad * 32 + lane;
+  const int n = MODE == 2 ? (n0 >> 1) + (row & 63) : n0 + row;
+#pragma unroll 1
+  for (int c = 0; c < BN; c += 16) {
+    if (t0 + c >= T) break;
+    float v[16], g[16];
+    if (have_acc) {
+      tmem_ld16(acc_addr + (uint32_t)c, v);
+      if (MODE == 1) tmem_ld16(acc_addr + (uint32_t)(BN + c), g);
+    } else {
+#pragma unroll
+      for (int e = 0; e < 16; ++e) v[e] = g[e] = 0.f;
+    }
+    if (MODE == 2) {
+      float* xb = xbuf + ((c >> 4) & 1) * (64 * 17);
+      if (quad >= 2) {
+#pragma unroll
+        for (int e = 0; e < 16; ++e) xb[(row - 64) * 17 + e] = v[e];
+      }
+      asm volatile("bar.sync 1, 128;" ::: "memory");
+      if (quad < 2) {
+#pragma unroll
+        for (int e = 0; e < 16; ++e) g[e] = xb[row * 17 + e];
+      }
+    }
+    if (store && n < n_limit && (MODE != 2 || quad < 2)) {
+#pragma unroll
+      for (int e = 0; e < 16; ++e) {
+        const int t = t0 + c + e;
+        if (t < T) {
+          float r = v[e];
+          if (MODE != 0) r = __fdividef(r, 1.0f + __expf(-r)) * g[e];
+          out[(size_t)t * ldy + n] = from_f32<TY>(r);
+        }
+      }
+    }
+  }
+}
+
+// ---------------------------------------------------------------------------
 // The kernel: persistent CTAs over work units.  A unit is (tile of 128 rows
 // of W, tile of BN tokens, one split of K); unit u = ((split * row_tiles +
 // row_tile) * token_tiles + token_tile), so CTAs that run side by side share
@@ -125,7 +187,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
                TY* __restrict__ Y, int T, int N, int K, long long ldy, int k_blocks_per_split,
                long long split_stride, int F, int n_stages, int row_tiles, int token_tiles, int n_units) {
   extern __shared__ uint8_t smem_raw[];
-  constexpr int N_ACC = MODE == 1 ? 2 : 1;
+  constexpr int N_ACC = MODE == 1 ? 2 : 1;   // MODE 2 has one accumulator: gate and up rows share a tile
   constexpr uint32_t A_BYTES = TC_BM * TC_BK * 2;
   constexpr uint32_t B_BYTES = BN * TC_BK * 2;
   constexpr uint32_t STAGE_BYTES = N_ACC * A_BYTES + B_BYTES;
@@ -143,6 +205,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
   const uint32_t full0 = smem_u32(bars), empty0 = full0 + 8u * n_stages;
   const uint32_t acc_full0 = empty0 + 8u * n_stages, acc_empty0 = acc_full0 + 16u;
   uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(bars + 2 * n_stages + 4);
+  float* xbuf = reinterpret_cast<float*>(bars + 2 * n_stages + 6);   // MODE 2 only
 
   pdl_launch_dependents();
   if (threadIdx.x == 0) {
@@ -221,6 +284,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
           tma_load_2d(stage, &map_w, k, n0, bar);
           if (MODE == 1) tma_load_2d(stage + A_BYTES, &map_w, k, n0 + F, bar);
           tma_load_2d(stage + N_ACC * A_BYTES, &map_x, k, t0, bar);
+          if (BN > 64 && i + TC_L2_AHEAD < n_kb) {
+            tma_prefetch_l2_2d(&map_w, k + TC_L2_AHEAD * TC_BK, n0);
+            if (MODE == 1) tma_prefetch_l2_2d(&map_w, k + TC_L2_AHEAD * TC_BK, n0 + F);
+          }
         }
       }
     }
@@ -259,19 +326,19 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
   } else {
     // ---------------- epilogue ----------------
     const int quad = warp & 3;          // the quarter of tensor memory this warp may read
-    const int row = quad * 32 + lane;   // row of the tile = lane of tensor memory
-    const int n_limit = MODE == 1 ? F : N;
-    bool waited = false;
+    const int n_limit = MODE == 0 ? N : F;
+    bool waited = false, failed = false;
     int j = 0;
     for (int u = blockIdx.x; u < n_units; u += gridDim.x, ++j) {
       int n0, t0, kb_begin, n_kb, split;
       unit_coords(u, n0, t0, kb_begin, n_kb, split);
-      const int n = n0 + row;
       const int buf = j % ACC_BUFS, use = j / ACC_BUFS;
-      bool ok = mbar_wait(acc_full0 + 8u * buf, use & 1);
-      if (!ok && lane == 0) atomicExch(&g_tc_status, 3);
-      ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
-      if (!ok) break;
+      if (!failed) {
+        bool ok = mbar_wait(acc_full0 + 8u * buf, use & 1);
+        if (!ok && lane == 0) atomicExch(&g_tc_status, 3);
+        failed = __shfl_sync(0xffffffffu, ok ? 0 : 1, 0) != 0;
+      }
+      if (failed && MODE != 2) break;   // MODE 2 keeps walking (without loads or stores): its warps meet at a barrier
       tc_fence_after();
       if (n_kb == 0 && !waited) {       // no load ordered this unit after the kernel before: do it here
         pdl_wait();
@@ -279,29 +346,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
       }
       TY* out = Y + (MODE == 0 ? (size_t)split * split_stride : 0);
       const uint32_t acc_addr = tmem_base + (uint32_t)buf * ACC_COLS + ((uint32_t)(quad * 32) << 16);
-#pragma unroll 1
-      for (int c = 0; c < BN; c += 16) {
-        if (t0 + c >= T) break;
-        float v[16], g[16];
-        if (n_kb > 0) {
-          tmem_ld16(acc_addr + (uint32_t)c, v);
-          if (MODE == 1) tmem_ld16(acc_addr + (uint32_t)(BN + c), g);
-        } else {
-#pragma unroll
-          for (int e = 0; e < 16; ++e) v[e] = g[e] = 0.f;
-        }
-        if (n < n_limit) {
-#pragma unroll
-          for (int e = 0; e < 16; ++e) {
-            const int t = t0 + c + e;
-            if (t < T) {
-              float r = v[e];
-              if (MODE == 1) r = (r / (1.0f + __expf(-r))) * g[e];
-              out[(size_t)t * ldy + n] = from_f32<TY>(r);
-            }
-          }
-        }
-      }
+      epilogue_tile<BN, MODE, TY>(acc_addr, n_kb > 0 && !failed, !failed, out, n0, t0, T, n_limit, ldy, quad, lane, xbuf);
       // hand the accumulator set back to the MMA warp
       tc_fence_before();
       __syncwarp();
@@ -313,6 +358,252 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
   if (warp == 1) {
     tc_fence_after();
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
+  }
+}
+
+// ---------------------------------------------------------------------------
+// The same product on CTA pairs (tcgen05 cta_group::2) for prompt-sized token
+// tiles.  A cluster of two CTAs on neighbouring SMs owns 256 rows of W and a
+// tile of BN tokens: each CTA loads its own 128 rows of W and HALF of the
+// token tile, and the leader CTA issues one MMA of M = 256, N = BN that reads
+// both CTAs' shared memory and writes both CTAs' tensor memory.  Per SM that is
+// 32 KB of operands per 512 MMA cycles instead of 48 KB, which is what the
+// single-CTA kernel starves on.  Barriers: the leader's `full` barrier counts
+// one expect-tx arrival from each CTA's producer (TMA with cta_group::2 may
+// signal the peer's barrier); `empty` and `acc_full` are signalled in both
+// CTAs by one multicast tcgen05.commit; both CTAs' epilogue warps arrive on
+// the leader's `acc_empty`.  Every wait is bounded.
+// ---------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ uint32_t map_to_cta(uint32_t addr, uint32_t rank) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(addr), "r"(rank));
+  return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+  asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait_cluster(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n.reg .pred p;\n"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+      "selp.u32 %0, 1, 0, p;\n}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+__device__ __forceinline__ bool mbar_wait_cluster(uint32_t bar, uint32_t parity) {
+  if (mbar_try_wait_cluster(bar, parity)) return true;
+  const long long t0 = clock64();
+  while (!mbar_try_wait_cluster(bar, parity)) {
+    if (clock64() - t0 > TC_WAIT_CYCLES) return false;
+  }
+  return true;
+}
+__device__ __forceinline__ void mbar_remote_expect_tx(uint32_t cluster_addr, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cluster.b64 _, [%0], %1;" ::"r"(cluster_addr),
+               "r"(bytes)
+               : "memory");
+}
+__device__ __forceinline__ void mbar_remote_arrive(uint32_t cluster_addr) {
+  asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+__device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const CUtensorMap* map, int x, int y,
+                                                 uint32_t leader_bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes "
+      "[%0], [%1, {%2, %3}], [%4];"
+      ::"r"(dst), "l"(map), "r"(x), "r"(y), "r"(leader_bar)
+      : "memory");
+}
+__device__ __forceinline__ void umma_bf16_pair(uint32_t tmem_d, uint64_t a, uint64_t b, uint32_t idesc,
+                                               uint32_t accumulate) {
+  asm volatile(
+      "{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\n"
+      "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n}"
+      ::"r"(tmem_d), "l"(a), "l"(b), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+__device__ __forceinline__ void umma_commit_pair(uint32_t bar) {   // arrives on `bar` in both CTAs
+  asm volatile(
+      "tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
+      ::"r"(bar), "h"((uint16_t)3)
+      : "memory");
+}
+__host__ __device__ constexpr uint32_t umma_idesc_pair(int n) {   // M = 256 over the pair
+  return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(256 >> 4) << 24);
+}
+
+// Units: (pair of row tiles = 256 rows of W, tile of BN tokens); unit u -> token tile fastest.
+template <int BN, int MODE, typename TY>
+__global__ void __launch_bounds__(TC_THREADS)
+gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
+                    TY* __restrict__ Y, int T, int N, int K, long long ldy, int F, int n_stages, int row_pairs,
+                    int token_tiles, int n_units) {
+  extern __shared__ uint8_t smem_raw[];
+  constexpr int N_ACC = MODE == 1 ? 2 : 1;
+  constexpr int HALF = BN / 2;                                              // tokens this CTA loads
+  constexpr uint32_t A_BYTES = TC_BM * TC_BK * 2;
+  constexpr uint32_t B_BYTES = HALF * TC_BK * 2;
+  constexpr uint32_t STAGE_BYTES = N_ACC * A_BYTES + B_BYTES;                // per CTA
+  constexpr uint32_t ACC_COLS = N_ACC * BN;
+  constexpr int ACC_BUFS = (2 * ACC_COLS <= 512) ? 2 : 1;
+  constexpr uint32_t TMEM_COLS = ACC_BUFS * ACC_COLS;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t rank = cluster_ctarank();
+  const bool leader = rank == 0;
+  const int pair = blockIdx.x >> 1, n_pairs = gridDim.x >> 1;
+  const int total_kb = (K + TC_BK - 1) / TC_BK;
+
+  const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  uint8_t* base_ptr = smem_raw + (base - smem_u32(smem_raw));
+  uint64_t* bars = reinterpret_cast<uint64_t*>(base_ptr + (size_t)n_stages * STAGE_BYTES);
+  const uint32_t full0 = smem_u32(bars), empty0 = full0 + 8u * n_stages;
+  const uint32_t acc_full0 = empty0 + 8u * n_stages, acc_empty0 = acc_full0 + 16u;
+  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(bars + 2 * n_stages + 4);
+  float* xbuf = reinterpret_cast<float*>(bars + 2 * n_stages + 6);   // MODE 2 only
+  // the leader's copies of the barriers that both CTAs signal
+  const uint32_t leader_full0 = map_to_cta(full0, 0), leader_acc_empty0 = map_to_cta(acc_empty0, 0);
+
+  pdl_launch_dependents();
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < n_stages; ++s) {
+      mbar_init(full0 + 8u * s, 2);        // one expect-tx arrival per CTA (used in the leader only)
+      mbar_init(empty0 + 8u * s, 1);       // the multicast commit
+    }
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(acc_full0 + 8u * i, 1);    // the multicast commit
+      mbar_init(acc_empty0 + 8u * i, 8);   // four epilogue warps of each CTA (used in the leader only)
+    }
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("prefetch.tensormap [%0];" ::"l"(&map_w) : "memory");
+    asm volatile("prefetch.tensormap [%0];" ::"l"(&map_x) : "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_holder)),
+                 "r"(TMEM_COLS)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  cluster_sync_all();                      // barriers and tensor memory of both CTAs are ready
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_holder;
+
+  auto unit_coords = [&](int u, int& n0, int& t0) {
+    const int tt = u % token_tiles;
+    n0 = (u / token_tiles) * 2 * TC_BM + (int)rank * TC_BM;   // this CTA's 128 rows
+    t0 = tt * BN;
+  };
+
+  if (warp == 0) {
+    // ---------------- producer (one per CTA) ----------------
+    if (lane == 0) {
+      int it = 0;
+      bool waited = false, ok = true;
+      for (int u = pair; u < n_units && ok; u += n_pairs) {
+        int n0, t0;
+        unit_coords(u, n0, t0);
+        const int tx = t0 + (int)rank * HALF;                 // this CTA's half of the token tile
+        int i = 0;
+        if (!waited) {
+          const int pre = total_kb < n_stages ? total_kb : n_stages;
+          for (int j = 0; j < pre; ++j) {
+            const uint32_t stage = base + (uint32_t)j * STAGE_BYTES, bar = leader_full0 + 8u * j;
+            mbar_remote_expect_tx(bar, STAGE_BYTES);
+            tma_load_2d_pair(stage, &map_w, j * TC_BK, n0, bar);
+            if (MODE == 1) tma_load_2d_pair(stage + A_BYTES, &map_w, j * TC_BK, n0 + F, bar);
+          }
+          pdl_wait();
+          waited = true;
+          for (int j = 0; j < pre; ++j)
+            tma_load_2d_pair(base + (uint32_t)j * STAGE_BYTES + N_ACC * A_BYTES, &map_x, j * TC_BK, tx,
+                             leader_full0 + 8u * j);
+          i = pre;
+          it = pre;
+        }
+        for (; i < total_kb; ++i, ++it) {
+          const int s = it % n_stages;
+          const uint32_t parity = ((it / n_stages) & 1) ^ 1;
+          if (!mbar_wait_cluster(empty0 + 8u * s, parity)) { atomicExch(&g_tc_status, 11); ok = false; break; }
+          const uint32_t stage = base + (uint32_t)s * STAGE_BYTES, bar = leader_full0 + 8u * s;
+          mbar_remote_expect_tx(bar, STAGE_BYTES);
+          tma_load_2d_pair(stage, &map_w, i * TC_BK, n0, bar);
+          if (MODE == 1) tma_load_2d_pair(stage + A_BYTES, &map_w, i * TC_BK, n0 + F, bar);
+          tma_load_2d_pair(stage + N_ACC * A_BYTES, &map_x, i * TC_BK, tx, bar);
+          if (i + TC_L2_AHEAD < total_kb) {
+            tma_prefetch_l2_2d(&map_w, (i + TC_L2_AHEAD) * TC_BK, n0);
+            if (MODE == 1) tma_prefetch_l2_2d(&map_w, (i + TC_L2_AHEAD) * TC_BK, n0 + F);
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ---------------- MMA issuer (leader CTA only) ----------------
+    if (leader && lane == 0) {
+      constexpr uint32_t idesc = umma_idesc_pair(BN);
+      int it = 0, j = 0;
+      bool ok = true;
+      for (int u = pair; u < n_units && ok; u += n_pairs, ++j) {
+        const int buf = j % ACC_BUFS, use = j / ACC_BUFS;
+        const uint32_t acc_addr = tmem_base + (uint32_t)buf * ACC_COLS;
+        if (!mbar_wait_cluster(acc_empty0 + 8u * buf, (use & 1) ^ 1)) { atomicExch(&g_tc_status, 14); ok = false; break; }
+        tc_fence_after();
+        for (int i = 0; i < total_kb; ++i, ++it) {
+          const int s = it % n_stages;
+          if (!mbar_wait_cluster(full0 + 8u * s, (it / n_stages) & 1)) { atomicExch(&g_tc_status, 12); ok = false; break; }
+          tc_fence_after();
+          const uint32_t stage = base + (uint32_t)s * STAGE_BYTES;
+#pragma unroll
+          for (int kk = 0; kk < TC_BK / TC_UMMA_K; ++kk) {
+            const uint64_t db = umma_desc(stage + N_ACC * A_BYTES + kk * (TC_UMMA_K * 2));
+            const uint32_t acc = (i > 0 || kk > 0) ? 1u : 0u;
+            umma_bf16_pair(acc_addr, umma_desc(stage + kk * (TC_UMMA_K * 2)), db, idesc, acc);
+            if (MODE == 1)
+              umma_bf16_pair(acc_addr + BN, umma_desc(stage + A_BYTES + kk * (TC_UMMA_K * 2)), db, idesc, acc);
+          }
+          umma_commit_pair(empty0 + 8u * s);
+        }
+        umma_commit_pair(acc_full0 + 8u * buf);
+      }
+    }
+  } else {
+    // ---------------- epilogue (both CTAs) ----------------
+    const int quad = warp & 3;
+    const int n_limit = MODE == 0 ? N : F;
+    bool failed = false;
+    int j = 0;
+    for (int u = pair; u < n_units; u += n_pairs, ++j) {
+      int n0, t0;
+      unit_coords(u, n0, t0);
+      const int buf = j % ACC_BUFS, use = j / ACC_BUFS;
+      if (!failed) {
+        bool ok = mbar_wait_cluster(acc_full0 + 8u * buf, use & 1);
+        if (!ok && lane == 0) atomicExch(&g_tc_status, 13);
+        failed = __shfl_sync(0xffffffffu, ok ? 0 : 1, 0) != 0;
+      }
+      if (failed && MODE != 2) break;
+      tc_fence_after();
+      const uint32_t acc_addr = tmem_base + (uint32_t)buf * ACC_COLS + ((uint32_t)(quad * 32) << 16);
+      epilogue_tile<BN, MODE, TY>(acc_addr, !failed, !failed, Y, n0, t0, T, n_limit, ldy, quad, lane, xbuf);
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_remote_arrive(leader_acc_empty0 + 8u * buf);
+    }
+  }
+  tc_fence_before();
+  cluster_sync_all();                      // the peer may still read this CTA's shared and tensor memory until here
+  if (warp == 1) {
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
   }
 }
 
@@ -371,11 +662,11 @@ static int launch(const CUtensorMap& mw, const CUtensorMap& mx, void* Y, int T, 
   // Decode tiles (few tokens) stream weights: two CTAs per SM, so that more loads are in flight per SM.
   // Prompt tiles take the whole SM.
   const int ctas_per_sm = BN <= 64 ? 2 : 1;
-  const size_t budget = BN <= 64 ? 100 * 1024 : 200 * 1024;
+  const size_t budget = BN <= 64 ? 100 * 1024 : (MODE == 2 ? 192 * 1024 : 200 * 1024);
   int stages = (int)(budget / STAGE);
   if (stages > 12) stages = 12;
   if (stages < 2) stages = 2;
-  const size_t smem = 1024 + (size_t)stages * STAGE + (2 * stages + 4) * 8 + 16;
+  const size_t smem = 1024 + (size_t)stages * STAGE + (2 * stages + 6) * 8 + (MODE == 2 ? TC_XBUF_FLOATS * 4 : 0);
   auto kernel = gemm_tc_kernel<BN, MODE, TY>;
   static bool attr_set = false;
   if (!attr_set) {
@@ -383,7 +674,7 @@ static int launch(const CUtensorMap& mw, const CUtensorMap& mx, void* Y, int T, 
     if (e != cudaSuccess) return (int)e;
     attr_set = true;
   }
-  const int rows = MODE == 1 ? F : N;
+  const int rows = MODE == 1 ? F : N;   // MODE 2 walks all 2F interleaved rows
   const int row_tiles = (rows + TC_BM - 1) / TC_BM, token_tiles = (T + BN - 1) / BN;
   const long long n_units = (long long)row_tiles * token_tiles * n_split;
   if (n_units > 0x7fffffff) return LLMX_REFUSED(3);
@@ -397,14 +688,16 @@ static int launch(const CUtensorMap& mw, const CUtensorMap& mx, void* Y, int T, 
 // X [T,K] bf16 (row stride ldx), W [N,K] bf16 (row stride ldw).
 // mode 0: Y [T,N] of y_dtype, or with n_split > 1 float32 partials [n_split][T,N] (split_stride elements apart).
 // mode 1: W = [gate rows; up rows] with N = 2F; Y = act [T,F] of y_dtype.
+// mode 2: W = blocks of 128 rows, each 64 gate rows then the 64 up rows of the same features (N = 2F, F % 64 == 0);
+//         Y = act [T,F] bf16.
 LLMX_API int llmx_gemm_tc(const void* X, const void* W, void* Y, int y_dtype, int T, int N, int K, long long ldx,
                           long long ldw, long long ldy, int n_split, long long split_stride, int mode,
                           cudaStream_t stream) {
   if (T <= 0 || N <= 0) return 0;
   if (K <= 0 || (K % 8) || (ldx % 8) || (ldw % 8) || ((uintptr_t)X & 15) || ((uintptr_t)W & 15)) return LLMX_REFUSED(1);
   if (n_split < 1 || (n_split > 1 && (mode != 0 || y_dtype != LLMX_F32))) return LLMX_REFUSED(1);
-  if (mode == 1 && (N % 2)) return LLMX_REFUSED(1);
-  const int F = mode == 1 ? N / 2 : 0;
+  if (mode < 0 || mode > 2 || (mode == 1 && (N % 2)) || (mode == 2 && (N % 128))) return LLMX_REFUSED(1);
+  const int F = mode != 0 ? N / 2 : 0;
   int bn = 16;
   while (bn < T && bn < (mode == 1 ? 128 : 256)) bn <<= 1;
   CUtensorMap mw, mx;
@@ -430,8 +723,77 @@ LLMX_API int llmx_gemm_tc(const void* X, const void* W, void* Y, int y_dtype, in
       default: GO(256, 1, bf16);
     }
   }
+  if (mode == 2 && y_dtype == LLMX_BF16) { BY_BN(2, bf16) }
 #undef BY_BN
 #undef GO
+  return LLMX_REFUSED(2);
+}
+
+template <int BN, int MODE, typename TY>
+static int launch_pair(const CUtensorMap& mw, const CUtensorMap& mx, void* Y, int T, int N, int K, long long ldy,
+                       int F, cudaStream_t stream) {
+  constexpr int N_ACC = MODE == 1 ? 2 : 1;
+  constexpr size_t STAGE = (size_t)N_ACC * TC_BM * TC_BK * 2 + (size_t)(BN / 2) * TC_BK * 2;
+  int stages = (int)(((MODE == 2 ? 192 : 200) * 1024) / STAGE);
+  if (stages > 12) stages = 12;
+  const size_t smem = 1024 + (size_t)stages * STAGE + (2 * stages + 6) * 8 + (MODE == 2 ? TC_XBUF_FLOATS * 4 : 0);
+  auto kernel = gemm_tc_pair_kernel<BN, MODE, TY>;
+  static bool attr_set = false;
+  if (!attr_set) {
+    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+    if (e != cudaSuccess) return (int)e;
+    attr_set = true;
+  }
+  const int rows = MODE == 1 ? F : N;
+  const int row_pairs = (rows + 2 * TC_BM - 1) / (2 * TC_BM), token_tiles = (T + BN - 1) / BN;
+  const long long n_units = (long long)row_pairs * token_tiles;
+  if (n_units > 0x7fffffff) return LLMX_REFUSED(3);
+  cudaLaunchConfig_t cfg = {};
+  cfg.blockDim = dim3(TC_THREADS);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[2];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 2;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[1].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  // A persistent grid must fit the GPU at once: not every SM can be half of a pair (it depends on how
+  // the SMs are grouped), so the number of pairs that run together is asked for, once per kernel.
+  static int max_pairs = 0;
+  if (!max_pairs) {
+    cfg.gridDim = dim3(sm_count() / 2 * 2);
+    cfg.numAttrs = 1;
+    int n = 0;
+    if (cudaOccupancyMaxActiveClusters(&n, kernel, &cfg) != cudaSuccess || n <= 0) n = sm_count() / 2 - 4;
+    max_pairs = n;
+  }
+  const int pairs = n_units < max_pairs ? (int)n_units : max_pairs;
+  cfg.gridDim = dim3(2 * pairs);
+  cfg.numAttrs = 2;
+  cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, mw, mx, (TY*)Y, T, N, K, ldy, F, stages, row_pairs, token_tiles,
+                                     (int)n_units);
+  if (e != cudaSuccess) return (int)e;
+  return LLMX_LAUNCH_STATUS();
+}
+
+// The CTA-pair kernel: prompt-sized token counts only (T > 128), no split.  Same arguments as llmx_gemm_tc.
+LLMX_API int llmx_gemm_tc_pair(const void* X, const void* W, void* Y, int y_dtype, int T, int N, int K,
+                               long long ldx, long long ldw, long long ldy, int mode, cudaStream_t stream) {
+  if (T <= 0 || N <= 0) return 0;
+  if (K <= 0 || (K % 8) || (ldx % 8) || (ldw % 8) || ((uintptr_t)X & 15) || ((uintptr_t)W & 15)) return LLMX_REFUSED(1);
+  if (T <= 128 || mode < 0 || mode > 2 || (mode == 1 && (N % 2)) || (mode == 2 && (N % 128))) return LLMX_REFUSED(1);
+  const int F = mode != 0 ? N / 2 : 0;
+  const int bn = mode == 1 ? 128 : 256;
+  CUtensorMap mw, mx;
+  if (make_map(&mw, W, (uint64_t)N, (uint64_t)K, (uint64_t)ldw, TC_BM, true)) return LLMX_REFUSED(4);
+  if (make_map(&mx, X, (uint64_t)T, (uint64_t)K, (uint64_t)ldx, (uint32_t)(bn / 2), false)) return LLMX_REFUSED(4);
+  if (mode == 0 && y_dtype == LLMX_BF16) return launch_pair<256, 0, bf16>(mw, mx, Y, T, N, K, ldy, F, stream);
+  if (mode == 0 && y_dtype == LLMX_F32) return launch_pair<256, 0, float>(mw, mx, Y, T, N, K, ldy, F, stream);
+  if (mode == 1 && y_dtype == LLMX_BF16) return launch_pair<128, 1, bf16>(mw, mx, Y, T, N, K, ldy, F, stream);
+  if (mode == 2 && y_dtype == LLMX_BF16) return launch_pair<256, 2, bf16>(mw, mx, Y, T, N, K, ldy, F, stream);
   return LLMX_REFUSED(2);
 }
 

@@ -155,8 +155,10 @@ def qk_norm_rope_cache(qkv, q_out, k_cache, v_cache, block_table, token_seq, tok
              int(write_cache), _stream()), "qk_norm_rope_cache")
 
 
-def silu_gate(gu: torch.Tensor, out: torch.Tensor) -> None:
-    """gu [S,T,2F] or [T,2F] (gate columns, then up columns) -> out [T,F] = silu(gate) * up."""
+def silu_gate(gu: torch.Tensor, out: torch.Tensor, block: int = 0) -> None:
+    """gu [S,T,2F] or [T,2F] -> out [T,F] = silu(gate) * up.  ``block`` = 0:
+    gate columns, then up columns; ``block`` > 0: blocks of that many gate
+    columns each followed by the up columns of the same features."""
     _dev(gu, out)
     _contig("gu", gu), _contig("out", out)
     if gu.dim() == 2:
@@ -164,8 +166,8 @@ def silu_gate(gu: torch.Tensor, out: torch.Tensor) -> None:
     S, T, F2 = gu.shape
     assert out.shape == (T, F2 // 2)
     f = _fn("elementwise", "llmx_silu_gate",
-            [c_void_p, c_int, c_int, c_longlong, c_void_p, c_int, c_int, c_int, c_void_p])
-    _check(f(_ptr(gu), _tag(gu), S, gu.stride(0), _ptr(out), _tag(out), T, F2 // 2, _stream()), "silu_gate")
+            [c_void_p, c_int, c_int, c_longlong, c_void_p, c_int, c_int, c_int, c_int, c_void_p])
+    _check(f(_ptr(gu), _tag(gu), S, gu.stride(0), _ptr(out), _tag(out), T, F2 // 2, block, _stream()), "silu_gate")
 
 
 def sum_splits(parts: torch.Tensor, out: torch.Tensor) -> None:
@@ -289,10 +291,15 @@ def gemm_tc_supports(x: torch.Tensor, w: torch.Tensor) -> bool:
             and x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0)
 
 
-def gemm_tc(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, n_split: int = 1, gated: bool = False) -> None:
+def gemm_tc(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, n_split: int = 1, gated=False,
+            pair: bool = False) -> None:
     """bfloat16 x [T,K] times w [N,K]^T on tcgen05.  ``out`` is [T,N] (bfloat16
     or float32), or float32 partials [n_split,T,N] of a split reduction, or,
-    with ``gated`` (w = [gate rows; up rows]), [T,N/2] = silu(gate) * up."""
+    with ``gated``, [T,N/2] = silu(gate) * up: ``gated=True`` (or 1) for
+    w = [gate rows; up rows], ``gated=2`` for w in blocks of 64 gate rows each
+    followed by the 64 up rows of the same features (N/2 a multiple of 64).
+    ``pair`` runs the CTA-pair kernel (prompt-sized T > 128, no split)."""
+    gated = int(gated)
     _dev(x, w, out)
     T, K = x.shape
     N = w.shape[0]
@@ -306,11 +313,19 @@ def gemm_tc(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, n_split: int = 
     else:
         assert out.shape == (T, N)
         ldy, stride = N, 0
+    if pair:
+        assert n_split == 1 and T > 128
+        f = _fn("gemm_tc", "llmx_gemm_tc_pair",
+                [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_longlong, c_longlong, c_longlong, c_int,
+                 c_void_p])
+        _check(f(_ptr(x), _ptr(w), _ptr(out), _tag(out), T, N, K, x.stride(0), w.stride(0), ldy,
+                 gated, _stream()), "gemm_tc_pair")
+        return
     f = _fn("gemm_tc", "llmx_gemm_tc",
             [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_longlong, c_longlong, c_longlong, c_int,
              c_longlong, c_int, c_void_p])
     _check(f(_ptr(x), _ptr(w), _ptr(out), _tag(out), T, N, K, x.stride(0), w.stride(0), ldy, n_split, stride,
-             1 if gated else 0, _stream()), "gemm_tc")
+             gated, _stream()), "gemm_tc")
 
 
 def gemm_tc_status(reset: bool = True) -> int:

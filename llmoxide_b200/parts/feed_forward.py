@@ -22,17 +22,27 @@ class GatedMLP:
         wg, wu = weights.pop(t["gate"].name), weights.pop(t["up"].name)
         if wg.dtype != wu.dtype:
             wg, wu = wg.float(), wu.float()
-        self.gate_up = Linear(torch.cat([wg, wu], dim=0), rt)
+        # One matrix for gate and up.  Where the width allows, rows go in blocks of 64 gate rows each
+        # followed by the 64 up rows of the same features: a 128-row tile of the matrix product then holds
+        # both halves of 64 features, and the activation can be its epilogue.  Otherwise gate rows, then up rows.
+        self.block = 64 if self.F % 64 == 0 else 0
+        if self.block:
+            k = wg.shape[1]
+            fused = torch.stack([wg.view(-1, 64, k), wu.view(-1, 64, k)], dim=1).reshape(2 * self.F, k)
+        else:
+            fused = torch.cat([wg, wu], dim=0)
         del wg, wu
+        self.gate_up = Linear(fused, rt)
+        del fused
         self.down = Linear(weights.pop(t["down"].name), rt)
 
     def forward(self, x, ctx):
         tc = self.gate_up._tc
         if tc is not None and x.dtype == torch.bfloat16 and x.shape[0] > 64 and kernels.gemm_tc_supports(x, tc.weight):
             # prefill: the activation is the epilogue of the gate/up product
-            act = tc.gated(x, self.rt.act_dtype)
+            act = tc.gated(x, self.rt.act_dtype, self.block)
         else:
             gu = self.gate_up(x, splits_ok=True)
             act = torch.empty((x.shape[0], self.F), dtype=self.rt.act_dtype, device=x.device)
-            kernels.silu_gate(gu, act)
+            kernels.silu_gate(gu, act, self.block)
         return self.down(act, splits_ok=True)

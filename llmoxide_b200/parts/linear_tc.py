@@ -17,6 +17,7 @@ N_SM = 148
 TILE_ROWS = 128
 CTAS_PER_SM = 2               # what the kernel fits per SM at decode tile sizes
 MIN_KBLOCKS_PER_SPLIT = 4     # 64-element blocks of K per split, at least
+PAIR_MIN_TOKENS = 128         # above this, CTA pairs (tcgen05 cta_group::2) share each token tile
 
 
 def choose_splits(n_rows: int, k: int, n_tokens: int, max_splits: int = 16) -> int:
@@ -56,13 +57,14 @@ class TensorCoreLinear:
             kernels.gemm_tc(x, self.weight, out, n_split=s)
             return out
         out = torch.empty((T, self.N), dtype=out_dtype, device=x.device)
-        kernels.gemm_tc(x, self.weight, out)
+        kernels.gemm_tc(x, self.weight, out, pair=T > PAIR_MIN_TOKENS)
         return out
 
-    def gated(self, x, out_dtype):
-        """weight = [gate rows; up rows] -> silu(gate x) * (up x), [T, N/2]."""
+    def gated(self, x, out_dtype, block: int = 0):
+        """silu(gate x) * (up x), [T, N/2]; ``block`` = 0 for weight = [gate rows; up rows], 64 for
+        blocks of 64 gate rows each followed by the 64 up rows of the same features."""
         out = torch.empty((x.shape[0], self.N // 2), dtype=out_dtype, device=x.device)
-        kernels.gemm_tc(x, self.weight, out, gated=True)
+        kernels.gemm_tc(x, self.weight, out, gated=2 if block == 64 else 1, pair=x.shape[0] > PAIR_MIN_TOKENS)
         return out
 
 

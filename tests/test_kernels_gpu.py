@@ -225,6 +225,12 @@ def test_silu_gate_and_sum_splits(dtype):
     out = torch.empty(T, 2 * F, dtype=torch.float32, device=DEV)
     kernels.sum_splits(gu.to(DEV), out)
     assert rel(out, g) < 2e-6
+    # blocks of 10 gate columns followed by the 10 up columns of the same features
+    blocked = g.view(T, 2, F // 10, 10).permute(0, 2, 1, 3).reshape(T, 2 * F).to(dtype)
+    act2 = torch.empty(T, F, dtype=dtype, device=DEV)
+    kernels.silu_gate(blocked.to(DEV), act2, block=10)
+    gb = blocked.float().view(T, F // 10, 2, 10)
+    assert rel(act2, (plain.silu(gb[:, :, 0]) * gb[:, :, 1]).reshape(T, F)) < tol(dtype)
 
 
 def test_argmax_takes_the_last_of_equal_maxima():
@@ -339,6 +345,46 @@ def test_gemm_tc(T, N, K):
         kernels.gemm_tc(xd, wd, act, gated=True)
         gate, up = want[:, :F].float(), want[:, F:].float()
         assert rel(act, plain.silu(gate) * up) < 8e-3
+    if N % 128 == 0:      # rows in blocks of 64 gate rows + the 64 up rows of the same features
+        F = N // 2
+        blocks = want.float().view(T, N // 128, 2, 64)
+        act = torch.full((T, F), float("nan"), dtype=torch.bfloat16, device=DEV)
+        kernels.gemm_tc(xd, wd, act, gated=2)
+        assert rel(act, (plain.silu(blocks[:, :, 0]) * blocks[:, :, 1]).reshape(T, F)) < 8e-3
+    assert kernels.gemm_tc_status() == 0
+
+
+@pytest.mark.parametrize("T, N, K", [(129, 256, 64), (300, 520, 320), (2048, 1024, 512), (600, 20480, 192),
+                                     (1000, 200, 1000), (257, 4096 + 128, 4096)])
+def test_gemm_tc_pair(T, N, K):
+    """The CTA-pair (cta_group::2) kernel against float64, plain and gated."""
+    from llmoxide_b200 import kernels
+    g = torch.Generator().manual_seed(T + N)
+    x = torch.randn(T, K, generator=g).bfloat16()
+    w = (torch.randn(N, K, generator=g) / math.sqrt(K)).bfloat16()
+    x[:, K // 3] *= 30
+    x[T // 2] *= 5                         # one loud token: a swapped half of the token tile shows
+    want = x.double() @ w.double().t()
+    xd, wd = x.to(DEV), w.to(DEV)
+    out32 = torch.full((T, N), float("nan"), dtype=torch.float32, device=DEV)
+    kernels.gemm_tc(xd, wd, out32, pair=True)
+    assert kernels.gemm_tc_status() == 0
+    assert rel(out32, want) < 1e-5
+    out16 = torch.empty(T, N, dtype=torch.bfloat16, device=DEV)
+    kernels.gemm_tc(xd, wd, out16, pair=True)
+    assert rel(out16, want) < 6e-3
+    if N % 2 == 0:
+        F = N // 2
+        act = torch.full((T, F), float("nan"), dtype=torch.bfloat16, device=DEV)
+        kernels.gemm_tc(xd, wd, act, gated=True, pair=True)
+        gate, up = want[:, :F].float(), want[:, F:].float()
+        assert rel(act, plain.silu(gate) * up) < 8e-3
+    if N % 128 == 0:
+        F = N // 2
+        blocks = want.float().view(T, N // 128, 2, 64)
+        act = torch.full((T, F), float("nan"), dtype=torch.bfloat16, device=DEV)
+        kernels.gemm_tc(xd, wd, act, gated=2, pair=True)
+        assert rel(act, (plain.silu(blocks[:, :, 0]) * blocks[:, :, 1]).reshape(T, F)) < 8e-3
     assert kernels.gemm_tc_status() == 0
 
 
