@@ -116,8 +116,10 @@ class Engine:
         # A replayed graph writes its logits to the same memory every time.
         return logits.clone() if replayed else logits
 
-    def _step(self, entries, want=None):
+    def _step(self, entries, want=None, feed_tokens=None):
         lay, ctx = self._prepare(entries, want)
+        if feed_tokens is not None:
+            ctx.tokens.copy_(feed_tokens)      # on the stream, after the step buffer's copy
         replayed = bool(self.options.cuda_graphs and ctx.is_decode and self.model.graph_safe)
         if replayed:
             logits = self._graphed_forward(lay, ctx)
@@ -201,11 +203,24 @@ class Engine:
     def step_sample(self, entries, samplings, recents, uniforms) -> list:
         """One step, then one token per entry from the logits at its last
         token, chosen on the device.  Returns the token ids as a host list."""
+        return self.launch_step_sample(entries, samplings, recents, uniforms).tokens()
+
+    def launch_step_sample(self, entries, samplings, recents, uniforms, feed=None):
+        """The same without waiting: returns a handle whose ``tokens()`` waits
+        for the result.  With ``feed`` (the handle of the step before, over the
+        same sequences in the same order) every entry's single token is taken
+        on the device from that step's result, so this step can be launched
+        before the host has seen those tokens."""
         if self._sampler is None:
             from ..sampling.device import DeviceSampler
             self._sampler = DeviceSampler(self.device, self.spec.vocab_size)
-        logits, _ = self._step(entries)
-        return self._sampler.sample(logits, samplings, recents, uniforms)
+        if feed is None:
+            logits, _ = self._step(entries)
+        else:
+            if feed.n != len(entries) or any(len(t) != 1 for _, t in entries):
+                raise ValueError("a fed step takes one token per sequence of the step before")
+            logits, _ = self._step(entries, feed_tokens=feed.dev[: feed.n])
+        return self._sampler.launch(logits, samplings, recents, uniforms)
 
     # ---- facts -------------------------------------------------------------------
 

@@ -25,7 +25,7 @@ from dataclasses import dataclass, field
 from typing import Callable, Optional, Sequence
 
 from ..cache.allocator import PAGE
-from ..errors import ContextOverflow
+from ..errors import CacheExhausted, ContextOverflow
 from ..sampling.params import Rng, Sampling
 
 STOP, LENGTH, CANCELLED = "stop", "length", "cancelled"
@@ -105,6 +105,16 @@ def plan_batches(prompt_lens, new_lens, limits: Limits) -> list:
     return batches
 
 
+class _Done:
+    """A finished step in the shape of a handle (for backends that only step synchronously)."""
+
+    def __init__(self, tokens):
+        self._tokens = tokens
+
+    def tokens(self):
+        return self._tokens
+
+
 class _Live:
     __slots__ = ("index", "slot", "sampling", "rng", "stops", "max_new", "out", "next_token")
 
@@ -153,12 +163,7 @@ class GenerationLoop:
             self.timings.prefill_seconds += time.perf_counter() - t0
             self.timings.prefill_tokens += sum(len(requests[s.index].prompt) for s in live)
             t0 = time.perf_counter()
-            while True:
-                live = self._settle(live, requests, outcomes, on_token)
-                if not live:
-                    break
-                self._sample_step(live, [(s.slot, [s.next_token]) for s in live])
-                self.timings.decode_tokens += len(live)
+            live = self._decode(live, requests, outcomes, on_token)
             self.timings.decode_seconds += time.perf_counter() - t0
         finally:
             for s in live:
@@ -201,6 +206,64 @@ class GenerationLoop:
         self.timings.steps += 1
         for s, tok, f in zip(seqs, tokens, sampled):
             s.next_token = int(tok) if f else None
+
+    # ---- decoding, one step ahead ------------------------------------------
+
+    def _launch(self, seqs, feed=None):
+        """Starts a decode step for ``seqs`` (each brings its ``next_token``, or,
+        with ``feed``, the token the step before is still computing)."""
+        entries = [(s.slot, [0 if feed is not None else s.next_token]) for s in seqs]
+        uniforms = [0.0 if s.sampling.is_greedy() else s.rng.next_f32() for s in seqs]
+        args = (entries, [s.sampling for s in seqs], [s.out for s in seqs], uniforms)
+        self.timings.steps += 1
+        self.timings.decode_tokens += len(seqs)
+        if hasattr(self.backend, "launch_step_sample"):
+            return self.backend.launch_step_sample(*args, feed=feed)
+        return _Done(self.backend.step_sample(*args))
+
+    def _can_run_ahead(self, seqs) -> bool:
+        """A second step may be launched before the first one's tokens are known
+        when its inputs do not need them on the host: no repetition penalty
+        (which reads the tokens), and no sequence that the first step's token
+        ends by length.  A sequence that the first step ends by a stop token is
+        only known afterwards; its share of the second step is thrown away."""
+        if not hasattr(self.backend, "launch_step_sample"):
+            return False
+        return all(s.sampling.repeat_penalty == 1.0 and len(s.out) + 1 < s.max_new for s in seqs)
+
+    def _decode(self, live, requests, outcomes, on_token):
+        """The decode loop.  Every live sequence holds a ``next_token`` that is
+        not yet recorded.  Returns the sequences still live (none, normally)."""
+        live = self._settle(live, requests, outcomes, on_token)
+        if not live:
+            return live
+        step = self._launch(live)
+        while True:
+            ahead = None
+            if self._can_run_ahead(live):
+                try:
+                    ahead = self._launch(live, feed=step)
+                except (ContextOverflow, CacheExhausted):
+                    ahead = None                    # no room for a token that may not be needed: do not run ahead
+            for s, tok in zip(live, step.tokens()):
+                s.next_token = int(tok)
+            before = live
+            live = self._settle(before, requests, outcomes, on_token)
+            if not live:
+                return live
+            if ahead is not None and len(live) < len(before):
+                # Some sequence ended on the first step's token.  The second step already ran with it in
+                # the batch; the other sequences' tokens are right all the same (a sequence's result does
+                # not depend on its neighbours), so they are kept and the batch goes on without it.
+                place = {id(s): i for i, s in enumerate(before)}
+                toks = ahead.tokens()
+                for s in live:
+                    s.next_token = int(toks[place[id(s)]])
+                live = self._settle(live, requests, outcomes, on_token)
+                if not live:
+                    return live
+                ahead = None
+            step = ahead if ahead is not None else self._launch(live)
 
     def _settle(self, live, requests, outcomes, on_token):
         """Records each sequence's new token and decides who goes on."""

@@ -1,6 +1,8 @@
 """Runs the sampling kernels over a step's logits.  Per-row parameters travel
 in one small pinned buffer; a batch in which every row is greedy and
-unpenalised takes the argmax kernel alone."""
+unpenalised takes the argmax kernel alone.  A launch returns at once with a
+handle; the host reads the tokens when it needs them, so the next step can
+already be running (the generation loop launches one step ahead)."""
 
 from __future__ import annotations
 
@@ -11,64 +13,91 @@ from .. import kernels
 from ..errors import Unsupported
 
 MAX_TOP_K = 1024  # SMP_MAX_K in sampling.cu
+RING = 3          # launches whose results may be unread at the same time
+
+
+class SampledTokens:
+    """The tokens of one launch: on the device at once, on the host after
+    ``tokens()`` has waited for the copy."""
+
+    def __init__(self, dev, host, event, n):
+        self.dev, self._host, self._event, self.n = dev, host, event, n
+
+    def tokens(self) -> list:
+        self._event.synchronize()
+        return self._host[: self.n].tolist()
 
 
 class DeviceSampler:
     def __init__(self, device, vocab_size: int, max_rows: int = 64):
         self.device, self.vocab = device, vocab_size
         self._cap = 0
+        self._turn = 0
         self._grow(max_rows)
         self.status = torch.zeros(1, dtype=torch.int32, device=device)
 
     def _grow(self, rows: int, width: int = 64):
+        torch.cuda.current_stream().synchronize()      # nothing in flight may still use the old buffers
         self._cap, self._width = rows, width
         n = rows * (5 + width)
-        self._host = torch.empty(n, dtype=torch.int32).pin_memory()
-        self._dev = torch.empty(n, dtype=torch.int32, device=self.device)
-        self.tokens = torch.empty(rows, dtype=torch.int32, device=self.device)
-        self.tokens_host = torch.empty(rows, dtype=torch.int32).pin_memory()
+        self._params_host = [torch.empty(n, dtype=torch.int32).pin_memory() for _ in range(RING)]
+        self._params_dev = [torch.empty(n, dtype=torch.int32, device=self.device) for _ in range(RING)]
+        self._tokens_dev = [torch.empty(rows, dtype=torch.int32, device=self.device) for _ in range(RING)]
+        self._tokens_host = [torch.empty(rows, dtype=torch.int32).pin_memory() for _ in range(RING)]
+        self._events = [None] * RING
 
     def check(self, s) -> None:
         if s.is_greedy():
             return
-        if s.top_k < 0 or s.top_k > MAX_TOP_K and s.top_k < self.vocab:
+        if s.top_k < 0 or (MAX_TOP_K < s.top_k < self.vocab):
             raise Unsupported(f"top_k {s.top_k}: the sampling kernel sorts up to {MAX_TOP_K} candidates; "
                               f"use 0 for no limit")
         if (s.top_k == 0 or s.top_k >= self.vocab) and s.top_p < 1.0 and self.vocab > MAX_TOP_K:
             raise Unsupported("top_p < 1 needs top_k <= 1024 on this vocabulary")
 
-    def sample(self, logits: torch.Tensor, params: list, recents: list, uniforms: list) -> list:
+    def launch(self, logits: torch.Tensor, params: list, recents: list, uniforms: list) -> SampledTokens:
         """One token per row.  ``params[i]`` is row i's Sampling, ``recents[i]``
         its generated tokens so far, ``uniforms[i]`` its draw in [0, 1)."""
         n = logits.shape[0]
         assert n == len(params) == len(recents) == len(uniforms)
-        if all(p.is_greedy() and p.repeat_penalty == 1.0 for p in params):
-            if n > self._cap:
-                self._grow(max(n, 2 * self._cap), self._width)
-            kernels.argmax(logits, self.tokens[:n])
+        penalised = any(p.repeat_penalty != 1.0 for p in params)
+        width = max(1, max(min(p.repeat_window, len(r)) for p, r in zip(params, recents))) if penalised else 1
+        if n > self._cap or width > self._width:
+            self._grow(max(n, 2 * self._cap if n > self._cap else self._cap), max(width, self._width))
+        i = self._turn
+        self._turn = (i + 1) % RING
+        if self._events[i] is not None:
+            self._events[i].synchronize()              # the slot's last launch has been read back
+        out = self._tokens_dev[i]
+        if all(p.is_greedy() for p in params) and not penalised:
+            kernels.argmax(logits, out[:n])
         else:
-            width = max(1, max(min(p.repeat_window, len(r)) for p, r in zip(params, recents)))
-            if n > self._cap or width > self._width:
-                self._grow(max(n, self._cap), max(width, self._width))
+            for p in params:
+                self.check(p)
             W = self._width
-            host = self._host.numpy()
+            host = self._params_host[i].numpy()
             f = host.view(np.float32)
-            for i, (p, r, u) in enumerate(zip(params, recents, uniforms)):
-                f[i] = p.temperature
-                host[n + i] = p.top_k if p.top_k < self.vocab else 0
-                f[2 * n + i] = p.top_p
-                f[3 * n + i] = p.repeat_penalty
-                f[4 * n + i] = u
-                row = host[5 * n + i * W : 5 * n + (i + 1) * W]
+            for r, (p, rec, u) in enumerate(zip(params, recents, uniforms)):
+                f[r] = p.temperature
+                host[n + r] = p.top_k if p.top_k < self.vocab else 0
+                f[2 * n + r] = p.top_p
+                f[3 * n + r] = p.repeat_penalty
+                f[4 * n + r] = u
+                row = host[5 * n + r * W : 5 * n + (r + 1) * W]
                 row[:] = -1
-                tail = r[max(0, len(r) - p.repeat_window):] if p.repeat_penalty != 1.0 else []
+                tail = rec[max(0, len(rec) - p.repeat_window):] if p.repeat_penalty != 1.0 else []
                 row[: len(tail)] = tail
             total = n * (5 + W)
-            self._dev[:total].copy_(self._host[:total], non_blocking=True)
-            d = self._dev
+            d = self._params_dev[i]
+            d[:total].copy_(self._params_host[i][:total], non_blocking=True)
             fl = d.view(torch.float32)
             kernels.sample(logits, fl[0:n], d[n : 2 * n], fl[2 * n : 3 * n], fl[3 * n : 4 * n],
-                           d[5 * n : 5 * n + n * W].view(n, W), fl[4 * n : 5 * n], self.tokens[:n], self.status)
-        self.tokens_host[:n].copy_(self.tokens[:n], non_blocking=True)
-        torch.cuda.current_stream().synchronize()
-        return self.tokens_host[:n].tolist()
+                           d[5 * n : 5 * n + n * W].view(n, W), fl[4 * n : 5 * n], out[:n], self.status)
+        self._tokens_host[i][:n].copy_(out[:n], non_blocking=True)
+        ev = torch.cuda.Event()
+        ev.record()
+        self._events[i] = ev
+        return SampledTokens(out, self._tokens_host[i], ev, n)
+
+    def sample(self, logits, params, recents, uniforms) -> list:
+        return self.launch(logits, params, recents, uniforms).tokens()

@@ -241,3 +241,56 @@ def test_rng_matches_the_plain_implementation_and_is_per_sequence():
     r9, r10 = plain.Rng(9), plain.Rng(10)
     assert [d[0] for d in draws] == [r9.next_f32() for _ in range(3)]
     assert [d[1] for d in draws] == [r10.next_f32() for _ in range(3)]
+
+
+class AheadBackend(ScriptedBackend):
+    """A scripted backend that can be launched one step ahead: with ``feed`` a
+    sequence's token is the one the step before produced."""
+
+    class Handle:
+        def __init__(self, tokens):
+            self._tokens, self.n, self.read = tokens, len(tokens), False
+
+        def tokens(self):
+            self.read = True
+            return self._tokens
+
+    def __init__(self, scripts, n_slots):
+        super().__init__(scripts, n_slots)
+        self.fed_ahead = 0
+
+    def launch_step_sample(self, entries, samplings, recents, uniforms, feed=None):
+        if feed is not None:
+            assert not feed.read, "a step is launched ahead before the step before has been read"
+            entries = [(slot, [tok]) for (slot, _), tok in zip(entries, feed._tokens)]
+            recents = [list(r) + [tok] for r, tok in zip(recents, feed._tokens)]
+            self.fed_ahead += 1
+        return self.Handle(self.step_sample(entries, samplings, recents, uniforms))
+
+
+def test_running_one_step_ahead_changes_no_outcome():
+    scripts = {1: [5, 6, 99, 7, 7, 7], 2: [8] * 12, 3: [4, 4, 4, 4, 99, 1], 4: [99]}
+    reqs = [Request([1, 10], max_tokens=8), Request([2], max_tokens=9), Request([3, 30, 31], max_tokens=8),
+            Request([4], max_tokens=3)]
+    lim = Limits(max_batch=4, max_tokens=64 * 8, max_step_tokens=100, max_seq_len=128)
+    plain_be = ScriptedBackend(scripts, 4)
+    want = GenerationLoop(plain_be, lim, Sampling.greedy(), (99,)).run(reqs)
+    be = AheadBackend(scripts, 4)
+    got = GenerationLoop(be, lim, Sampling.greedy(), (99,)).run(reqs)
+    assert [(o.tokens, o.reason) for o in got] == [(o.tokens, o.reason) for o in want]
+    assert be.fed_ahead >= 4                       # steps really were launched ahead
+    assert sorted(be.free) == [0, 1, 2, 3] and len(be.released) == 4
+    # what each sequence was fed: its prompt, then its own tokens in order (a stop token may have been
+    # fed by a step that was already running when it was read; nothing after it)
+    for slot, fed in be.released:
+        script, n_prompt = scripts[fed[0]], {1: 2, 2: 1, 3: 3, 4: 1}[fed[0]]
+        assert fed[n_prompt:] == script[: len(fed) - n_prompt]
+        assert 99 not in fed[n_prompt:-1]
+    # with a repetition penalty the tokens are needed on the host first: nothing runs ahead
+    be2 = AheadBackend(scripts, 4)
+    GenerationLoop(be2, lim, Sampling(temperature=0.0, repeat_penalty=1.2), (99,)).run(reqs)
+    assert be2.fed_ahead == 0
+    # a sequence whose next token is its last by length is not run ahead
+    be3 = AheadBackend({2: [8] * 12}, 1)
+    out = GenerationLoop(be3, lim, Sampling.greedy(), (99,)).run([Request([2], max_tokens=2)])[0]
+    assert out.tokens == [8, 8] and be3.fed_ahead == 0
