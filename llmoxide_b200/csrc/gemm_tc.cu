@@ -15,6 +15,10 @@
 //               column = token), convert, store; or store float32 partials
 //               of a split reduction; or, with two accumulators (gate and up
 //               rows of the same features), silu(gate) * up
+// CTAs are persistent: each walks several (row tile, token tile, K split) units
+// with the TMA ring running on across units and two accumulator sets in tensor
+// memory, so a unit's epilogue overlaps the next unit's MMAs.  Prompt-sized token
+// tiles run on CTA pairs (cta_group::2, second kernel below).
 // Every wait on an mbarrier is bounded; when one runs out the CTA records it
 // in a status word, stops issuing work, frees its tensor memory and returns.
 //
@@ -29,9 +33,6 @@
 #define TC_UMMA_K 16
 #define TC_THREADS 192
 #define TC_WAIT_CYCLES 4000000000ll   // about two seconds: far beyond any legitimate wait
-// Prompt tiles: weight tiles this many k-blocks ahead of the load are prefetched into L2, so that the load
-// itself sees L2 latency, not DRAM latency (the shared-memory ring alone is too short to hide DRAM).
-#define TC_L2_AHEAD 12
 
 __device__ int g_tc_status = 0;   // 0, or which bounded wait ran out: 1 producer, 2 MMA, 3 epilogue, 4 MMA on the accumulator
 
@@ -71,10 +72,6 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map
       "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
       ::"r"(dst), "l"(map), "r"(x), "r"(y), "r"(bar)
       : "memory");
-}
-// Asks the TMA unit to bring a tile into L2 only (no shared memory, no barrier).
-__device__ __forceinline__ void tma_prefetch_l2_2d(const CUtensorMap* map, int x, int y) {
-  asm volatile("cp.async.bulk.prefetch.tensor.2d.L2.global [%0, {%1, %2}];" ::"l"(map), "r"(x), "r"(y) : "memory");
 }
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
@@ -284,10 +281,6 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
           tma_load_2d(stage, &map_w, k, n0, bar);
           if (MODE == 1) tma_load_2d(stage + A_BYTES, &map_w, k, n0 + F, bar);
           tma_load_2d(stage + N_ACC * A_BYTES, &map_x, k, t0, bar);
-          if (BN > 64 && i + TC_L2_AHEAD < n_kb) {
-            tma_prefetch_l2_2d(&map_w, k + TC_L2_AHEAD * TC_BK, n0);
-            if (MODE == 1) tma_prefetch_l2_2d(&map_w, k + TC_L2_AHEAD * TC_BK, n0 + F);
-          }
         }
       }
     }
@@ -539,10 +532,6 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
           tma_load_2d_pair(stage, &map_w, i * TC_BK, n0, bar);
           if (MODE == 1) tma_load_2d_pair(stage + A_BYTES, &map_w, i * TC_BK, n0 + F, bar);
           tma_load_2d_pair(stage + N_ACC * A_BYTES, &map_x, i * TC_BK, tx, bar);
-          if (i + TC_L2_AHEAD < total_kb) {
-            tma_prefetch_l2_2d(&map_w, (i + TC_L2_AHEAD) * TC_BK, n0);
-            if (MODE == 1) tma_prefetch_l2_2d(&map_w, (i + TC_L2_AHEAD) * TC_BK, n0 + F);
-          }
         }
       }
     }

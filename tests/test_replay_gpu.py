@@ -87,3 +87,24 @@ def test_steps_without_wanted_logits_write_no_file(folders, tmp_path):
     want = ru.expected_logits(folder, {"a": [1, 2, 3, 4]})["a"][3:]
     got = np.fromfile(tmp_path / "1.f32", dtype="<f4").reshape(1, -1)
     assert ru.rel_err(got, want) <= ru.TOL["float32"]
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_layer_sizes_of_qwen3_8b(tmp_path_factory, dtype):
+    """One layer at Qwen3-8B layer sizes: a prompt longer than the prompt kernels' tiles (so the
+    CTA-pair matrix product, the gated epilogue and the tiled attention run), decoding with split
+    reductions, and a batch of unequal lengths."""
+    folder = make_folder(tmp_path_factory.mktemp("m8b"), "8B", "bfloat16")      # bfloat16 weights in both runs
+    toks = prompts(1536, [200, 150, 37], seed=3)
+    reqs = {f"r{i}": t for i, t in enumerate(toks)}
+    want = ru.expected_logits(folder, reqs)
+    eng = _engine(folder, dtype, max_tokens=1024)
+    for what, steps in (("whole", ru.trace_whole(reqs)), ("last 32 one by one", ru.trace_tail_decode(reqs, 32)),
+                        ("unequal batch", ru.trace_batches(reqs, 3, 0.8))):
+        out = tmp_path_factory.mktemp("o")
+        ru.run_in_process(eng, steps, out)
+        got = ru.collect(steps, out, 1536)
+        ru.assert_matches(got, want, dtype, f"8B layer/{dtype}/{what}")
+        print(f"8B layer/{dtype}/{what}: worst rel err {max(ru.rel_err(got[r], want[r]) for r in reqs):.2e}")
+    from llmoxide_b200 import kernels
+    assert kernels.gemm_tc_status() == 0

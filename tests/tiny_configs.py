@@ -45,6 +45,16 @@ TINY_E = dict(
     tie_word_embeddings=False, max_position_embeddings=1024, use_sliding_window=False,
     torch_dtype="float32", eos_token_id=0,
 )
+# One layer at the layer sizes of Qwen3-8B (hidden 4096, 32 heads, 8 kv heads, head 128, feed-forward
+# 12288) with a small vocabulary: the shapes the large kernels are tuned for, at a size the plain
+# implementation still walks in seconds.
+LAYER_8B = dict(
+    architectures=["Qwen3ForCausalLM"], model_type="qwen3",
+    num_hidden_layers=1, hidden_size=4096, num_attention_heads=32, num_key_value_heads=8, head_dim=128,
+    intermediate_size=12288, vocab_size=1536, rope_theta=1000000.0, rms_norm_eps=1e-6,
+    tie_word_embeddings=False, max_position_embeddings=4096, use_sliding_window=False,
+    torch_dtype="bfloat16", eos_token_id=0,
+)
 ALL = {"A": TINY_A, "B": TINY_B, "C": TINY_C, "D": TINY_D, "E": TINY_E}
 
 
@@ -53,7 +63,7 @@ def make_folder(tmp_path, name: str, dtype: str, seed: int = 1234) -> Path:
     from llmoxide_b200.config import read_config
     from llmoxide_b200.weights import write_model_folder
 
-    cfg = dict(ALL[name])
+    cfg = dict(LAYER_8B if name == "8B" else ALL[name])
     cfg["torch_dtype"] = dtype
     folder = Path(tmp_path) / f"tiny_{name}_{dtype}"
     if not (folder / "model.safetensors").exists():
