@@ -29,8 +29,8 @@ __global__ void attention_paged_kernel(const TA* __restrict__ q, TA* __restrict_
   pdl_launch_dependents();
   pdl_wait();
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  const int t = blockIdx.y;
-  const int hq = blockIdx.x * ATT_WARPS + warp;
+  const int t = blockIdx.x;                        // tokens on x: a step may bring more than 65535
+  const int hq = blockIdx.y * ATT_WARPS + warp;
   if (hq >= H) return;
   const int g = hq / (H / G);
   const int p = token_pos[t];
@@ -92,7 +92,7 @@ LLMX_API int llmx_attention_paged(const void* q, void* out, int act_dtype, const
                                   int window, float scale, cudaStream_t stream) {
   if (n_tokens <= 0) return 0;
   if (H <= 0 || G <= 0 || H % G != 0 || D <= 0 || D > ATT_MAX_D || window < 0) return LLMX_REFUSED(1);
-  dim3 grid((H + ATT_WARPS - 1) / ATT_WARPS, n_tokens);
+  dim3 grid(n_tokens, (H + ATT_WARPS - 1) / ATT_WARPS);
   const size_t smem = (size_t)ATT_WARPS * D * sizeof(float);
 #define CASE(TA, TC)                                                                                      \
   launch_pdl(attention_paged_kernel<TA, TC>, grid, dim3(ATT_WARPS * 32), smem, stream,                    \

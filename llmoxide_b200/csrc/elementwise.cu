@@ -204,8 +204,8 @@ __global__ void qk_norm_rope_cache_kernel(const TIN* __restrict__ qkv, int n_spl
   pdl_launch_dependents();
   pdl_wait();
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  const int t = blockIdx.y;
-  const int slot = blockIdx.x * QKV_WARPS + warp;  // which head of the fused row
+  const int t = blockIdx.x;                        // tokens on x: a step may bring more than 65535
+  const int slot = blockIdx.y * QKV_WARPS + warp;  // which head of the fused row
   const int n_slots = write_cache ? H + 2 * G : H;
   if (slot >= n_slots) return;
   float* buf = head_buf + warp * D;
@@ -303,7 +303,7 @@ LLMX_API int llmx_qk_norm_rope_cache(const void* qkv, int in_dtype, int n_split,
   if (H <= 0 || G <= 0 || D <= 0 || n_rot < 0 || n_rot > D || (n_rot & 1) || n_split < 1) return LLMX_REFUSED(1);
   if (n_rot > 0 && (!cos_t || !sin_t)) return LLMX_REFUSED(4);
   const int n_slots = write_cache ? H + 2 * G : H;
-  dim3 grid((n_slots + QKV_WARPS - 1) / QKV_WARPS, n_tokens);
+  dim3 grid(n_tokens, (n_slots + QKV_WARPS - 1) / QKV_WARPS);
   const size_t smem = (size_t)QKV_WARPS * D * sizeof(float);
   if (smem > 48 * 1024) return LLMX_REFUSED(3);
 #define CASE(TIN, TA, TC)                                                                                          \

@@ -21,22 +21,28 @@ PAIR_MIN_TOKENS = 128         # above this, CTA pairs (tcgen05 cta_group::2) sha
 
 
 def choose_splits(n_rows: int, k: int, n_tokens: int, max_splits: int = 16) -> int:
-    """How many ways to split the reduction over K at ``n_tokens`` tokens.
-    The aim is whole rounds of N_SM * CTAS_PER_SM CTAs, bounded so that the
-    float32 partials (written once, read once) stay a few per cent of the
-    weight bytes."""
+    """How many ways to split the reduction over K at ``n_tokens`` tokens, from
+    a small time model of the streaming kernel (microseconds): CTAs run in
+    rounds of N_SM * CTAS_PER_SM; a CTA streams its share of the weights at
+    the HBM rate divided by the CTAs running, but never faster than one CTA
+    can pull; every round costs a fixed start and drain; float32 partials are
+    written once and read once by the kernel that consumes them."""
     if n_tokens > 64:
         return 1
     tiles = (n_rows + TILE_ROWS - 1) // TILE_ROWS
     k_blocks = (k + 63) // 64
     slots = N_SM * CTAS_PER_SM
-    cap = min(max_splits, max(1, k_blocks // MIN_KBLOCKS_PER_SPLIT), max(1, int(0.05 * k / n_tokens)))
-    best, best_cost = 1, None
-    for s in range(1, cap + 1):
-        rounds = -(-tiles * s // slots)
-        cost = rounds * (-(-k_blocks // s) + 6)       # k-blocks per CTA plus a fixed prologue/epilogue cost
-        if best_cost is None or cost < best_cost:
-            best, best_cost = s, cost
+    hbm, one_cta, fixed = 6.5e6, 2.5e4, 4.0          # bytes per microsecond; microseconds
+    best, best_t = 1, None
+    for s in range(1, min(max_splits, max(1, k_blocks // MIN_KBLOCKS_PER_SPLIT)) + 1):
+        ctas = tiles * s
+        rounds = -(-ctas // slots)
+        rate = min(hbm / min(ctas, slots), one_cta)
+        t = rounds * (TILE_ROWS * (k / s) * 2 / rate + fixed)
+        if s > 1:
+            t += 2.0 * s * n_tokens * n_rows * 4 / 5.0e6
+        if best_t is None or t < best_t - 1e-9:
+            best, best_t = s, t
     return best
 
 

@@ -108,3 +108,20 @@ def test_layer_sizes_of_qwen3_8b(tmp_path_factory, dtype):
         print(f"8B layer/{dtype}/{what}: worst rel err {max(ru.rel_err(got[r], want[r]) for r in reqs):.2e}")
     from llmoxide_b200 import kernels
     assert kernels.gemm_tc_status() == 0
+
+
+def test_a_step_of_more_than_65535_tokens(folders):
+    """Grid dimensions other than x end at 65535: a prompt step larger than that must still be right."""
+    import plain_qwen3 as plain
+    from llmoxide_b200.engine.engine import Engine, LoadOptions
+
+    for dtype in ("float32", "bfloat16"):
+        folder = folders[("E", dtype)]
+        toks = prompts(ALL["E"]["vocab_size"], [950] * 70, seed=9)           # 66 500 tokens in one step
+        eng = Engine.load(folder, LoadOptions(dtype=dtype, max_tokens=70 * 960, max_batch=70, max_step_tokens=70000))
+        slots = [eng.acquire() for _ in toks]
+        logits = eng.step(list(zip(slots, toks))).cpu().numpy()              # the last position of each
+        cfg, w = plain.read_model(folder)
+        for i in (0, 37, 69):
+            want = plain.forward(cfg, w, toks[i])[-1].numpy()
+            assert ru.rel_err(logits[i][None], want[None]) <= ru.TOL[dtype], (dtype, i)
