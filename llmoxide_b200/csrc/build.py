@@ -38,11 +38,12 @@ LIBRARIES = {
     "attention": (["attention.cu"], []),
     "attention_decode": (["attention_decode.cu"], []),
     "attention_prefill": (["attention_prefill.cu"], []),
+    "attention_prefill_tc": (["attention_prefill_tc.cu"], []),
     "gemm_fma": (["gemm_fma.cu"], []),
     "gemm_tc": (["gemm_tc.cu"], []),
     "sampling": (["sampling.cu"], []),
 }
-HEADERS = ["common.cuh", "attention_decode_noalloc.h"]
+HEADERS = ["common.cuh", "attention_decode_noalloc.h", "tc_ptx.cuh"]
 
 _loaded: dict = {}
 _lock = threading.Lock()
@@ -64,7 +65,8 @@ def find_nvcc() -> str:
 
 
 def _flags() -> list:
-    return list(NVCC_FLAGS)
+    # LLMX_NVCC_EXTRA: extra nvcc flags (for experiments with -D switches); part of the library's hash
+    return list(NVCC_FLAGS) + os.environ.get("LLMX_NVCC_EXTRA", "").split()
 
 
 def _digest(name: str) -> str:
@@ -157,6 +159,10 @@ def compile_library(name: str, verbose=True) -> Path:
             return target
         finally:
             fcntl.flock(lock_file, fcntl.LOCK_UN)
+            try:
+                lock_path.unlink()
+            except OSError:
+                pass
 
 
 def load_library(name: str) -> ctypes.CDLL:

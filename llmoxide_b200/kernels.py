@@ -268,6 +268,29 @@ def attention_prefill(q, out, k_cache, v_cache, block_table, seq_start, seq_past
              scale, _stream()), "attention_prefill")
 
 
+def attention_prefill_tc(q, out, k_cache, v_cache, block_table, seq_start, seq_past, n_seqs: int, max_new: int,
+                         n_heads: int, n_kv_heads: int, head_dim: int, window, scale: float) -> None:
+    """Prompt attention on tcgen05, bfloat16, head size 128: q, out [T,H*128]
+    packed sequence after sequence; the cache entry is [n_pages,G,64,128]."""
+    _dev(q, out, k_cache, v_cache, block_table, seq_start, seq_past)
+    _contig("q", q), _contig("out", out), _contig("block_table", block_table)
+    assert k_cache.is_contiguous() and v_cache.is_contiguous()
+    if head_dim != 128 or q.dtype != torch.bfloat16 or k_cache.dtype != torch.bfloat16:
+        raise Unsupported("the tcgen05 prompt attention takes bfloat16 and head size 128")
+    f = _fn("attention_prefill_tc", "llmx_attention_prefill_tc",
+            [c_void_p, c_void_p, c_void_p, c_void_p, c_longlong, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int,
+             c_int, c_int, c_int, c_int, c_int, c_float, c_void_p])
+    _check(f(_ptr(q), _ptr(out), _ptr(k_cache), _ptr(v_cache), k_cache.shape[0], _ptr(block_table),
+             block_table.shape[1], _ptr(seq_start), _ptr(seq_past), n_seqs, q.shape[0], max_new, n_heads,
+             n_kv_heads, head_dim, int(window or 0), scale, _stream()), "attention_prefill_tc")
+
+
+def attention_prefill_tc_status(reset: bool = True) -> int:
+    """0, or which bounded wait of the tcgen05 prompt attention ran out.  Synchronises the device."""
+    f = _fn("attention_prefill_tc", "llmx_attention_prefill_tc_status", [c_int])
+    return f(int(reset))
+
+
 def gemm_fma(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> None:
     """out[M,N] = x[M,K] @ w[N,K]^T on the FMA units, float32 accumulation in
     the order k = 0..K-1.  Rows may be strided; the K axis must be dense."""

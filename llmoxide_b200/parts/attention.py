@@ -73,14 +73,18 @@ class GQAttention:
         return self.o(out, splits_ok=True)
 
     def attend(self, q, out, view, block_table, ctx):
-        """bfloat16: the split-key kernel when every sequence brings one token,
-        the tiled tensor-core kernel for prompts at head sizes it takes; the
-        general kernel otherwise and always in float32."""
+        """bfloat16: the split-key kernel when every sequence brings one token;
+        for prompts the tcgen05 kernel at head size 128 and the mma.sync tiled
+        kernel at head size 64; the general kernel otherwise and always in
+        float32."""
         H, G, D = self.H, self.G, self.D
         fast = q.dtype == torch.bfloat16 and view.k.dtype == torch.bfloat16 and self.rt.tensor_cores
         if fast and ctx.is_decode:
             kernels.attention_decode(q, out, view.k, view.v, block_table, ctx.seq_past, H, G, D, self.window,
                                      self.scale)
+        elif fast and D == 128:
+            kernels.attention_prefill_tc(q, out, view.k, view.v, block_table, ctx.seq_start, ctx.seq_past,
+                                         ctx.n_seqs, ctx.max_new, H, G, D, self.window, self.scale)
         elif fast and kernels.attention_prefill_supports(q, view.k, D):
             kernels.attention_prefill(q, out, view.k, view.v, block_table, ctx.seq_start, ctx.seq_past,
                                       ctx.n_seqs, ctx.max_new, H, G, D, self.window, self.scale)

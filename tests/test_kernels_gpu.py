@@ -436,6 +436,23 @@ def test_attention_prefill_tiled(H, G, D, window):
         assert rel(out[lo:hi], want[lo:hi]) < 1.2e-2, (i, lens[i], pasts[i])
 
 
+@pytest.mark.parametrize("H, G", [(8, 2), (5, 1), (3, 3)])
+@pytest.mark.parametrize("window", [None, 100, 300])
+def test_attention_prefill_tcgen05(H, G, window):
+    from llmoxide_b200 import kernels
+    D = 128
+    lens, pasts = [1, 64, 200, 65, 130, 700], [0, 0, 0, 70, 300, 0]   # whole prompts and later chunks of prompts
+    q, kc, vc, table, starts, past, want = _attention_case(H, G, D, lens, pasts, window)
+    out = torch.full_like(q, float("nan"), device=DEV)
+    kernels.attention_prefill_tc(q.to(DEV), out, kc.to(DEV), vc.to(DEV), table.to(DEV), starts.to(DEV), past.to(DEV),
+                                 len(lens), max(lens), H, G, D, window, 1 / math.sqrt(D))
+    assert kernels.attention_prefill_tc_status() == 0
+    assert not out.isnan().any()
+    for i in range(len(lens)):
+        lo, hi = starts[i], starts[i + 1]
+        assert rel(out[lo:hi], want[lo:hi]) < 1.2e-2, (i, lens[i], pasts[i])
+
+
 @pytest.mark.parametrize("H, G, D", [(8, 2, 128), (6, 6, 64), (5, 1, 48), (16, 2, 80), (4, 4, 256)])
 @pytest.mark.parametrize("window", [None, 100])
 def test_attention_decode_split(H, G, D, window):
