@@ -49,6 +49,7 @@ class Qwen3Config:
     bos_token_id: Optional[int] = None
     architectures: tuple = ("Qwen3ForCausalLM",)
     extra: dict = field(default_factory=dict)  # keys carried through untouched
+    generation: dict = field(default_factory=dict)  # sampling settings of generation_config.json, if the folder has one
 
     # ---- reading -----------------------------------------------------------
 
@@ -201,6 +202,16 @@ class Qwen3Config:
             f", {self.n_params() / 1e6:.1f} M params, {self.torch_dtype}"
         )
 
+    def _default_sampling(self) -> dict:
+        out = dict(temperature=0.7, top_k=20, top_p=0.8)
+        g = self.generation or {}
+        for key in ("temperature", "top_k", "top_p"):
+            if g.get(key) is not None:
+                out[key] = g[key]
+        if g.get("repetition_penalty") is not None:
+            out["repeat_penalty"] = g["repetition_penalty"]
+        return out
+
     # ---- description as parts ------------------------------------------------
 
     def to_spec(self) -> ModelSpec:
@@ -246,7 +257,7 @@ class Qwen3Config:
             max_positions=self.max_position_embeddings,
             stop_ids=tuple(self.eos_token_id),
             storage_dtype=self.torch_dtype,
-            # What the model's authors recommend; the reference falls back to
-            # these for qwen3 (crates/model/src/sample.rs:43-53).
-            default_sampling=dict(temperature=0.7, top_k=20, top_p=0.8),
+            # The folder's own generation_config.json where it has one; else what the model's authors
+            # recommend, which the reference falls back to for qwen3 (crates/model/src/sample.rs:43-53).
+            default_sampling=self._default_sampling(),
         )

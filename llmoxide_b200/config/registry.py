@@ -50,4 +50,15 @@ def read_config(source):
             raw = json.loads(path.read_text())
         except json.JSONDecodeError as e:
             raise ConfigError(f"{path} is not valid JSON: {e}") from None
-    return config_class(architecture_name(raw)).from_dict(raw)
+    cfg = config_class(architecture_name(raw)).from_dict(raw)
+    # A model folder may carry its authors' sampling settings beside the configuration.
+    if not isinstance(source, dict):
+        gen = Path(source)
+        gen = (gen if gen.is_dir() else gen.parent) / "generation_config.json"
+        if gen.is_file() and hasattr(cfg, "generation"):
+            try:
+                cfg.generation = {k: v for k, v in json.loads(gen.read_text()).items()
+                                  if k in ("temperature", "top_k", "top_p", "repetition_penalty")}
+            except (json.JSONDecodeError, OSError):
+                pass
+    return cfg

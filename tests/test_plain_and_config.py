@@ -45,6 +45,14 @@ def test_config_defaults_and_round_trip():
     assert read_config(TINY_B).eos_token_id == (11, 12)
 
 
+def test_generation_config_sets_the_default_sampling(tmp_path):
+    (tmp_path / "config.json").write_text(json.dumps(TINY_A))
+    assert read_config(tmp_path).to_spec().default_sampling == dict(temperature=0.7, top_k=20, top_p=0.8)
+    (tmp_path / "generation_config.json").write_text(json.dumps(dict(temperature=0.6, top_k=40, repetition_penalty=1.05)))
+    assert read_config(tmp_path).to_spec().default_sampling == dict(temperature=0.6, top_k=40, top_p=0.8,
+                                                                    repeat_penalty=1.05)
+
+
 def test_window_layers():
     assert read_config(TINY_C).layer_windows() == [None, 24, 24, None]
     raw = dict(TINY_B, use_sliding_window=True, sliding_window=16, max_window_layers=1)
