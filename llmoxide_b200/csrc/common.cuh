@@ -29,7 +29,65 @@ enum { LLMX_F32 = 0, LLMX_BF16 = 1 };
 // kernels; this overlaps each launch and prologue with the kernel before.
 // ---------------------------------------------------------------------------
 #ifdef __CUDACC__
+#ifndef LLMX_TIMELINE
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+#define LLMX_MARK(id)
+#else
+// Built with -DLLMX_TIMELINE, the first thread of every kernel's first CTA records when it reached its
+// dependency wait and when the wait returned (the global nanosecond timer), with the source line of the
+// wait as the kernel's name.  Successive return times are the critical path of a chain of dependent
+// kernels, measured in place (inside a replayed graph, with programmatic launch overlap), which no
+// serialising profiler shows.  Every library keeps its own records; llmx_timeline_read() copies them out
+// and starts over.  Off by default: the records cost a few instructions and an atomic per kernel.
+#define LLMX_TIMELINE_MAX 65536
+static __device__ unsigned long long llmx_timeline_records[3 * LLMX_TIMELINE_MAX];
+static __device__ unsigned int llmx_timeline_count;
+__device__ __forceinline__ unsigned long long llmx_global_ns() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+__device__ __forceinline__ void pdl_wait_at(int line) {
+  const bool rec = (threadIdx.x | threadIdx.y | threadIdx.z | blockIdx.x | blockIdx.y | blockIdx.z) == 0;
+  unsigned long long t0 = 0;
+  if (rec) t0 = llmx_global_ns();
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+  if (rec) {
+    const unsigned long long t1 = llmx_global_ns();
+    const unsigned int i = atomicAdd(&llmx_timeline_count, 1u);
+    if (i < LLMX_TIMELINE_MAX) {
+      llmx_timeline_records[3 * i] = (unsigned long long)line;
+      llmx_timeline_records[3 * i + 1] = t0;
+      llmx_timeline_records[3 * i + 2] = t1;
+    }
+  }
+}
+#define pdl_wait() pdl_wait_at(__LINE__)
+// A mark inside a kernel, by whichever thread calls it: (1000000 + id, linear CTA index, time).
+__device__ __forceinline__ void llmx_mark(int id) {
+  const unsigned int i = atomicAdd(&llmx_timeline_count, 1u);
+  if (i < LLMX_TIMELINE_MAX) {
+    llmx_timeline_records[3 * i] = 1000000ull + (unsigned long long)id;
+    llmx_timeline_records[3 * i + 1] = blockIdx.x + gridDim.x * (blockIdx.y + (unsigned long long)gridDim.y * blockIdx.z);
+    llmx_timeline_records[3 * i + 2] = llmx_global_ns();
+  }
+}
+#define LLMX_MARK(id) llmx_mark(id)
+// out: room for 3 * max_records words (line, reached, returned).  Returns the number of records copied, or the
+// negated cudaError_t of a failed call.
+extern "C" __attribute__((visibility("default"))) int llmx_timeline_read(unsigned long long* out, int max_records) {
+  unsigned int n = 0;
+  cudaError_t e = cudaDeviceSynchronize();
+  if (e == cudaSuccess) e = cudaMemcpyFromSymbol(&n, llmx_timeline_count, sizeof(n));
+  if (e != cudaSuccess) return -(int)e;
+  if (n > LLMX_TIMELINE_MAX) n = LLMX_TIMELINE_MAX;
+  if ((int)n > max_records) n = (unsigned int)max_records;
+  if (n) e = cudaMemcpyFromSymbol(out, llmx_timeline_records, (size_t)n * 3 * sizeof(unsigned long long));
+  const unsigned int zero = 0;
+  if (e == cudaSuccess) e = cudaMemcpyToSymbol(llmx_timeline_count, &zero, sizeof(zero));
+  return e == cudaSuccess ? (int)n : -(int)e;
+}
+#endif
 __device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 
 template <typename... KArgs, typename... Args>

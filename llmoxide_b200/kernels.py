@@ -201,30 +201,38 @@ def attention_paged(q, out, k_cache, v_cache, block_table, token_seq, token_pos,
 N_SM = 148
 
 
-def decode_split(n_seqs: int, n_kv_heads: int, group: int, n_pages: int) -> tuple:
-    """(pages_per_warp, n_chunks) for the decode attention kernel, whose CTA
-    has two warps and so covers 2 * pages_per_warp pages.  Two CTAs fit an SM;
-    the choice minimises rounds of resident CTAs times the length of a warp's
-    walk (a page costs 1, starting and finishing a CTA about 1.5).  It depends
+def decode_chunks(n_seqs: int, n_kv_heads: int, group: int, n_pages: int) -> int:
+    """Into how many shares the decode attention kernel cuts every sequence's
+    visible keys.  A CTA (two warps) takes one share of one (sequence, kv head,
+    8 query heads); two CTAs fit an SM, and the whole grid should be resident
+    at once, so the shares are as many as that allows, up to 16 (the last CTA
+    merges them), and never more than would leave a warp without a 32-key
+    tile of a full block table.  It depends
     on the batch's shape only (not on its lengths), so a captured graph stays
-    valid while the shape does."""
-    base = n_seqs * n_kv_heads * ((group + 15) // 16)
-    slots = 2 * N_SM
-    best = None
-    for ppw in range(1, max(1, -(-n_pages // 2)) + 1):
-        n_chunks = -(-n_pages // (2 * ppw))
-        rounds = -(-base * n_chunks // slots)
-        cost = rounds * (ppw + 1.5)
-        if best is None or cost < best[0]:
-            best = (cost, ppw, n_chunks)
-    return best[1], best[2]
+    valid while the shape does; each sequence's own length is divided on the
+    device."""
+    base = n_seqs * n_kv_heads * ((group + 7) // 8)
+    return max(1, min(2 * N_SM // base, n_pages, 16))
+
+
+_decode_counters: dict = {}
+
+
+def _counters(device, n: int):
+    """Zeroed arrival counters for kernels whose last CTA finishes a reduction;
+    every launch leaves them zero, so one buffer per device serves all calls."""
+    buf = _decode_counters.get(device)
+    if buf is None or buf.numel() < n:
+        buf = torch.zeros(max(n, 16384), dtype=torch.int32, device=device)
+        _decode_counters[device] = buf
+    return buf
 
 
 def attention_decode(q, out, k_cache, v_cache, block_table, seq_past, n_heads: int, n_kv_heads: int,
                      head_dim: int, window, scale: float) -> None:
     """One new token per sequence, bfloat16: q, out [B,H*D] in batch order;
-    seq_past[b] is the token's position.  The key range is split over CTAs and
-    merged through a float32 workspace."""
+    seq_past[b] is the token's position.  Each sequence's keys are split over
+    CTAs; the CTA that finishes last merges them through a float32 workspace."""
     _dev(q, out, k_cache, v_cache, block_table, seq_past)
     _contig("q", q), _contig("out", out), _contig("block_table", block_table)
     assert q.dtype == torch.bfloat16 and k_cache.dtype == torch.bfloat16 and out.dtype == torch.bfloat16
@@ -234,18 +242,26 @@ def attention_decode(q, out, k_cache, v_cache, block_table, seq_past, n_heads: i
     n_pages = block_table.shape[1]
     if window:
         n_pages = min(n_pages, (window + PAGE - 2) // PAGE + 1)
-    ppw, n_chunks = decode_split(B, n_kv_heads, n_heads // n_kv_heads, n_pages)
-    ws = (torch.empty(B * n_heads * n_chunks * (head_dim + 2), dtype=torch.float32, device=q.device)
-          if n_chunks > 1 else None)
-    f = _fn("attention_decode", "llmx_attention_decode",
-            [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int,
-             c_int, c_int, c_float, c_int, c_int, c_void_p])
-    _check(f(_ptr(q), _ptr(out), _ptr(k_cache), _ptr(v_cache), _ptr(block_table), block_table.shape[1],
-             _ptr(seq_past), _ptr(ws), B, n_heads, n_kv_heads, head_dim, int(window or 0), scale, ppw, n_chunks,
-             _stream()), "attention_decode")
+    group = n_heads // n_kv_heads
+    n_chunks = decode_chunks(B, n_kv_heads, group, n_pages)
+    ws = counters = None
     if n_chunks > 1:
-        global launch_count
-        launch_count += 1   # the merge kernel
+        ws = torch.empty(B * n_heads * n_chunks * (head_dim + 4), dtype=torch.float32, device=q.device)
+        counters = _counters(q.device, B * n_kv_heads * ((group + 7) // 8))
+    f = _fn("attention_decode", "llmx_attention_decode",
+            [c_void_p, c_void_p, c_void_p, c_void_p, c_longlong, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int,
+             c_int, c_int, c_int, c_int, c_float, c_int, c_void_p])
+    _check(f(_ptr(q), _ptr(out), _ptr(k_cache), _ptr(v_cache), k_cache.shape[0], _ptr(block_table),
+             block_table.shape[1],
+             _ptr(seq_past), _ptr(ws), _ptr(counters), B, n_heads, n_kv_heads, head_dim, int(window or 0), scale,
+             n_chunks, _stream()), "attention_decode")
+
+
+def attention_decode_status() -> int:
+    """0, or 1 after a decode attention launch whose shared-memory copies never completed."""
+    lib = load_library("attention_decode")
+    lib.llmx_attention_decode_status.restype = c_int
+    return int(lib.llmx_attention_decode_status())
 
 
 def attention_prefill_supports(q, k_cache, head_dim: int) -> bool:

@@ -397,7 +397,7 @@ def test_gemm_tc_refuses_what_it_cannot_do():
         kernels.gemm_tc(x, w, torch.empty(4, 16, dtype=torch.bfloat16, device=DEV))
 
 
-def _attention_case(H, G, D, lens, pasts, window, seed=0):
+def _attention_case(H, G, D, lens, pasts, window, seed=0, n_pages=64):
     """Sequences with ``pasts[i]`` cached positions and ``lens[i]`` new tokens;
     returns everything the bfloat16 attention kernels need and the plain result
     for the new tokens."""
@@ -415,7 +415,7 @@ def _attention_case(H, G, D, lens, pasts, window, seed=0):
             q[n - 1, H - 1, :8] = 3.0
         full = plain.causal_attention(q, k, v, G, window)
         qs.append(q[P:]), ks.append(k), vs.append(v), want.append(full[P:])
-    kc, vc, table = _paged(list(zip(ks, vs)), G, D, torch.bfloat16, n_pages=64)
+    kc, vc, table = _paged(list(zip(ks, vs)), G, D, torch.bfloat16, n_pages=n_pages)
     starts = torch.tensor([0] + list(np.cumsum(lens)), dtype=torch.int32)
     q_all = torch.cat(qs).reshape(-1, H * D).bfloat16()
     return q_all, kc, vc, table, starts, torch.tensor(pasts, dtype=torch.int32), torch.cat(want).reshape(-1, H * D)
@@ -453,7 +453,7 @@ def test_attention_prefill_tcgen05(H, G, window):
         assert rel(out[lo:hi], want[lo:hi]) < 1.2e-2, (i, lens[i], pasts[i])
 
 
-@pytest.mark.parametrize("H, G, D", [(8, 2, 128), (6, 6, 64), (5, 1, 48), (16, 2, 80), (4, 4, 256)])
+@pytest.mark.parametrize("H, G, D", [(8, 2, 128), (6, 6, 64), (5, 1, 48), (16, 2, 80), (4, 4, 256), (24, 2, 16)])
 @pytest.mark.parametrize("window", [None, 100])
 def test_attention_decode_split(H, G, D, window):
     from llmoxide_b200 import kernels
@@ -473,3 +473,24 @@ def test_attention_decode_split(H, G, D, window):
     kernels.attention_decode(q.to(DEV), out2, kc.to(DEV), vc.to(DEV), wide.to(DEV), past.to(DEV), H, G, D, window,
                              1 / math.sqrt(D))
     assert rel(out2, out) < 1e-2
+    # and again: the arrival counters were left at zero
+    out3 = torch.full_like(out, float("nan"))
+    kernels.attention_decode(q.to(DEV), out3, kc.to(DEV), vc.to(DEV), table.to(DEV), past.to(DEV), H, G, D, window,
+                             1 / math.sqrt(D))
+    assert torch.equal(out3, out)
+    assert kernels.attention_decode_status() == 0
+
+
+def test_attention_decode_many_sequences_one_share_each():
+    """A batch that fills the GPU by itself: every sequence's keys stay in one CTA and nothing is merged."""
+    from llmoxide_b200 import kernels
+    H, G, D = 8, 4, 64
+    pasts = [(37 * i) % 260 for i in range(80)]
+    assert kernels.decode_chunks(len(pasts), G, H // G, 5) == 1
+    q, kc, vc, table, starts, past, want = _attention_case(H, G, D, [1] * len(pasts), pasts, None, n_pages=256)
+    out = torch.full_like(q, float("nan"), device=DEV)
+    kernels.attention_decode(q.to(DEV), out, kc.to(DEV), vc.to(DEV), table.to(DEV), past.to(DEV), H, G, D, None,
+                             1 / math.sqrt(D))
+    assert not out.isnan().any()
+    for i in range(len(pasts)):
+        assert rel(out[i], want[i]) < 1.2e-2, (i, pasts[i])

@@ -43,8 +43,8 @@ def test_no_alloc_entry_point_matches_the_allocating_one():
 
     lib = load_library("attention_decode")
     fn = lib.llmx_attention_decode_noalloc
-    fn.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int,
-                   c_int, c_float, c_int, c_int, c_void_p]
+    fn.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, ctypes.c_longlong, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int,
+                   c_int, c_float, c_int, c_void_p]
     fn.restype = c_int
     H, G, D = 8, 2, 128
     scale = 1 / math.sqrt(D)
@@ -54,18 +54,18 @@ def test_no_alloc_entry_point_matches_the_allocating_one():
         q, kc, vc, table, past = _case(B, H, G, D, lengths, seed=call)
         want = torch.empty_like(q)
         kernels.attention_decode(q, want, kc, vc, table, past, H, G, D, None, scale)
-        ppw, n_chunks = kernels.decode_split(B, G, H // G, table.shape[1])
+        n_chunks = kernels.decode_chunks(B, G, H // G, table.shape[1])
         assert n_chunks > 1, "the case must use the workspace"
         got = torch.full_like(q, float("nan"))
-        rc = fn(q.data_ptr(), got.data_ptr(), kc.data_ptr(), vc.data_ptr(), table.data_ptr(), table.shape[1],
-                past.data_ptr(), B, H, G, D, 0, scale, ppw, n_chunks, stream)
+        rc = fn(q.data_ptr(), got.data_ptr(), kc.data_ptr(), vc.data_ptr(), kc.shape[0], table.data_ptr(), table.shape[1],
+                past.data_ptr(), B, H, G, D, 0, scale, n_chunks, stream)
         assert rc == 0
         torch.cuda.synchronize()
         assert not got.isnan().any()
         err = (got.float() - want.float()).abs().max() / want.float().abs().max()
         assert err < 6e-3, (call, float(err))      # the kernel tests' tolerance for one bfloat16 rounding
     # a request beyond the fixed workspace is refused, and nothing runs
-    big_chunks = WS_FLOATS // (B * H * (D + 2)) + 1
-    rc = fn(q.data_ptr(), got.data_ptr(), kc.data_ptr(), vc.data_ptr(), table.data_ptr(), table.shape[1],
-            past.data_ptr(), B, H, G, D, 0, scale, 1, big_chunks, stream)
+    big_chunks = WS_FLOATS // (B * H * (D + 4)) + 1
+    rc = fn(q.data_ptr(), got.data_ptr(), kc.data_ptr(), vc.data_ptr(), kc.shape[0], table.data_ptr(), table.shape[1],
+            past.data_ptr(), B, H, G, D, 0, scale, big_chunks, stream)
     assert rc == TOO_LARGE
