@@ -34,11 +34,15 @@
 // the first tiles stream while the kernel that wrote q and the new key still
 // runs; only the tile that holds the new token's row waits.
 //
-// The two warps are merged through shared memory and the CTA writes one
-// unnormalised partial (acc, max, sum) per head to the workspace.  The CTA
-// that arrives last at its (sequence, kv head, head group)'s counter merges
-// the chunks, always in chunk order, so the result does not depend on which
-// CTA that was; it leaves the counter at zero for the next launch.
+// The two warps are merged through shared memory into one unnormalised
+// partial (acc, max, sum) per head.  With up to 8 chunks the CTAs of one
+// (sequence, kv head, head group) form a thread-block cluster and merge their
+// partials out of each other's shared memory, each CTA a slice of the output:
+// no workspace, no trip through global memory.  With more chunks the partials
+// go to a workspace, and the CTA that arrives last at the group's counter
+// merges them and leaves the counter at zero for the next launch.  Either way
+// the chunks are summed in chunk order, so the result does not depend on
+// timing.
 #include "tc_ptx.cuh"
 
 #define DEC_WARPS 2
@@ -112,7 +116,7 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
                         const bf16* __restrict__ q, const bf16* __restrict__ k_cache, const bf16* __restrict__ v_cache,
                         const int* __restrict__ block_table, int table_width, const int* __restrict__ seq_past,
                         float* __restrict__ ws, unsigned int* __restrict__ counters, bf16* __restrict__ out, int H,
-                        int G, int window, float scale_log2, int n_chunks) {
+                        int G, int window, float scale_log2, int n_chunks, int cluster_merge) {
   using S = DecSmem<D>;
   constexpr int KSTEPS = D / 16;
   constexpr uint32_t TILE_BYTES = 2u * DEC_TILE * D * 2u;        // what one stage's copies bring
@@ -136,10 +140,8 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
 
   uint8_t* wsm = smem + warp * S::WARP;
   const uint32_t sKV = (uint32_t)__cvta_generic_to_shared(wsm);
-  if (S::TMA && (sKV & 1023u)) {           // the swizzled layout is a function of the address: refuse, never guess
-    if (threadIdx.x == 0) atomicExch(&g_dec_status, 2);
-    return;
-  }
+  const bool misaligned = S::TMA && (sKV & 1023u);   // the swizzled layout is a function of the address: refuse, never guess
+  if (misaligned && threadIdx.x == 0) atomicExch(&g_dec_status, 2);
   const uint32_t bars = (uint32_t)__cvta_generic_to_shared(smem + S::BARS) + warp * DEC_STAGES * 8;
   if (lane == 0) {
     // a tensor copy's bytes are counted against one announcement; cp.async counts one arrival per lane
@@ -157,7 +159,7 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
   const int per_warp = (t_last - t_first + n_chunks * DEC_WARPS) / (n_chunks * DEC_WARPS);   // ceil(tiles / warps)
   const int tile_lo = t_first + (chunk * DEC_WARPS + warp) * per_warp;
   const int tile_hi = min(tile_lo + per_warp - 1, t_last);
-  const int n_tiles = tile_hi - tile_lo + 1;                      // <= 0: nothing to do
+  const int n_tiles = misaligned ? 0 : tile_hi - tile_lo + 1;     // <= 0: nothing to do
 
   auto load_tile = [&](int tile, int stage) {
     const int key0 = tile * DEC_TILE;
@@ -323,6 +325,8 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
   __syncthreads();
   float* macc = reinterpret_cast<float*>(smem);                                  // [DEC_WARPS][DEC_ROWS][D]
   float* mml = macc + DEC_WARPS * DEC_ROWS * D;                                  // [DEC_WARPS][DEC_ROWS][2]
+  float* cacc = mml + DEC_WARPS * DEC_ROWS * 2;                                  // [DEC_ROWS][D]  the CTA's partial,
+  float* cml = cacc + DEC_ROWS * D;                                              // [DEC_ROWS][2]  for its cluster
   {
     const int hA = 2 * tq, hB = hA + 1;
 #pragma unroll
@@ -356,6 +360,12 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
     }
     if (n_chunks == 1) {
       out[((size_t)b * H + h0 + h) * D + d] = __float2bfloat16_rn(a / ls);   // nothing to merge with
+    } else if (cluster_merge) {
+      cacc[idx] = a;
+      if (d == 0) {
+        cml[2 * h] = mx;
+        cml[2 * h + 1] = ls;
+      }
     } else {
       float* dst = ws + (((size_t)b * H + h0 + h) * n_chunks + chunk) * DEC_WS_ROW(D);
       __stcg(dst + d, a);
@@ -366,6 +376,58 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
     }
   }
   if (n_chunks == 1) return;
+
+  if (cluster_merge) {
+    // ---- the cluster's CTAs (rank = chunk) each merge a slice of the outputs out of all ranks' shared memory ----
+    // out = sum_c 2^(m_c - m) acc_c / sum_c 2^(m_c - m) l_c   (the maxima are in the base-2 domain)
+    asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+    asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+    const uint32_t my_acc = (uint32_t)__cvta_generic_to_shared(cacc), my_ml = (uint32_t)__cvta_generic_to_shared(cml);
+    const int groups = n_heads * (D / 4), per = (groups + n_chunks - 1) / n_chunks;
+    const int hi = min(groups, (chunk + 1) * per);
+    for (int idx = chunk * per + threadIdx.x; idx < hi; idx += DEC_WARPS * 32) {
+      const int h = idx / (D / 4), d = (idx % (D / 4)) * 4;
+      float mc[8], lc[8], mx = -INFINITY;
+#pragma unroll
+      for (int c = 0; c < 8; ++c) {
+        mc[c] = -INFINITY;
+        lc[c] = 0.f;
+        if (c < n_chunks) {
+          uint32_t ra;
+          asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(ra) : "r"(my_ml + 8u * h), "r"(c));
+          asm volatile("ld.shared::cluster.v2.f32 {%0, %1}, [%2];" : "=f"(mc[c]), "=f"(lc[c]) : "r"(ra));
+          mx = fmaxf(mx, mc[c]);
+        }
+      }
+      float4 a = make_float4(0.f, 0.f, 0.f, 0.f);
+      float l = 0.f;
+#pragma unroll
+      for (int c = 0; c < 8; ++c) {
+        if (c < n_chunks && mc[c] != -INFINITY) {            // -inf: a chunk that got none of the keys
+          const float w = exp2f(mc[c] - mx);
+          uint32_t ra;
+          float4 v;
+          asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(ra) : "r"(my_acc + 4u * (h * D + d)), "r"(c));
+          asm volatile("ld.shared::cluster.v4.f32 {%0, %1, %2, %3}, [%4];"
+                       : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w)
+                       : "r"(ra));
+          a.x += w * v.x;
+          a.y += w * v.y;
+          a.z += w * v.z;
+          a.w += w * v.w;
+          l += w * lc[c];
+        }
+      }
+      const float r = 1.f / l;
+      __nv_bfloat162 lo = __floats2bfloat162_rn(a.x * r, a.y * r), hi2 = __floats2bfloat162_rn(a.z * r, a.w * r);
+      uint2 packed = make_uint2(*reinterpret_cast<uint32_t*>(&lo), *reinterpret_cast<uint32_t*>(&hi2));
+      *reinterpret_cast<uint2*>(out + ((size_t)b * H + h0 + h) * D + d) = packed;
+    }
+    // nobody leaves while another CTA may still read its shared memory
+    asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+    asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+    return;
+  }
 
   // ---- the last CTA of this (sequence, kv head, head group) merges the chunks ------------------
   // out = sum_c 2^(m_c - m) acc_c / sum_c 2^(m_c - m) l_c   (the maxima are in the base-2 domain)
@@ -438,7 +500,7 @@ static int launch_decode(const void* q, void* out, const void* k_cache, const vo
   const int head_groups = (R + DEC_ROWS - 1) / DEC_ROWS;
   dim3 grid(n_chunks, G * head_groups, B);
   size_t smem = DecSmem<D>::TOTAL;
-  size_t merge = (size_t)DEC_WARPS * DEC_ROWS * (D + 2) * sizeof(float);
+  size_t merge = (size_t)(DEC_WARPS + 1) * DEC_ROWS * (D + 2) * sizeof(float);
   if (merge < (size_t)DEC_ROWS * (2 * DEC_MAX_CHUNKS + 1) * sizeof(float)) merge = (size_t)DEC_ROWS * (2 * DEC_MAX_CHUNKS + 1) * sizeof(float);
   if (merge > smem) smem = merge;
   auto kernel = attention_decode_kernel<D>;
@@ -456,15 +518,22 @@ static int launch_decode(const void* q, void* out, const void* k_cache, const vo
     if (make_map(&mk, k_cache, cache_rows, D, D, DEC_TILE, false)) return LLMX_REFUSED(4);
     if (make_map(&mv, v_cache, cache_rows, D, D, DEC_TILE, false)) return LLMX_REFUSED(4);
   }
-  launch_pdl(kernel, grid, dim3(DEC_WARPS * 32), smem, stream, mk, mv, (const bf16*)q, (const bf16*)k_cache,
-             (const bf16*)v_cache, block_table, table_width, seq_past, ws, counters, (bf16*)out, H, G, window,
-             scale * 1.4426950408889634f, n_chunks);
+  // up to 8 chunks (the portable cluster size): merged inside a cluster, nothing goes through the workspace
+  const int cluster_merge = (n_chunks > 1 && n_chunks <= 8) ? 1 : 0;
+  if (cluster_merge)
+    launch_pdl_cluster(kernel, grid, dim3(DEC_WARPS * 32), smem, stream, (unsigned)n_chunks, mk, mv, (const bf16*)q,
+                       (const bf16*)k_cache, (const bf16*)v_cache, block_table, table_width, seq_past, ws, counters,
+                       (bf16*)out, H, G, window, scale * 1.4426950408889634f, n_chunks, cluster_merge);
+  else
+    launch_pdl(kernel, grid, dim3(DEC_WARPS * 32), smem, stream, mk, mv, (const bf16*)q, (const bf16*)k_cache,
+               (const bf16*)v_cache, block_table, table_width, seq_past, ws, counters, (bf16*)out, H, G, window,
+               scale * 1.4426950408889634f, n_chunks, cluster_merge);
   return LLMX_LAUNCH_STATUS();
 }
 
 // q, out: bf16 [B, H*D] (one token per sequence, in batch order); seq_past[b] = the token's position.
 // k_cache, v_cache: one cache entry [n_pages, G, 64, D], 16-byte aligned.
-// Every sequence's visible keys are cut into n_chunks <= 32 shares.  With n_chunks > 1: ws is a float32 workspace
+// Every sequence's visible keys are cut into n_chunks <= 32 shares.  With n_chunks > 8: ws is a float32 workspace
 // of B*H*n_chunks*(D+4) elements (16-byte aligned), and counters holds B * G * ceil((H/G)/8) words that are zero before the first
 // launch (each launch leaves them zero).
 LLMX_API int llmx_attention_decode(const void* q, void* out, const void* k_cache, const void* v_cache,
@@ -473,7 +542,7 @@ LLMX_API int llmx_attention_decode(const void* q, void* out, const void* k_cache
                                    int n_chunks, cudaStream_t stream) {
   if (B <= 0) return 0;
   if (H <= 0 || G <= 0 || H % G || window < 0 || n_chunks < 1 || n_chunks > DEC_MAX_CHUNKS ||
-      (n_chunks > 1 && (!ws || !counters || ((uintptr_t)ws & 15))) || n_pages <= 0 ||
+      (n_chunks > 8 && (!ws || !counters || ((uintptr_t)ws & 15))) || n_pages <= 0 ||
       ((uintptr_t)k_cache & 15) || ((uintptr_t)v_cache & 15) || ((uintptr_t)q & 3))
     return LLMX_REFUSED(1);
   if (B > 65535 || (long long)G * ((H / G + DEC_ROWS - 1) / DEC_ROWS) > 65535) return LLMX_REFUSED(3);

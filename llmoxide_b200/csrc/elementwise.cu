@@ -63,60 +63,115 @@ LLMX_API int llmx_embed(const void* table, int table_dtype, const int* tokens, f
 //   out[r,:] = v * (1/sqrt(mean(v^2)+eps)) * gain
 // One block per row; a row wider than one pass is staged in shared memory as float32.
 // ---------------------------------------------------------------------------
-// Threads per row are fixed by d alone (so the reduction order does not depend on the batch):
-// a thread takes 4 consecutive elements per pass, and rows up to 4096 wide finish in one pass.
-template <typename TD, typename TO>
-__global__ void add_rms_norm_kernel(float* __restrict__ h, const TD* __restrict__ delta, int n_split,
-                                    size_t split_stride, const int* __restrict__ rows,
-                                    const float* __restrict__ gain, float eps, TO* __restrict__ out,
-                                    int d, int write_h) {
+// The thread count and each thread's elements are fixed by d alone, so the reduction order does not depend on the
+// batch.  A CTA has at most 512 threads of at most 64 registers: it fits an SM beside the CTAs of the matrix
+// product before it, so it is resident, with its weights fetched, when that kernel ends.  Rows up to 8192 wide
+// stay in registers from the sum to the store (up to 4 vectors of 4 elements per thread, vector c of thread j at
+// column 4 (c nthreads + j)); wider rows are staged in shared memory.
+
+// v += sum_s p[s * stride .. +4), the partials added in the order s = 0..S-1, their loads issued eight at a time
+// (a loop of load-then-add would pay one memory round trip per partial).
+template <typename TD>
+__device__ __forceinline__ void add_partials4(float4& v, const TD* p, int n_split, size_t split_stride) {
+  for (int s0 = 0; s0 < n_split; s0 += 8) {
+    float4 y[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j)
+      if (s0 + j < n_split) y[j] = load4(p + (size_t)(s0 + j) * split_stride);
+#pragma unroll
+    for (int j = 0; j < 8; ++j)
+      if (s0 + j < n_split) {
+        v.x += y[j].x; v.y += y[j].y; v.z += y[j].z; v.w += y[j].w;
+      }
+  }
+}
+
+// CH > 0: the row fits CH vectors per thread.  CH == 0: any width, staged in shared memory.
+template <typename TD, typename TO, int CH>
+__global__ void __launch_bounds__(512)
+add_rms_norm_kernel(float* __restrict__ h, const TD* __restrict__ delta, int n_split, size_t split_stride,
+                    const int* __restrict__ rows, const float* __restrict__ gain, float eps, TO* __restrict__ out,
+                    int d, int write_h) {
   extern __shared__ float row_buf[];
   __shared__ float red[32];
   pdl_launch_dependents();
-  pdl_wait();
+  // The row index (a step input) and the gain (a weight) do not come from the kernel before: they are
+  // fetched while that kernel still runs.
   const int r = blockIdx.x;
   const int t = rows ? rows[r] : r;
   float* hrow = h + (size_t)t * d;
   const int nthreads = blockDim.x;
   float ss = 0.f;
-  if ((d & 3) == 0 && d <= 4 * nthreads) {
-    // The row fits one pass: a thread keeps its four elements in registers from the sum to the store.
-    const int i = threadIdx.x * 4;
-    const bool live = i < d;
-    float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
-    if (live) {
-      v = load4(hrow + i);
-      if (delta) {
-        const TD* p = delta + (size_t)t * d + i;
-        for (int s = 0; s < n_split; ++s) {
-          const float4 y = load4(p + s * split_stride);
-          v.x += y.x; v.y += y.y; v.z += y.z; v.w += y.w;
+  if (CH > 0) {
+    constexpr int NC = CH > 0 ? CH : 1;
+    float4 g[NC], v[NC];
+#pragma unroll
+    for (int c = 0; c < NC; ++c) {
+      const int i = (c * nthreads + threadIdx.x) * 4;
+      g[c] = (out && i < d) ? load4(gain + i) : make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+    pdl_wait();
+#pragma unroll
+    for (int c = 0; c < NC; ++c) {
+      const int i = (c * nthreads + threadIdx.x) * 4;
+      v[c] = i < d ? load4(hrow + i) : make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+    if (delta) {
+      // partials of every vector of the thread, eight loads in flight
+      constexpr int J = 8 / NC;
+      for (int s0 = 0; s0 < n_split; s0 += J) {
+        float4 y[NC][J];
+#pragma unroll
+        for (int c = 0; c < NC; ++c) {
+          const int i = (c * nthreads + threadIdx.x) * 4;
+#pragma unroll
+          for (int j = 0; j < J; ++j)
+            if (i < d && s0 + j < n_split) y[c][j] = load4(delta + (size_t)(s0 + j) * split_stride + (size_t)t * d + i);
         }
-        if (write_h) store4(hrow + i, v);
+#pragma unroll
+        for (int c = 0; c < NC; ++c) {
+          const int i = (c * nthreads + threadIdx.x) * 4;
+#pragma unroll
+          for (int j = 0; j < J; ++j)
+            if (i < d && s0 + j < n_split) {
+              v[c].x += y[c][j].x; v[c].y += y[c][j].y; v[c].z += y[c][j].z; v[c].w += y[c][j].w;
+            }
+        }
       }
-      ss = v.x * v.x;
-      ss += v.y * v.y;
-      ss += v.z * v.z;
-      ss += v.w * v.w;
+      if (write_h) {
+#pragma unroll
+        for (int c = 0; c < NC; ++c) {
+          const int i = (c * nthreads + threadIdx.x) * 4;
+          if (i < d) store4(hrow + i, v[c]);
+        }
+      }
+    }
+#pragma unroll
+    for (int c = 0; c < NC; ++c) {        // dead vectors are zero
+      ss += v[c].x * v[c].x;
+      ss += v[c].y * v[c].y;
+      ss += v[c].z * v[c].z;
+      ss += v[c].w * v[c].w;
     }
     const float total = block_sum(ss, red);
     const float scale = 1.0f / sqrtf(total / (float)d + eps);
-    if (out && live) {
-      const float4 g = load4(gain + i);
-      store4(out + (size_t)r * d + i,
-             make_float4((v.x * scale) * g.x, (v.y * scale) * g.y, (v.z * scale) * g.z, (v.w * scale) * g.w));
+    if (out) {
+#pragma unroll
+      for (int c = 0; c < NC; ++c) {
+        const int i = (c * nthreads + threadIdx.x) * 4;
+        if (i < d)
+          store4(out + (size_t)r * d + i, make_float4((v[c].x * scale) * g[c].x, (v[c].y * scale) * g[c].y,
+                                                      (v[c].z * scale) * g[c].z, (v[c].w * scale) * g[c].w));
+      }
     }
     return;
   }
+  pdl_wait();
   if ((d & 3) == 0) {
     for (int i = threadIdx.x * 4; i < d; i += nthreads * 4) {
       float4 v = load4(hrow + i);
       if (delta) {
-        const TD* p = delta + (size_t)t * d + i;
-        for (int s = 0; s < n_split; ++s) {
-          const float4 y = load4(p + s * split_stride);
-          v.x += y.x; v.y += y.y; v.z += y.z; v.w += y.w;
-        }
+        add_partials4(v, delta + (size_t)t * d + i, n_split, split_stride);
         if (write_h) store4(hrow + i, v);
       }
       store4(row_buf + i, v);
@@ -145,24 +200,41 @@ __global__ void add_rms_norm_kernel(float* __restrict__ h, const TD* __restrict_
   }
 }
 
-static int norm_threads(int d) {
-  int t = (d / 4 + 31) / 32 * 32;
-  return t < 64 ? 64 : (t > 1024 ? 1024 : t);
+// (vectors per thread, threads) for a row of d elements; 0 vectors: the staged path
+static void norm_shape(int d, int& ch, int& threads) {
+  const int vecs = (d + 3) / 4;
+  ch = 0;
+  threads = 512;
+  if ((d & 3) == 0 && vecs <= 4 * 512) {
+    ch = vecs <= 512 ? 1 : (vecs <= 1024 ? 2 : 4);
+    threads = ((vecs + ch - 1) / ch + 31) / 32 * 32;
+    if (threads < 64) threads = 64;
+  }
 }
 
 template <typename TD, typename TO>
 static int launch_add_rms_norm(float* h, const void* delta, int n_split, size_t split_stride, const int* rows,
                                int n_rows, const float* gain, float eps, void* out, int d, int write_h,
                                cudaStream_t stream) {
-  const size_t smem = (size_t)d * sizeof(float);
-  auto kernel = add_rms_norm_kernel<TD, TO>;
-  if (smem > 48 * 1024) {
-    if (smem > 200 * 1024) return LLMX_REFUSED(3);
-    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    if (e != cudaSuccess) return (int)e;
+  int ch, threads;
+  norm_shape(d, ch, threads);
+#define GO(CH, SMEM)                                                                                              \
+  launch_pdl(add_rms_norm_kernel<TD, TO, CH>, dim3(n_rows), dim3(threads), SMEM, stream, h, (const TD*)delta,    \
+             n_split, split_stride, rows, gain, eps, (TO*)out, d, write_h)
+  if (ch == 1) GO(1, 0);
+  else if (ch == 2) GO(2, 0);
+  else if (ch == 4) GO(4, 0);
+  else {
+    const size_t smem = (size_t)d * sizeof(float);
+    if (smem > 48 * 1024) {
+      if (smem > 200 * 1024) return LLMX_REFUSED(3);
+      cudaError_t e = cudaFuncSetAttribute(add_rms_norm_kernel<TD, TO, 0>,
+                                           cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+      if (e != cudaSuccess) return (int)e;
+    }
+    GO(0, smem);
   }
-  launch_pdl(kernel, dim3(n_rows), dim3(norm_threads(d)), smem, stream, h, (const TD*)delta, n_split, split_stride, rows, gain, eps,
-                                                    (TO*)out, d, write_h);
+#undef GO
   return LLMX_LAUNCH_STATUS();
 }
 
@@ -202,7 +274,8 @@ __global__ void qk_norm_rope_cache_kernel(const TIN* __restrict__ qkv, int n_spl
                                           int write_cache) {
   extern __shared__ float head_buf[];
   pdl_launch_dependents();
-  pdl_wait();
+  // Positions, block table, gains and rotation tables are step inputs or weights, not results of the kernel
+  // before: they are fetched ahead of the dependency wait, which only the qkv values need.
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int t = blockIdx.x;                        // tokens on x: a step may bring more than 65535
   const int slot = blockIdx.y * QKV_WARPS + warp;  // which head of the fused row
@@ -230,19 +303,23 @@ __global__ void qk_norm_rope_cache_kernel(const TIN* __restrict__ qkv, int n_spl
     // Head size 128 with full rotation: a lane owns dims 4*lane..4*lane+3, read and written as one
     // vector; the rotation partner (dim +-64) lives in lane +-16 and comes by shuffle.
     const int d0 = 4 * lane;
-    float4 x = load4(src + d0);
-    for (int s = 1; s < n_split; ++s) {
-      const float4 y = load4(src + s * split_stride + d0);
-      x.x += y.x; x.y += y.y; x.z += y.z; x.w += y.w;
+    const bool is_v = !is_q && !is_k;
+    float4 gn = make_float4(1.f, 1.f, 1.f, 1.f), cs = gn, sn = gn;
+    if (!is_v) {
+      if (gain) gn = load4(gain + d0);
+      cs = load4(cos_t + (size_t)pos * 64 + (d0 & 63));
+      sn = load4(sin_t + (size_t)pos * 64 + (d0 & 63));
     }
-    if (!is_q && !is_k) {  // v: stored as it is
+    pdl_wait();
+    float4 x = load4(src + d0);
+    add_partials4(x, src + split_stride + d0, n_split - 1, split_stride);
+    if (is_v) {  // v: stored as it is
       store4(cache_row + d0, x);
       return;
     }
     if (gain) {
       const float ssq = warp_sum(x.x * x.x + x.y * x.y + x.z * x.z + x.w * x.w);
       const float scale = 1.0f / sqrtf(ssq / 128.0f + eps);
-      const float4 gn = load4(gain + d0);
       x.x = (x.x * scale) * gn.x; x.y = (x.y * scale) * gn.y; x.z = (x.z * scale) * gn.z; x.w = (x.w * scale) * gn.w;
     }
     float4 p;
@@ -250,8 +327,6 @@ __global__ void qk_norm_rope_cache_kernel(const TIN* __restrict__ qkv, int n_spl
     p.y = __shfl_xor_sync(0xffffffffu, x.y, 16);
     p.z = __shfl_xor_sync(0xffffffffu, x.z, 16);
     p.w = __shfl_xor_sync(0xffffffffu, x.w, 16);
-    const int ti = d0 & 63;
-    const float4 cs = load4(cos_t + (size_t)pos * 64 + ti), sn = load4(sin_t + (size_t)pos * 64 + ti);
     float4 r;
     if (lane < 16) {   // dims i < 64: x_i cos - x_{i+64} sin
       r = make_float4(x.x * cs.x - p.x * sn.x, x.y * cs.y - p.y * sn.y, x.z * cs.z - p.z * sn.z, x.w * cs.w - p.w * sn.w);
@@ -262,6 +337,7 @@ __global__ void qk_norm_rope_cache_kernel(const TIN* __restrict__ qkv, int n_spl
     else store4(cache_row + d0, r);
     return;
   }
+  pdl_wait();
   if (!is_q && !is_k) {  // v: stored as it is
     for (int i = lane; i < D; i += 32) cache_row[i] = from_f32<TC>(value(i));
     return;

@@ -205,14 +205,14 @@ def decode_chunks(n_seqs: int, n_kv_heads: int, group: int, n_pages: int) -> int
     """Into how many shares the decode attention kernel cuts every sequence's
     visible keys.  A CTA (two warps) takes one share of one (sequence, kv head,
     8 query heads); two CTAs fit an SM, and the whole grid should be resident
-    at once, so the shares are as many as that allows, up to 16 (the last CTA
-    merges them), and never more than would leave a warp without a 32-key
-    tile of a full block table.  It depends
+    at once, so the shares are as many as that allows, up to 8 (the CTAs of a
+    sequence and kv head then merge as one thread-block cluster), and never
+    more than would leave a warp without a 32-key tile of a full block table.  It depends
     on the batch's shape only (not on its lengths), so a captured graph stays
     valid while the shape does; each sequence's own length is divided on the
     device."""
     base = n_seqs * n_kv_heads * ((group + 7) // 8)
-    return max(1, min(2 * N_SM // base, n_pages, 16))
+    return max(1, min(2 * N_SM // base, n_pages, 8))
 
 
 _decode_counters: dict = {}
@@ -229,10 +229,11 @@ def _counters(device, n: int):
 
 
 def attention_decode(q, out, k_cache, v_cache, block_table, seq_past, n_heads: int, n_kv_heads: int,
-                     head_dim: int, window, scale: float) -> None:
+                     head_dim: int, window, scale: float, n_chunks: int = 0) -> None:
     """One new token per sequence, bfloat16: q, out [B,H*D] in batch order;
     seq_past[b] is the token's position.  Each sequence's keys are split over
-    CTAs; the CTA that finishes last merges them through a float32 workspace."""
+    n_chunks CTAs (0: chosen from the batch's shape), which merge inside a
+    cluster, or beyond 8 chunks through a float32 workspace."""
     _dev(q, out, k_cache, v_cache, block_table, seq_past)
     _contig("q", q), _contig("out", out), _contig("block_table", block_table)
     assert q.dtype == torch.bfloat16 and k_cache.dtype == torch.bfloat16 and out.dtype == torch.bfloat16
@@ -243,9 +244,9 @@ def attention_decode(q, out, k_cache, v_cache, block_table, seq_past, n_heads: i
     if window:
         n_pages = min(n_pages, (window + PAGE - 2) // PAGE + 1)
     group = n_heads // n_kv_heads
-    n_chunks = decode_chunks(B, n_kv_heads, group, n_pages)
+    n_chunks = n_chunks or decode_chunks(B, n_kv_heads, group, n_pages)
     ws = counters = None
-    if n_chunks > 1:
+    if n_chunks > 8:
         ws = torch.empty(B * n_heads * n_chunks * (head_dim + 4), dtype=torch.float32, device=q.device)
         counters = _counters(q.device, B * n_kv_heads * ((group + 7) // 8))
     f = _fn("attention_decode", "llmx_attention_decode",

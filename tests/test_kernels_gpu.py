@@ -478,6 +478,17 @@ def test_attention_decode_split(H, G, D, window):
     kernels.attention_decode(q.to(DEV), out3, kc.to(DEV), vc.to(DEV), table.to(DEV), past.to(DEV), H, G, D, window,
                              1 / math.sqrt(D))
     assert torch.equal(out3, out)
+    # more than 8 shares: merged through the workspace by the CTA that arrives last; twice (the counters return to zero)
+    for _ in range(2):
+        out4 = torch.full_like(out, float("nan"))
+        kernels.attention_decode(q.to(DEV), out4, kc.to(DEV), vc.to(DEV), table.to(DEV), past.to(DEV), H, G, D, window,
+                                 1 / math.sqrt(D), n_chunks=11)
+        assert rel(out4, out) < 1e-2
+    # and one share
+    out5 = torch.full_like(out, float("nan"))
+    kernels.attention_decode(q.to(DEV), out5, kc.to(DEV), vc.to(DEV), table.to(DEV), past.to(DEV), H, G, D, window,
+                             1 / math.sqrt(D), n_chunks=1)
+    assert rel(out5, out) < 1e-2
     assert kernels.attention_decode_status() == 0
 
 
