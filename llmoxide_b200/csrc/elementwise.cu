@@ -117,8 +117,8 @@ add_rms_norm_kernel(float* __restrict__ h, const TD* __restrict__ delta, int n_s
       v[c] = i < d ? load4(hrow + i) : make_float4(0.f, 0.f, 0.f, 0.f);
     }
     if (delta) {
-      // partials of every vector of the thread, eight loads in flight
-      constexpr int J = 8 / NC;
+      // partials of every vector of the thread, about a dozen loads in flight (with the row's own above)
+      constexpr int J = NC == 1 ? 8 : (NC == 2 ? 5 : 2);
       for (int s0 = 0; s0 < n_split; s0 += J) {
         float4 y[NC][J];
 #pragma unroll
