@@ -71,15 +71,15 @@ LLMX_API int llmx_embed(const void* table, int table_dtype, const int* tokens, f
 
 // v += sum_s p[s * stride .. +4), the partials added in the order s = 0..S-1, their loads issued eight at a time
 // (a loop of load-then-add would pay one memory round trip per partial).
-template <typename TD>
+template <int J = 8, typename TD>
 __device__ __forceinline__ void add_partials4(float4& v, const TD* p, int n_split, size_t split_stride) {
-  for (int s0 = 0; s0 < n_split; s0 += 8) {
-    float4 y[8];
+  for (int s0 = 0; s0 < n_split; s0 += J) {
+    float4 y[J];
 #pragma unroll
-    for (int j = 0; j < 8; ++j)
+    for (int j = 0; j < J; ++j)
       if (s0 + j < n_split) y[j] = load4(p + (size_t)(s0 + j) * split_stride);
 #pragma unroll
-    for (int j = 0; j < 8; ++j)
+    for (int j = 0; j < J; ++j)
       if (s0 + j < n_split) {
         v.x += y[j].x; v.y += y[j].y; v.z += y[j].z; v.w += y[j].w;
       }
@@ -87,7 +87,9 @@ __device__ __forceinline__ void add_partials4(float4& v, const TD* p, int n_spli
 }
 
 // CH > 0: the row fits CH vectors per thread.  CH == 0: any width, staged in shared memory.
-template <typename TD, typename TO, int CH>
+// DEEP: many partials and few rows (a decode step): a dozen loads in flight per thread.  Otherwise (one delta,
+// thousands of rows) few registers, so that several CTAs share an SM.
+template <typename TD, typename TO, int CH, bool DEEP>
 __global__ void __launch_bounds__(512)
 add_rms_norm_kernel(float* __restrict__ h, const TD* __restrict__ delta, int n_split, size_t split_stride,
                     const int* __restrict__ rows, const float* __restrict__ gain, float eps, TO* __restrict__ out,
@@ -118,7 +120,7 @@ add_rms_norm_kernel(float* __restrict__ h, const TD* __restrict__ delta, int n_s
     }
     if (delta) {
       // partials of every vector of the thread, about a dozen loads in flight (with the row's own above)
-      constexpr int J = NC == 1 ? 8 : (NC == 2 ? 5 : 2);
+      constexpr int J = !DEEP ? 1 : (NC == 1 ? 8 : (NC == 2 ? 5 : 2));
       for (int s0 = 0; s0 < n_split; s0 += J) {
         float4 y[NC][J];
 #pragma unroll
@@ -171,7 +173,7 @@ add_rms_norm_kernel(float* __restrict__ h, const TD* __restrict__ delta, int n_s
     for (int i = threadIdx.x * 4; i < d; i += nthreads * 4) {
       float4 v = load4(hrow + i);
       if (delta) {
-        add_partials4(v, delta + (size_t)t * d + i, n_split, split_stride);
+        add_partials4<DEEP ? 8 : 1>(v, delta + (size_t)t * d + i, n_split, split_stride);
         if (write_h) store4(hrow + i, v);
       }
       store4(row_buf + i, v);
@@ -218,9 +220,16 @@ static int launch_add_rms_norm(float* h, const void* delta, int n_split, size_t 
                                cudaStream_t stream) {
   int ch, threads;
   norm_shape(d, ch, threads);
+  const bool deep = delta && n_split > 1;
 #define GO(CH, SMEM)                                                                                              \
-  launch_pdl(add_rms_norm_kernel<TD, TO, CH>, dim3(n_rows), dim3(threads), SMEM, stream, h, (const TD*)delta,    \
-             n_split, split_stride, rows, gain, eps, (TO*)out, d, write_h)
+  do {                                                                                                            \
+    if (deep)                                                                                                     \
+      launch_pdl(add_rms_norm_kernel<TD, TO, CH, true>, dim3(n_rows), dim3(threads), SMEM, stream, h,            \
+                 (const TD*)delta, n_split, split_stride, rows, gain, eps, (TO*)out, d, write_h);                \
+    else                                                                                                          \
+      launch_pdl(add_rms_norm_kernel<TD, TO, CH, false>, dim3(n_rows), dim3(threads), SMEM, stream, h,           \
+                 (const TD*)delta, n_split, split_stride, rows, gain, eps, (TO*)out, d, write_h);                \
+  } while (0)
   if (ch == 1) GO(1, 0);
   else if (ch == 2) GO(2, 0);
   else if (ch == 4) GO(4, 0);
@@ -228,8 +237,11 @@ static int launch_add_rms_norm(float* h, const void* delta, int n_split, size_t 
     const size_t smem = (size_t)d * sizeof(float);
     if (smem > 48 * 1024) {
       if (smem > 200 * 1024) return LLMX_REFUSED(3);
-      cudaError_t e = cudaFuncSetAttribute(add_rms_norm_kernel<TD, TO, 0>,
+      cudaError_t e = cudaFuncSetAttribute(add_rms_norm_kernel<TD, TO, 0, true>,
                                            cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+      if (e == cudaSuccess)
+        e = cudaFuncSetAttribute(add_rms_norm_kernel<TD, TO, 0, false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 (int)smem);
       if (e != cudaSuccess) return (int)e;
     }
     GO(0, smem);
@@ -262,7 +274,7 @@ LLMX_API int llmx_add_rms_norm(float* h, const void* delta, int delta_dtype, int
 // ---------------------------------------------------------------------------
 #define QKV_WARPS 4
 
-template <typename TIN, typename TA, typename TC>
+template <typename TIN, typename TA, typename TC, bool DEEP>
 __global__ void qk_norm_rope_cache_kernel(const TIN* __restrict__ qkv, int n_split, size_t split_stride,
                                           TA* __restrict__ q_out,
                                           TC* __restrict__ k_cache, TC* __restrict__ v_cache,
@@ -312,7 +324,7 @@ __global__ void qk_norm_rope_cache_kernel(const TIN* __restrict__ qkv, int n_spl
     }
     pdl_wait();
     float4 x = load4(src + d0);
-    add_partials4(x, src + split_stride + d0, n_split - 1, split_stride);
+    add_partials4<DEEP ? 8 : 1>(x, src + split_stride + d0, n_split - 1, split_stride);
     if (is_v) {  // v: stored as it is
       store4(cache_row + d0, x);
       return;
@@ -382,10 +394,18 @@ LLMX_API int llmx_qk_norm_rope_cache(const void* qkv, int in_dtype, int n_split,
   dim3 grid(n_tokens, (n_slots + QKV_WARPS - 1) / QKV_WARPS);
   const size_t smem = (size_t)QKV_WARPS * D * sizeof(float);
   if (smem > 48 * 1024) return LLMX_REFUSED(3);
+  // many partials (a decode step): their loads batched; one tensor (a prompt): few registers, many warps per SM
 #define CASE(TIN, TA, TC)                                                                                          \
-  launch_pdl(qk_norm_rope_cache_kernel<TIN, TA, TC>, grid, dim3(QKV_WARPS * 32), smem, stream,                     \
-      (const TIN*)qkv, n_split, (size_t)split_stride, (TA*)q_out, (TC*)k_cache, (TC*)v_cache, block_table,          \
-      table_width, token_seq, token_pos, q_gain, k_gain, eps, cos_t, sin_t, n_rot, H, G, D, write_cache)
+  do {                                                                                                             \
+    if (n_split > 2)                                                                                               \
+      launch_pdl(qk_norm_rope_cache_kernel<TIN, TA, TC, true>, grid, dim3(QKV_WARPS * 32), smem, stream,           \
+        (const TIN*)qkv, n_split, (size_t)split_stride, (TA*)q_out, (TC*)k_cache, (TC*)v_cache, block_table,        \
+        table_width, token_seq, token_pos, q_gain, k_gain, eps, cos_t, sin_t, n_rot, H, G, D, write_cache);         \
+    else                                                                                                           \
+      launch_pdl(qk_norm_rope_cache_kernel<TIN, TA, TC, false>, grid, dim3(QKV_WARPS * 32), smem, stream,          \
+        (const TIN*)qkv, n_split, (size_t)split_stride, (TA*)q_out, (TC*)k_cache, (TC*)v_cache, block_table,        \
+        table_width, token_seq, token_pos, q_gain, k_gain, eps, cos_t, sin_t, n_rot, H, G, D, write_cache);         \
+  } while (0)
   const int key = in_dtype * 4 + act_dtype * 2 + cache_dtype;
   switch (key) {
     case 0: CASE(float, float, float); break;
