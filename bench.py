@@ -107,6 +107,69 @@ def model_numbers(cfg, n_layers):
     return weight_bytes, kv_bytes_per_token, prefill_flops
 
 
+def timeline(eng, cfg, args, rng) -> int:
+    """One replayed decode step seen from inside: every kernel's first thread records when it reached its
+    programmatic-launch wait and when the wait returned.  The time from one kernel's return to the next one's is
+    that kernel's share of the step's critical path, measured in place (CUDA graph, overlapping launches)."""
+    import ctypes
+    import re
+    from collections import defaultdict
+
+    import torch
+    from llmoxide_b200.csrc.build import LIBRARIES, SRC_DIR, load_library
+
+    B, V = args.batch, cfg.vocab_size
+    slots = [eng.acquire() for _ in range(B)]
+    for s in slots:
+        eng.step([(s, rng.integers(0, V, args.depth).tolist())], [[]])
+
+    def step():
+        eng.step([(s, [int(rng.integers(0, V))]) for s in slots])
+
+    for _ in range(max(args.warmup, 4)):
+        step()
+    libs = ("elementwise", "gemm_tc", "attention_decode")
+
+    def kernel_at(lib, line):
+        src = (SRC_DIR / LIBRARIES[lib][0][0]).read_text().splitlines()
+        for i in range(line - 1, -1, -1):
+            m = re.search(r"^\s*(\w+_kernel)\(", src[i]) or re.search(r"__global__.*?(\w+_kernel)\(", src[i])
+            if m:
+                return m.group(1)
+        return f"{lib}:{line}"
+
+    def read_all():
+        out = []
+        for lib in libs:
+            fn = load_library(lib).llmx_timeline_read
+            fn.restype = ctypes.c_int
+            buf = (ctypes.c_ulonglong * (3 * 65536))()
+            n = fn(buf, 65536)
+            if n < 0:
+                raise RuntimeError(f"timeline of {lib}: CUDA error {-n}")
+            out += [(buf[3 * i + 2], buf[3 * i + 1], lib, int(buf[3 * i])) for i in range(n) if buf[3 * i] < 1000000]
+        return sorted(out)
+
+    read_all()
+    step()
+    torch.cuda.synchronize()
+    recs = read_all()
+    t0 = recs[0][0]
+    share = defaultdict(list)
+    print(f"{'#':>4} {'kernel':34} {'resident':>10} {'ready':>10} {'to next':>9}   (us)", file=sys.stderr)
+    for i, (ready, reached, lib, line) in enumerate(recs):
+        name = kernel_at(lib, line)
+        nxt = recs[i + 1][0] if i + 1 < len(recs) else ready
+        share[name].append((nxt - ready) / 1e3)
+        print(f"{i:4d} {name:34} {(reached - t0) / 1e3:10.2f} {(ready - t0) / 1e3:10.2f} {(nxt - ready) / 1e3:9.2f}",
+              file=sys.stderr)
+    total = (recs[-1][0] - t0) / 1e3
+    summary = {k: dict(n=len(v), mean_us=round(sum(v) / len(v), 2), sum_us=round(sum(v), 1)) for k, v in share.items()}
+    print(json.dumps(dict(timeline="one decode step", batch=B, depth=args.depth, layers=args.layers,
+                          kernels=len(recs), step_us=round(total, 1), per_kernel=summary)))
+    return 0
+
+
 def main() -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -121,6 +184,9 @@ def main() -> int:
     ap.add_argument("--prefill-tokens", type=int, default=2048)
     ap.add_argument("--no-points", action="store_true", help="skip the batch 1 and batch 64 points")
     ap.add_argument("--no-graphs", action="store_true")
+    ap.add_argument("--timeline", action="store_true",
+                    help="instead of the benchmark: build the kernels with their in-place timers and print, for "
+                         "one replayed decode step, when each kernel's dependency resolved")
     ap.add_argument("--cuda-profiler", choices=["decode", "prefill"], default=None,
                     help="bracket that region with cudaProfilerStart/Stop (for ncu --profile-from-start off)")
     args = ap.parse_args()
@@ -133,6 +199,10 @@ def main() -> int:
     if args.gpus != 1:
         print(json.dumps({"note": f"this library runs on one GPU; --gpus {args.gpus} is not supported", "n_gpus": args.gpus}))
         return 2
+
+    if args.timeline:
+        import os
+        os.environ["LLMX_NVCC_EXTRA"] = (os.environ.get("LLMX_NVCC_EXTRA", "") + " -DLLMX_TIMELINE").strip()
 
     import numpy as np
     import torch
@@ -165,6 +235,9 @@ def main() -> int:
         b.record()
         torch.cuda.synchronize()
         return a.elapsed_time(b)
+
+    if args.timeline:
+        return timeline(eng, cfg, args, rng)
 
     # ---- prefill: one prompt of 2,048 tokens ----------------------------------
     T = args.prefill_tokens

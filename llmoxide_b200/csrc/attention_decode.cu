@@ -125,7 +125,6 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
   pdl_launch_dependents();
 
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  if (threadIdx.x == 0) LLMX_MARK(1);
   const int gq = lane >> 2, tq = lane & 3;                        // the MMA fragments' row group and column pair
   const int chunk = blockIdx.x, b = blockIdx.z;
   const int R = H / G;
@@ -197,7 +196,6 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
   for (; issued < DEC_STAGES - 1 && issued < n_tiles && tile_lo + issued < t_last; ++issued)
     load_tile(tile_lo + issued, issued);
   pdl_wait();
-  if (threadIdx.x == 0) LLMX_MARK(2);
 
   if (n_tiles > 0) {
     for (; issued < DEC_STAGES - 1 && issued < n_tiles; ++issued) load_tile(tile_lo + issued, issued);
@@ -222,7 +220,6 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
       }
       ok = mbar_wait(bars + 8 * stage, (t / DEC_STAGES) & 1);
       if (!ok) break;
-      if (threadIdx.x == 0 && t == 0) LLMX_MARK(3);
       const uint32_t sK = sKV + stage * 2 * S::TILE, sV = sK + S::TILE;
       const int key0 = (tile_lo + t) * DEC_TILE;
       if (key0 + DEC_TILE - 1 > p) {
@@ -309,7 +306,6 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
       }
       __syncwarp();   // the stage is refilled by the next iteration's copies
     }
-    if (threadIdx.x == 0) LLMX_MARK(4);
     if (!ok && lane == 0) atomicExch(&g_dec_status, 1);
     if (!S::TMA) asm volatile("cp.async.wait_all;" ::: "memory");
 #pragma unroll
@@ -441,7 +437,6 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
     if (s_last) *ctr = 0u;                 // every CTA of the group has arrived: ready for the next launch
   }
   __syncthreads();
-  if (threadIdx.x == 0) LLMX_MARK(5);
   if (!s_last) return;
   // per (head, chunk): the factor 2^(m_c - m), and per head 1 / sum_c factor * l_c  (in the pipeline buffers, free now)
   float* fac = reinterpret_cast<float*>(smem);                   // [DEC_ROWS][DEC_MAX_CHUNKS]
@@ -489,7 +484,6 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
     uint2 packed = make_uint2(*reinterpret_cast<uint32_t*>(&lo), *reinterpret_cast<uint32_t*>(&hi));
     *reinterpret_cast<uint2*>(out + ((size_t)b * H + h0 + h) * D + d) = packed;
   }
-  if (threadIdx.x == 0) LLMX_MARK(6);
 }
 
 template <int D>
