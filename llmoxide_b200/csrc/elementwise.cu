@@ -39,6 +39,12 @@ __global__ void embed_kernel(const TW* __restrict__ table, const int* __restrict
   tok = tok < 0 ? 0 : (tok >= vocab ? vocab - 1 : tok);  // never read outside the table
   const TW* row = table + (size_t)tok * d;
   float* out = h + (size_t)t * d;
+  if ((d & 3) == 0) {
+    // four elements per load, four loads in flight per thread: the row is cold in DRAM
+#pragma unroll 4
+    for (int i = threadIdx.x * 4; i < d; i += blockDim.x * 4) store4(out + i, load4(row + i));
+    return;
+  }
   for (int i = threadIdx.x; i < d; i += blockDim.x) out[i] = to_f32(row[i]);
 }
 
@@ -274,6 +280,11 @@ LLMX_API int llmx_add_rms_norm(float* h, const void* delta, int delta_dtype, int
 // ---------------------------------------------------------------------------
 #define QKV_WARPS 4
 
+// DEEP: a decode step (few tokens, split partials): one head per warp, the partials' loads batched.  Otherwise
+// (a prompt): a warp takes QKV_SPW heads of its token one after another, so that the token's position, block
+// table entry, gains and rotation rows are fetched once for all of them, and their loads go out together.
+#define QKV_SPW 4
+
 template <typename TIN, typename TA, typename TC, bool DEEP>
 __global__ void qk_norm_rope_cache_kernel(const TIN* __restrict__ qkv, int n_split, size_t split_stride,
                                           TA* __restrict__ q_out,
@@ -284,100 +295,120 @@ __global__ void qk_norm_rope_cache_kernel(const TIN* __restrict__ qkv, int n_spl
                                           float eps, const float* __restrict__ cos_t,
                                           const float* __restrict__ sin_t, int n_rot, int H, int G, int D,
                                           int write_cache) {
+  constexpr int SPW = DEEP ? 1 : QKV_SPW;
   extern __shared__ float head_buf[];
   pdl_launch_dependents();
   // Positions, block table, gains and rotation tables are step inputs or weights, not results of the kernel
   // before: they are fetched ahead of the dependency wait, which only the qkv values need.
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int t = blockIdx.x;                        // tokens on x: a step may bring more than 65535
-  const int slot = blockIdx.y * QKV_WARPS + warp;  // which head of the fused row
+  const int slot0 = (blockIdx.y * QKV_WARPS + warp) * SPW;   // the warp's first head of the fused row
   const int n_slots = write_cache ? H + 2 * G : H;
-  if (slot >= n_slots) return;
+  if (slot0 >= n_slots) return;
   float* buf = head_buf + warp * D;
-  const TIN* src = qkv + (size_t)t * (H + 2 * G) * D + (size_t)slot * D;
+  const TIN* tok = qkv + (size_t)t * (H + 2 * G) * D;
   const int pos = token_pos[t];
-  // the head's values: one tensor, or split partials added in order
-  auto value = [&](int i) {
-    float v = to_f32(src[i]);
-    for (int s = 1; s < n_split; ++s) v += to_f32(src[s * split_stride + i]);
-    return v;
+  int page = 0;
+  if (slot0 + SPW > H) page = block_table[(size_t)token_seq[t] * table_width + pos / LLMX_PAGE];
+  auto cache_row_of = [&](int slot) -> TC* {        // slot >= H: a k head, then the v heads
+    const bool is_k = slot < H + G;
+    return (is_k ? k_cache : v_cache) + cache_row_offset(page, is_k ? slot - H : slot - H - G, pos % LLMX_PAGE, G, D);
   };
-  const bool is_q = slot < H, is_k = !is_q && slot < H + G;
 
-  TC* cache_row = nullptr;
-  if (!is_q) {
-    const int g = is_k ? slot - H : slot - H - G;
-    const int page = block_table[(size_t)token_seq[t] * table_width + pos / LLMX_PAGE];
-    cache_row = (is_k ? k_cache : v_cache) + cache_row_offset(page, g, pos % LLMX_PAGE, G, D);
-  }
-  const float* gain = is_q ? q_gain : k_gain;
-  if (D == 128 && (n_rot == 128 || (!is_q && !is_k))) {
+  if (D == 128 && n_rot == 128) {
     // Head size 128 with full rotation: a lane owns dims 4*lane..4*lane+3, read and written as one
     // vector; the rotation partner (dim +-64) lives in lane +-16 and comes by shuffle.
     const int d0 = 4 * lane;
-    const bool is_v = !is_q && !is_k;
-    float4 gn = make_float4(1.f, 1.f, 1.f, 1.f), cs = gn, sn = gn;
-    if (!is_v) {
-      if (gain) gn = load4(gain + d0);
-      cs = load4(cos_t + (size_t)pos * 64 + (d0 & 63));
-      sn = load4(sin_t + (size_t)pos * 64 + (d0 & 63));
-    }
+    const float4 one = make_float4(1.f, 1.f, 1.f, 1.f);
+    const float4 gq = q_gain ? load4(q_gain + d0) : one, gk = k_gain ? load4(k_gain + d0) : one;
+    const float4 cs = load4(cos_t + (size_t)pos * 64 + (d0 & 63)), sn = load4(sin_t + (size_t)pos * 64 + (d0 & 63));
     pdl_wait();
-    float4 x = load4(src + d0);
-    add_partials4<DEEP ? 8 : 1>(x, src + split_stride + d0, n_split - 1, split_stride);
-    if (is_v) {  // v: stored as it is
-      store4(cache_row + d0, x);
-      return;
+    float4 xs[SPW];
+#pragma unroll
+    for (int j = 0; j < SPW; ++j) {
+      if (slot0 + j < n_slots) {
+        const TIN* src = tok + (size_t)(slot0 + j) * D;
+        xs[j] = load4(src + d0);
+        add_partials4<DEEP ? 8 : 1>(xs[j], src + split_stride + d0, n_split - 1, split_stride);
+      }
+    }
+#pragma unroll
+    for (int j = 0; j < SPW; ++j) {
+      const int slot = slot0 + j;
+      if (slot >= n_slots) break;
+      float4 x = xs[j];
+      const bool is_q = slot < H, is_k = !is_q && slot < H + G;
+      if (!is_q && !is_k) {  // v: stored as it is
+        store4(cache_row_of(slot) + d0, x);
+        continue;
+      }
+      if (is_q ? q_gain != nullptr : k_gain != nullptr) {
+        const float4 gn = is_q ? gq : gk;
+        const float ssq = warp_sum(x.x * x.x + x.y * x.y + x.z * x.z + x.w * x.w);
+        const float scale = 1.0f / sqrtf(ssq / 128.0f + eps);
+        x.x = (x.x * scale) * gn.x; x.y = (x.y * scale) * gn.y; x.z = (x.z * scale) * gn.z; x.w = (x.w * scale) * gn.w;
+      }
+      float4 p;
+      p.x = __shfl_xor_sync(0xffffffffu, x.x, 16);
+      p.y = __shfl_xor_sync(0xffffffffu, x.y, 16);
+      p.z = __shfl_xor_sync(0xffffffffu, x.z, 16);
+      p.w = __shfl_xor_sync(0xffffffffu, x.w, 16);
+      float4 r;
+      if (lane < 16) {   // dims i < 64: x_i cos - x_{i+64} sin
+        r = make_float4(x.x * cs.x - p.x * sn.x, x.y * cs.y - p.y * sn.y, x.z * cs.z - p.z * sn.z, x.w * cs.w - p.w * sn.w);
+      } else {           // dims i + 64: x_i sin + x_{i+64} cos
+        r = make_float4(p.x * sn.x + x.x * cs.x, p.y * sn.y + x.y * cs.y, p.z * sn.z + x.z * cs.z, p.w * sn.w + x.w * cs.w);
+      }
+      if (is_q) store4(q_out + (size_t)t * H * D + (size_t)slot * D + d0, r);
+      else store4(cache_row_of(slot) + d0, r);
+    }
+    return;
+  }
+
+  pdl_wait();
+  for (int j = 0; j < SPW; ++j) {
+    const int slot = slot0 + j;
+    if (slot >= n_slots) break;
+    const TIN* src = tok + (size_t)slot * D;
+    // the head's values: one tensor, or split partials added in order
+    auto value = [&](int i) {
+      float v = to_f32(src[i]);
+      for (int s = 1; s < n_split; ++s) v += to_f32(src[s * split_stride + i]);
+      return v;
+    };
+    const bool is_q = slot < H, is_k = !is_q && slot < H + G;
+    TC* cache_row = is_q ? nullptr : cache_row_of(slot);
+    if (!is_q && !is_k) {  // v: stored as it is
+      for (int i = lane; i < D; i += 32) cache_row[i] = from_f32<TC>(value(i));
+      continue;
+    }
+    const float* gain = is_q ? q_gain : k_gain;
+    float ss = 0.f;
+    for (int i = lane; i < D; i += 32) {
+      const float v = value(i);
+      buf[i] = v;
+      ss += v * v;
     }
     if (gain) {
-      const float ssq = warp_sum(x.x * x.x + x.y * x.y + x.z * x.z + x.w * x.w);
-      const float scale = 1.0f / sqrtf(ssq / 128.0f + eps);
-      x.x = (x.x * scale) * gn.x; x.y = (x.y * scale) * gn.y; x.z = (x.z * scale) * gn.z; x.w = (x.w * scale) * gn.w;
+      const float scale = 1.0f / sqrtf(warp_sum(ss) / (float)D + eps);
+      for (int i = lane; i < D; i += 32) buf[i] = (buf[i] * scale) * gain[i];
     }
-    float4 p;
-    p.x = __shfl_xor_sync(0xffffffffu, x.x, 16);
-    p.y = __shfl_xor_sync(0xffffffffu, x.y, 16);
-    p.z = __shfl_xor_sync(0xffffffffu, x.z, 16);
-    p.w = __shfl_xor_sync(0xffffffffu, x.w, 16);
-    float4 r;
-    if (lane < 16) {   // dims i < 64: x_i cos - x_{i+64} sin
-      r = make_float4(x.x * cs.x - p.x * sn.x, x.y * cs.y - p.y * sn.y, x.z * cs.z - p.z * sn.z, x.w * cs.w - p.w * sn.w);
-    } else {           // dims i + 64: x_i sin + x_{i+64} cos
-      r = make_float4(p.x * sn.x + x.x * cs.x, p.y * sn.y + x.y * cs.y, p.z * sn.z + x.z * cs.z, p.w * sn.w + x.w * cs.w);
+    __syncwarp();
+    const int half = n_rot >> 1;
+    const float* c = cos_t ? cos_t + (size_t)pos * half : nullptr;
+    const float* sv = sin_t ? sin_t + (size_t)pos * half : nullptr;
+    TA* qrow = is_q ? q_out + (size_t)t * H * D + (size_t)slot * D : nullptr;
+    for (int i = lane; i < D; i += 32) {
+      float v = buf[i];
+      if (i < half) {
+        v = buf[i] * c[i] - buf[i + half] * sv[i];
+      } else if (i < n_rot) {
+        v = buf[i - half] * sv[i - half] + buf[i] * c[i - half];
+      }
+      if (is_q) qrow[i] = from_f32<TA>(v);
+      else cache_row[i] = from_f32<TC>(v);
     }
-    if (is_q) store4(q_out + (size_t)t * H * D + (size_t)slot * D + d0, r);
-    else store4(cache_row + d0, r);
-    return;
-  }
-  pdl_wait();
-  if (!is_q && !is_k) {  // v: stored as it is
-    for (int i = lane; i < D; i += 32) cache_row[i] = from_f32<TC>(value(i));
-    return;
-  }
-  float ss = 0.f;
-  for (int i = lane; i < D; i += 32) {
-    const float v = value(i);
-    buf[i] = v;
-    ss += v * v;
-  }
-  if (gain) {
-    const float scale = 1.0f / sqrtf(warp_sum(ss) / (float)D + eps);
-    for (int i = lane; i < D; i += 32) buf[i] = (buf[i] * scale) * gain[i];
-  }
-  __syncwarp();
-  const int half = n_rot >> 1;
-  const float* c = cos_t ? cos_t + (size_t)pos * half : nullptr;
-  const float* s = sin_t ? sin_t + (size_t)pos * half : nullptr;
-  TA* qrow = is_q ? q_out + (size_t)t * H * D + (size_t)slot * D : nullptr;
-  for (int i = lane; i < D; i += 32) {
-    float v = buf[i];
-    if (i < half) {
-      v = buf[i] * c[i] - buf[i + half] * s[i];
-    } else if (i < n_rot) {
-      v = buf[i - half] * s[i - half] + buf[i] * c[i - half];
-    }
-    if (is_q) qrow[i] = from_f32<TA>(v);
-    else cache_row[i] = from_f32<TC>(v);
+    __syncwarp();   // buf is filled again for the warp's next head
   }
 }
 
@@ -391,13 +422,15 @@ LLMX_API int llmx_qk_norm_rope_cache(const void* qkv, int in_dtype, int n_split,
   if (H <= 0 || G <= 0 || D <= 0 || n_rot < 0 || n_rot > D || (n_rot & 1) || n_split < 1) return LLMX_REFUSED(1);
   if (n_rot > 0 && (!cos_t || !sin_t)) return LLMX_REFUSED(4);
   const int n_slots = write_cache ? H + 2 * G : H;
-  dim3 grid(n_tokens, (n_slots + QKV_WARPS - 1) / QKV_WARPS);
+  const bool deep = n_split > 2;
+  const int per_cta = QKV_WARPS * (deep ? 1 : QKV_SPW);
+  dim3 grid(n_tokens, (n_slots + per_cta - 1) / per_cta);
   const size_t smem = (size_t)QKV_WARPS * D * sizeof(float);
   if (smem > 48 * 1024) return LLMX_REFUSED(3);
   // many partials (a decode step): their loads batched; one tensor (a prompt): few registers, many warps per SM
 #define CASE(TIN, TA, TC)                                                                                          \
   do {                                                                                                             \
-    if (n_split > 2)                                                                                               \
+    if (deep)                                                                                                      \
       launch_pdl(qk_norm_rope_cache_kernel<TIN, TA, TC, true>, grid, dim3(QKV_WARPS * 32), smem, stream,           \
         (const TIN*)qkv, n_split, (size_t)split_stride, (TA*)q_out, (TC*)k_cache, (TC*)v_cache, block_table,        \
         table_width, token_seq, token_pos, q_gain, k_gain, eps, cos_t, sin_t, n_rot, H, G, D, write_cache);         \
