@@ -71,10 +71,11 @@ attention_prefill_kernel(const bf16* __restrict__ q, bf16* __restrict__ out, con
   pdl_launch_dependents();
   pdl_wait();
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-  const int b = blockIdx.z, hq = blockIdx.y;
+  // heads fastest in launch order, query tiles from the last (longest) down: the tail is made of short tiles
+  const int b = blockIdx.z, hq = blockIdx.x;
   const int g = hq / (H / G);
   const int tok0 = seq_start[b], n_new = seq_start[b + 1] - tok0;
-  const int i0 = blockIdx.x * PF_BQ;
+  const int i0 = (gridDim.y - 1 - blockIdx.y) * PF_BQ;
   if (i0 >= n_new) return;
   const int past = seq_past[b];
   const int rows_here = min(PF_BQ, n_new - i0);
@@ -256,7 +257,7 @@ static int launch_prefill(const void* q, void* out, const void* k_cache, const v
     if (e != cudaSuccess) return (int)e;
     attr_set = true;
   }
-  dim3 grid((max_new + PF_BQ - 1) / PF_BQ, H, B);
+  dim3 grid(H, (max_new + PF_BQ - 1) / PF_BQ, B);
   launch_pdl(kernel, grid, dim3(PF_THREADS), smem, stream, (const bf16*)q, (bf16*)out, (const bf16*)k_cache, (const bf16*)v_cache,
                                              block_table, table_width, seq_start, seq_past, H, G, window,
                                              scale * 1.4426950408889634f);
@@ -271,7 +272,9 @@ LLMX_API int llmx_attention_prefill(const void* q, void* out, const void* k_cach
                                     const int* seq_past, int B, int max_new, int H, int G, int D, int window,
                                     float scale, cudaStream_t stream) {
   if (B <= 0 || max_new <= 0) return 0;
-  if (H <= 0 || G <= 0 || H % G || window < 0 || B > 65535 || H > 65535) return LLMX_REFUSED(1);
+  if (H <= 0 || G <= 0 || H % G || window < 0 || B > 65535 ||
+      (max_new + PF_BQ - 1) / PF_BQ > 65535)
+    return LLMX_REFUSED(1);
   if (D == 128)
     return launch_prefill<128>(q, out, k_cache, v_cache, block_table, table_width, seq_start, seq_past, B, max_new,
                                H, G, window, scale, stream);

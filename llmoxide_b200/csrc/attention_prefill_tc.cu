@@ -7,40 +7,46 @@
 // before this runs (cpu.rs:314-323).
 //
 // A CTA owns 128 consecutive query tokens of one head (row = lane of tensor
-// memory) and walks the visible keys 128 at a time (two cache pages):
+// memory) and walks the visible keys 64 at a time (one cache page):
 //   warp 0     TMA: the query tile once, then per key tile K and V, each as
-//              [2 panels of 64 dims][128 keys][128 bytes], 128-byte swizzle
+//              [2 panels of 64 dims][64 keys][128 bytes], 128-byte swizzle
 //   warp 1     one lane issues  S = Q K^T  (both operands K-major) into one of
 //              two S buffers in tensor memory, and  O += P V  (P K-major from
 //              shared memory, V MN-major straight from its cache layout)
 //   warps 2-5  softmax, one thread per query row: tcgen05.ld the row of S,
 //              mask, running maximum, exp2, row sum, P as bfloat16 into shared
-//              memory in the MMA's swizzled layout (two P buffers).  O stays in tensor memory;
+//              memory in the MMA's swizzled layout.  O stays in tensor memory;
 //              it is rescaled (load, multiply, store) only when a row's maximum
 //              has grown by more than 2^8 since the maximum its exponentials
 //              were taken against, which is rare after the first tiles.
 // S of tile j+1 is issued before P V of tile j, so the tensor core works on the
-// next scores while the softmax warps work on these.  Every mbarrier wait is
+// next scores while the softmax warps work on these.  A CTA takes half of an
+// SM (112 KB of shared memory, 256 columns of tensor memory, 168 registers),
+// so two CTAs share it: while one's softmax warps wait for a tensor-memory load
+// or the special-function unit, the other's run.  Every mbarrier wait is
 // bounded; a wait that runs out sets the status word and the CTA winds down.
 #include "tc_ptx.cuh"
 
 #define AT_ROWS 128        // query rows per CTA = MMA M
-#define AT_KEYS 128        // keys per tile = MMA N of S = two cache pages
+#define AT_KEYS 64         // keys per tile = MMA N of S = one cache page
 #define AT_D 128
 #define AT_THREADS 192        // warp 0 TMA, warp 1 MMA, warps 2..5 softmax
-#define AT_PANEL (128 * 128)   // bytes of one [128 rows x 64 elements] panel
-#define AT_TILE (2 * AT_PANEL) // bytes of a [128 x 128] bf16 tile
+#define AT_PANEL (128 * 128)   // bytes of one [128 rows x 64 elements] panel (Q, P)
+#define AT_TILE (2 * AT_PANEL) // bytes of the [128 x 128] query tile
+#define AT_KPANEL (AT_KEYS * 128)   // bytes of one [64 keys x 64 dims] panel of K or V
+#define AT_KTILE (2 * AT_KPANEL)    // bytes of a [64 keys x 128 dims] tile of K or V
+#define AT_SMEM (AT_TILE + 4 * AT_KTILE + AT_PANEL + 16 * 8 + 64)   // Q, K[2], V[2], P, barriers
 
 __device__ int g_at_status = 0;
 
 
-// instruction descriptors: bf16 x bf16 -> f32, M = 128, N = 128
-__host__ __device__ constexpr uint32_t at_idesc(bool b_mn_major) {
-  return (1u << 4) | (1u << 7) | (1u << 10) | ((b_mn_major ? 1u : 0u) << 16) | ((uint32_t)(128 >> 3) << 17) |
+// instruction descriptors: bf16 x bf16 -> f32, M = 128
+__host__ __device__ constexpr uint32_t at_idesc(bool b_mn_major, uint32_t n) {
+  return (1u << 4) | (1u << 7) | (1u << 10) | ((b_mn_major ? 1u : 0u) << 16) | ((n >> 3) << 17) |
          ((uint32_t)(128 >> 4) << 24);
 }
 
-__global__ void __launch_bounds__(AT_THREADS)
+__global__ void __launch_bounds__(AT_THREADS, 2)
 attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                             const __grid_constant__ CUtensorMap map_v, bf16* __restrict__ out,
                             const int* __restrict__ block_table, int table_width, const int* __restrict__ seq_start,
@@ -49,10 +55,12 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
   pdl_launch_dependents();
   pdl_wait();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int b = blockIdx.z, hq = blockIdx.y;
+  // Heads run fastest in launch order and query tiles from the last one down: every head's longest tile starts
+  // before any shorter one, so the work left at the end is made of short tiles.
+  const int b = blockIdx.z, hq = blockIdx.x;
   const int g = hq / (H / G);
   const int tok0 = seq_start[b], n_new = seq_start[b + 1] - tok0;
-  const int i0 = (gridDim.x - 1 - blockIdx.x) * AT_ROWS;    // the longest (latest) query tiles are launched first
+  const int i0 = (gridDim.y - 1 - blockIdx.y) * AT_ROWS;
   if (i0 >= n_new) return;                                   // uniform over the CTA, before anything is set up
   const int past = seq_past[b];
   const int rows_here = min(AT_ROWS, n_new - i0);
@@ -63,8 +71,8 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
   const int last_page = pos_hi / LLMX_PAGE;                  // pages past this one are never read
   const int* pages = block_table + (size_t)b * table_width;
 
-  // shared memory: Q, K[2], V[2], P[2] (each a 32 KB tile), then barriers
-  // Seven 32 KB tiles leave no room for alignment slack: the dynamic shared memory must start on a
+  // shared memory: Q (32 KB), K[2], V[2] (16 KB each), P (16 KB), then barriers
+  // Half an SM leaves no room for alignment slack: the dynamic shared memory must start on a
   // 1024-byte boundary (it does when the kernel has no static shared memory); otherwise nothing runs.
   const uint32_t base = smem_u32(smem_raw);
   if (base & 1023u) {
@@ -72,13 +80,13 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
     return;
   }
   uint8_t* base_ptr = smem_raw;
-  const uint32_t sQ = base, sK0 = base + AT_TILE, sV0 = base + 3 * AT_TILE, sP = base + 5 * AT_TILE;
-  uint8_t* pP = base_ptr + 5 * AT_TILE;
-  uint8_t* pV0 = base_ptr + 3 * AT_TILE;
-  uint64_t* bars = reinterpret_cast<uint64_t*>(base_ptr + 7 * AT_TILE);
+  const uint32_t sQ = base, sK0 = base + AT_TILE, sV0 = sK0 + 2 * AT_KTILE, sP = sV0 + 2 * AT_KTILE;
+  uint8_t* pV0 = base_ptr + AT_TILE + 2 * AT_KTILE;
+  uint8_t* pP = pV0 + 2 * AT_KTILE;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(pP + AT_PANEL);
   const uint32_t bar0 = smem_u32(bars);
   const uint32_t q_full = bar0, k_full0 = bar0 + 8, v_full0 = bar0 + 24, k_empty0 = bar0 + 40, v_empty0 = bar0 + 56;
-  const uint32_t s_full0 = bar0 + 72, p_ready0 = bar0 + 88, pv_done0 = bar0 + 104;   // pv_done[tile & 1]
+  const uint32_t s_full0 = bar0 + 72, p_ready = bar0 + 88, pv_done = bar0 + 96;     // one phase per key tile
   uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(bars + 15);
 
   if (threadIdx.x == 0) {
@@ -89,10 +97,9 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
       mbar_init(k_empty0 + 8u * i, 1);
       mbar_init(v_empty0 + 8u * i, 1);
       mbar_init(s_full0 + 8u * i, 1);
-      mbar_init(p_ready0 + 8u * i, 4);       // one arrival per softmax warp
     }
-    mbar_init(pv_done0, 1);
-    mbar_init(pv_done0 + 8u, 1);
+    mbar_init(p_ready, 4);                   // one arrival per softmax warp
+    mbar_init(pv_done, 1);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("prefetch.tensormap [%0];" ::"l"(&map_q) : "memory");
     asm volatile("prefetch.tensormap [%0];" ::"l"(&map_k) : "memory");
@@ -100,20 +107,15 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
   }
   if (warp == 1) {
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_holder)),
-                 "r"(512u)
+                 "r"(256u)
                  : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
   }
-  // The value tiles start as zeros: a half tile whose page does not exist is never loaded, and its rows
-  // are multiplied by probabilities that are exactly 0, so they must at least be finite.
-  for (int i = threadIdx.x; i < 2 * AT_TILE / 16; i += AT_THREADS)
-    reinterpret_cast<uint4*>(pV0)[i] = make_uint4(0u, 0u, 0u, 0u);
-  fence_proxy_async();
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_holder;
-  const uint32_t tS0 = tmem_base, tO = tmem_base + 256;      // S buffers at columns 0 and 128, O at 256
+  const uint32_t tS0 = tmem_base, tO = tmem_base + 2 * AT_KEYS;   // S buffers at columns 0 and 64, O at 128
 
   if (warp == 0) {
     // ---------------- TMA producer ----------------
@@ -124,58 +126,49 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
       for (int j = 0; j < n_tiles; ++j) {
         const int st = j & 1;
         const uint32_t parity = ((j >> 1) & 1) ^ 1;
-        const int lp0 = (tile_first + j) * 2;                 // the tile's two logical pages
-        const int n_pages = (lp0 + 1 <= last_page) ? 2 : 1;
-        const uint32_t bytes = (uint32_t)n_pages * 2u * 64u * 128u;
+        const int row = (pages[tile_first + j] * G + g) * LLMX_PAGE;      // the tile is one page of one kv head
         if (!mbar_wait(k_empty0 + 8u * st, parity)) { atomicExch(&g_at_status, 1); break; }
-        mbar_expect_tx(k_full0 + 8u * st, bytes);
-        for (int h = 0; h < n_pages; ++h) {
-          const int row = (pages[lp0 + h] * G + g) * LLMX_PAGE;
-          const uint32_t dst = sK0 + (uint32_t)st * AT_TILE + (uint32_t)h * 8192u;
-          tma_load_2d(dst, &map_k, 0, row, k_full0 + 8u * st);
-          tma_load_2d(dst + AT_PANEL, &map_k, 64, row, k_full0 + 8u * st);
-        }
+        mbar_expect_tx(k_full0 + 8u * st, AT_KTILE);
+        tma_load_2d(sK0 + (uint32_t)st * AT_KTILE, &map_k, 0, row, k_full0 + 8u * st);
+        tma_load_2d(sK0 + (uint32_t)st * AT_KTILE + AT_KPANEL, &map_k, 64, row, k_full0 + 8u * st);
         if (!mbar_wait(v_empty0 + 8u * st, parity)) { atomicExch(&g_at_status, 2); break; }
-        mbar_expect_tx(v_full0 + 8u * st, bytes);
-        for (int h = 0; h < n_pages; ++h) {
-          const int row = (pages[lp0 + h] * G + g) * LLMX_PAGE;
-          const uint32_t dst = sV0 + (uint32_t)st * AT_TILE + (uint32_t)h * 8192u;
-          tma_load_2d(dst, &map_v, 0, row, v_full0 + 8u * st);
-          tma_load_2d(dst + AT_PANEL, &map_v, 64, row, v_full0 + 8u * st);
-        }
+        mbar_expect_tx(v_full0 + 8u * st, AT_KTILE);
+        tma_load_2d(sV0 + (uint32_t)st * AT_KTILE, &map_v, 0, row, v_full0 + 8u * st);
+        tma_load_2d(sV0 + (uint32_t)st * AT_KTILE + AT_KPANEL, &map_v, 64, row, v_full0 + 8u * st);
       }
     }
   } else if (warp == 1) {
     // ---------------- MMA issuer ----------------
     if (lane == 0) {
-      constexpr uint32_t idesc_s = at_idesc(false), idesc_o = at_idesc(true);
+      constexpr uint32_t idesc_s = at_idesc(false, AT_KEYS), idesc_o = at_idesc(true, AT_D);
       bool ok = mbar_wait(q_full, 0);
       if (!ok) atomicExch(&g_at_status, 3);
       auto issue_pv = [&](int j) {       // O += P_j V_j
         const int st = j & 1;
-        if (!mbar_wait(p_ready0 + 8u * st, (j >> 1) & 1)) { atomicExch(&g_at_status, 5); return false; }
+        if (!mbar_wait(p_ready, j & 1)) { atomicExch(&g_at_status, 5); return false; }
         if (!mbar_wait(v_full0 + 8u * st, (j >> 1) & 1)) { atomicExch(&g_at_status, 6); return false; }
         tc_fence_after();
-        const uint32_t v = sV0 + (uint32_t)st * AT_TILE;
+        const uint32_t v = sV0 + (uint32_t)st * AT_KTILE;
 #pragma unroll
         for (int ks = 0; ks < AT_KEYS / 16; ++ks) {
-          const uint64_t da = umma_desc(sP + (uint32_t)st * AT_TILE + (uint32_t)(ks >> 2) * AT_PANEL + (uint32_t)(ks & 3) * 32u);
-          const uint64_t db = umma_desc_mn(v + (uint32_t)ks * 2048u, AT_PANEL, 1024u);
+          const uint64_t da = umma_desc(sP + (uint32_t)ks * 32u);
+          const uint64_t db = umma_desc_mn(v + (uint32_t)ks * 2048u, AT_KPANEL, 1024u);
           umma_bf16(tO, da, db, idesc_o, (j > 0 || ks > 0) ? 1u : 0u);
         }
         umma_commit(v_empty0 + 8u * st);
-        umma_commit(pv_done0 + 8u * st);
+        umma_commit(pv_done);
         return true;
       };
       for (int j = 0; j < n_tiles && ok; ++j) {
         const int st = j & 1;
         if (!mbar_wait(k_full0 + 8u * st, (j >> 1) & 1)) { atomicExch(&g_at_status, 4); ok = false; break; }
         tc_fence_after();
-        const uint32_t k = sK0 + (uint32_t)st * AT_TILE;
+        const uint32_t k = sK0 + (uint32_t)st * AT_KTILE;
 #pragma unroll
         for (int ks = 0; ks < AT_D / 16; ++ks) {
-          const uint32_t off = (uint32_t)(ks >> 2) * AT_PANEL + (uint32_t)(ks & 3) * 32u;
-          umma_bf16(tS0 + (uint32_t)st * 128u, umma_desc(sQ + off), umma_desc(k + off), idesc_s, ks > 0 ? 1u : 0u);
+          const uint32_t qoff = (uint32_t)(ks >> 2) * AT_PANEL + (uint32_t)(ks & 3) * 32u;
+          const uint32_t koff = (uint32_t)(ks >> 2) * AT_KPANEL + (uint32_t)(ks & 3) * 32u;
+          umma_bf16(tS0 + (uint32_t)st * AT_KEYS, umma_desc(sQ + qoff), umma_desc(k + koff), idesc_s, ks > 0 ? 1u : 0u);
         }
         umma_commit(k_empty0 + 8u * st);
         umma_commit(s_full0 + 8u * st);
@@ -201,7 +194,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
       ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
       if (!ok) break;
       tc_fence_after();
-      const uint32_t tS = tS0 + (uint32_t)st * 128u + lane_off;
+      const uint32_t tS = tS0 + (uint32_t)st * AT_KEYS + lane_off;
       const int key0 = (tile_first + j) * AT_KEYS;
       // the row of S: four loads in flight, one wait
       uint32_t sr[AT_KEYS];
@@ -234,50 +227,48 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
         alpha = (m_used == -INFINITY) ? 0.0f : exp2f(m_used - mt);
         m_used = mt;
       }
-      // This tile's P buffer was last read by P V of two tiles ago.
-      if (j >= 2) {
-        ok = mbar_wait(pv_done0 + 8u * st, ((j - 2) >> 1) & 1);
-        if (!ok && lane == 0) atomicExch(&g_at_status, 8);
-        ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
-        if (!ok) break;
-      }
-      // O is rescaled only when some row of the warp needs it, and then P V of the tile before must be at rest.
-      if (j >= 1 && __any_sync(0xffffffffu, alpha != 1.0f)) {
-        ok = mbar_wait(pv_done0 + 8u * (st ^ 1), ((j - 1) >> 1) & 1);
-        if (!ok && lane == 0) atomicExch(&g_at_status, 11);
-        ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
-        if (!ok) break;
-        tc_fence_after();
-#pragma unroll 1
-        for (int c = 0; c < AT_D; c += 32) {
-          float o[32];
-          tmem_ld32(tO + lane_off + (uint32_t)c, o);
-#pragma unroll
-          for (int e = 0; e < 32; ++e) o[e] *= alpha;
-          tmem_st32(tO + lane_off + (uint32_t)c, o);
-        }
-      }
       l *= alpha;
       // probabilities (a masked score is -inf and gives exactly 0), their sum, and P as bfloat16 in the
       // MMA's layout: [panel = key / 64][row][128 bytes], 16-byte chunk index XOR (row % 8)
       const float neg_ref = (m_used == -INFINITY) ? 0.f : -m_used;
       float sum4[4] = {0.f, 0.f, 0.f, 0.f};
+      uint32_t packed[AT_KEYS / 2];
 #pragma unroll
-      for (int c8 = 0; c8 < AT_KEYS / 8; ++c8) {
-        uint32_t packed[4];
-#pragma unroll
-        for (int h2 = 0; h2 < 4; ++h2) {
-          const float p0 = ex2_approx(fmaf(__uint_as_float(sr[8 * c8 + 2 * h2]), scale_log2, neg_ref));
-          const float p1 = ex2_approx(fmaf(__uint_as_float(sr[8 * c8 + 2 * h2 + 1]), scale_log2, neg_ref));
-          sum4[h2] += p0 + p1;
-          __nv_bfloat162 hh = __floats2bfloat162_rn(p0, p1);
-          packed[h2] = *reinterpret_cast<uint32_t*>(&hh);
-        }
-        uint8_t* prow = pP + st * AT_TILE + (c8 >> 3) * AT_PANEL + row * 128;
-        *reinterpret_cast<uint4*>(prow + (((c8 & 7) ^ (row & 7)) << 4)) =
-            make_uint4(packed[0], packed[1], packed[2], packed[3]);
+      for (int e = 0; e < AT_KEYS; e += 2) {
+        const float p0 = ex2_approx(fmaf(__uint_as_float(sr[e]), scale_log2, neg_ref));
+        const float p1 = ex2_approx(fmaf(__uint_as_float(sr[e + 1]), scale_log2, neg_ref));
+        sum4[(e >> 1) & 3] += p0 + p1;
+        __nv_bfloat162 hh = __floats2bfloat162_rn(p0, p1);
+        packed[e >> 1] = *reinterpret_cast<uint32_t*>(&hh);
       }
       l += (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
+      // The P buffer, and O, belong to P V of the tile before until it is done.
+      if (j >= 1) {
+        ok = mbar_wait(pv_done, (j - 1) & 1);
+        if (!ok && lane == 0) atomicExch(&g_at_status, 8);
+        ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+        if (!ok) break;
+        // O is rescaled only when some row of the warp needs it.
+        if (__any_sync(0xffffffffu, alpha != 1.0f)) {
+          tc_fence_after();
+#pragma unroll 1
+          for (int c = 0; c < AT_D; c += 32) {
+            float o[32];
+            tmem_ld32(tO + lane_off + (uint32_t)c, o);
+#pragma unroll
+            for (int e = 0; e < 32; ++e) o[e] *= alpha;
+            tmem_st32(tO + lane_off + (uint32_t)c, o);
+          }
+        }
+      }
+      // P as bfloat16 in the MMA's layout: [row][128 bytes], 16-byte chunk index XOR (row % 8)
+      {
+        uint8_t* prow = pP + row * 128;
+#pragma unroll
+        for (int c8 = 0; c8 < AT_KEYS / 8; ++c8)
+          *reinterpret_cast<uint4*>(prow + ((c8 ^ (row & 7)) << 4)) =
+              make_uint4(packed[4 * c8], packed[4 * c8 + 1], packed[4 * c8 + 2], packed[4 * c8 + 3]);
+      }
       // the last tile: rows of V past the newest key were never written (or belong to another owner of the page)
       if (key0 + AT_KEYS - 1 > pos_hi) {
         ok = mbar_wait(v_full0 + 8u * st, (j >> 1) & 1);
@@ -285,20 +276,20 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
         ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
         if (!ok) break;
         const int valid = pos_hi - key0 + 1;
-        uint8_t* vt = pV0 + st * AT_TILE;
+        uint8_t* vt = pV0 + st * AT_KTILE;
         for (int idx = (warp - 2) * 32 + lane; idx < (AT_KEYS - valid) * 16; idx += 128) {
           const int r = valid + (idx >> 4), part = idx & 15;       // 16 x 16 bytes per row: 8 per panel
-          *reinterpret_cast<uint4*>(vt + (part >> 3) * AT_PANEL + r * 128 + ((part & 7) << 4)) = make_uint4(0u, 0u, 0u, 0u);
+          *reinterpret_cast<uint4*>(vt + (part >> 3) * AT_KPANEL + r * 128 + ((part & 7) << 4)) = make_uint4(0u, 0u, 0u, 0u);
         }
       }
       fence_proxy_async();
       tc_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive(p_ready0 + 8u * st);
+      if (lane == 0) mbar_arrive(p_ready);
     }
     // ---------------- normalise and store ----------------
     if (ok) {
-      ok = mbar_wait(pv_done0 + 8u * ((n_tiles - 1) & 1), ((n_tiles - 1) >> 1) & 1);
+      ok = mbar_wait(pv_done, (n_tiles - 1) & 1);
       if (!ok && lane == 0) atomicExch(&g_at_status, 10);
       ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
     }
@@ -332,7 +323,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
   __syncthreads();
   if (warp == 1) {
     tc_fence_after();
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512u) : "memory");
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(256u) : "memory");
   }
 }
 
@@ -344,7 +335,7 @@ LLMX_API int llmx_attention_prefill_tc(const void* q, void* out, const void* k_c
                                        const int* seq_start, const int* seq_past, int B, int T, int max_new, int H,
                                        int G, int D, int window, float scale, cudaStream_t stream) {
   if (B <= 0 || max_new <= 0 || T <= 0) return 0;
-  if (D != AT_D || H <= 0 || G <= 0 || H % G || window < 0 || B > 65535 || H > 65535 || n_pages <= 0)
+  if (D != AT_D || H <= 0 || G <= 0 || H % G || window < 0 || B > 65535 || (max_new + AT_ROWS - 1) / AT_ROWS > 65535 || n_pages <= 0)
     return LLMX_REFUSED(1);
   if (((uintptr_t)q & 15) || ((uintptr_t)k_cache & 15) || ((uintptr_t)v_cache & 15)) return LLMX_REFUSED(1);
   CUtensorMap mq, mk, mv;
@@ -352,15 +343,19 @@ LLMX_API int llmx_attention_prefill_tc(const void* q, void* out, const void* k_c
   if (make_map(&mq, q, (uint64_t)T, (uint64_t)H * D, (uint64_t)H * D, AT_ROWS, false)) return LLMX_REFUSED(4);
   if (make_map(&mk, k_cache, cache_rows, D, D, LLMX_PAGE, false)) return LLMX_REFUSED(4);
   if (make_map(&mv, v_cache, cache_rows, D, D, LLMX_PAGE, false)) return LLMX_REFUSED(4);
-  const size_t smem = 7 * (size_t)AT_TILE + 16 * 8 + 64;
+  const size_t smem = AT_SMEM;
   static bool attr_set = false;
   if (!attr_set) {
     cudaError_t e = cudaFuncSetAttribute(attention_prefill_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          (int)smem);
+    // all of the SM's L1 as shared memory, so that two CTAs fit
+    if (e == cudaSuccess)
+      e = cudaFuncSetAttribute(attention_prefill_tc_kernel, cudaFuncAttributePreferredSharedMemoryCarveout,
+                               cudaSharedmemCarveoutMaxShared);
     if (e != cudaSuccess) return (int)e;
     attr_set = true;
   }
-  dim3 grid((max_new + AT_ROWS - 1) / AT_ROWS, H, B);
+  dim3 grid(H, (max_new + AT_ROWS - 1) / AT_ROWS, B);
   launch_pdl(attention_prefill_tc_kernel, grid, dim3(AT_THREADS), smem, stream, mq, mk, mv, (bf16*)out, block_table,
              table_width, seq_start, seq_past, H, G, window, scale * 1.4426950408889634f);
   return LLMX_LAUNCH_STATUS();
