@@ -5,6 +5,8 @@
 
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
+
+#include <cstdlib>
 #include <stdint.h>
 
 #define LLMX_API extern "C" __attribute__((visibility("default")))
@@ -42,6 +44,21 @@ __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;"
 #define LLMX_TIMELINE_MAX 65536
 static __device__ unsigned long long llmx_timeline_records[3 * LLMX_TIMELINE_MAX];
 static __device__ unsigned int llmx_timeline_count;
+// Optionally the same events also go, as they happen, to pinned host memory that the device can write
+// (llmx_timeline_host): word 0 counts them, then (line, 1 = reached the wait | 2 = the wait returned) pairs.
+// The host can read that while a kernel never ends, which is when it is wanted.
+static __device__ unsigned long long* llmx_timeline_host_buf;
+static __device__ unsigned int llmx_timeline_host_cap;
+__device__ __forceinline__ void llmx_progress(int line, int what) {
+  unsigned long long* hb = llmx_timeline_host_buf;
+  if (!hb) return;
+  const unsigned long long i = atomicAdd(hb, 1ull);
+  if (i < llmx_timeline_host_cap) {
+    hb[1 + 2 * i] = (unsigned long long)line;
+    hb[2 + 2 * i] = (unsigned long long)what;
+  }
+  __threadfence_system();
+}
 __device__ __forceinline__ unsigned long long llmx_global_ns() {
   unsigned long long t;
   asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
@@ -50,10 +67,14 @@ __device__ __forceinline__ unsigned long long llmx_global_ns() {
 __device__ __forceinline__ void pdl_wait_at(int line) {
   const bool rec = (threadIdx.x | threadIdx.y | threadIdx.z | blockIdx.x | blockIdx.y | blockIdx.z) == 0;
   unsigned long long t0 = 0;
-  if (rec) t0 = llmx_global_ns();
+  if (rec) {
+    t0 = llmx_global_ns();
+    llmx_progress(line, 1);
+  }
   asm volatile("griddepcontrol.wait;" ::: "memory");
   if (rec) {
     const unsigned long long t1 = llmx_global_ns();
+    llmx_progress(line, 2);
     const unsigned int i = atomicAdd(&llmx_timeline_count, 1u);
     if (i < LLMX_TIMELINE_MAX) {
       llmx_timeline_records[3 * i] = (unsigned long long)line;
@@ -73,6 +94,12 @@ __device__ __forceinline__ void llmx_mark(int id) {
   }
 }
 #define LLMX_MARK(id) llmx_mark(id)
+// host_buf: pinned host memory of 1 + 2 * cap 64-bit words, zeroed, that the device can address; nullptr: off.
+extern "C" __attribute__((visibility("default"))) int llmx_timeline_host(unsigned long long* host_buf, unsigned int cap) {
+  cudaError_t e = cudaMemcpyToSymbol(llmx_timeline_host_buf, &host_buf, sizeof(host_buf));
+  if (e == cudaSuccess) e = cudaMemcpyToSymbol(llmx_timeline_host_cap, &cap, sizeof(cap));
+  return -(int)e;
+}
 // out: room for 3 * max_records words (line, reached, returned).  Returns the number of records copied, or the
 // negated cudaError_t of a failed call.
 extern "C" __attribute__((visibility("default"))) int llmx_timeline_read(unsigned long long* out, int max_records) {
@@ -90,6 +117,17 @@ extern "C" __attribute__((visibility("default"))) int llmx_timeline_read(unsigne
 #endif
 __device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 
+// LLMX_NO_PDL=1 in the environment orders every kernel fully after the one before (for telling a fault of a
+// kernel from a fault of the overlap between two).
+static inline int llmx_pdl_allowed() {
+  static int v = -1;
+  if (v < 0) {
+    const char* e = getenv("LLMX_NO_PDL");
+    v = (e && e[0] == '1') ? 0 : 1;
+  }
+  return v;
+}
+
 template <typename... KArgs, typename... Args>
 static inline cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem,
                                      cudaStream_t stream, Args... args) {
@@ -100,7 +138,7 @@ static inline cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 b
   cfg.stream = stream;
   cudaLaunchAttribute attr[1];
   attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  attr[0].val.programmaticStreamSerializationAllowed = llmx_pdl_allowed();
   cfg.attrs = attr;
   cfg.numAttrs = 1;
   return cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
@@ -117,7 +155,7 @@ static inline cudaError_t launch_pdl_cluster(void (*kernel)(KArgs...), dim3 grid
   cfg.stream = stream;
   cudaLaunchAttribute attr[2];
   attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  attr[0].val.programmaticStreamSerializationAllowed = llmx_pdl_allowed();
   attr[1].id = cudaLaunchAttributeClusterDimension;
   attr[1].val.clusterDim.x = cluster_x;
   attr[1].val.clusterDim.y = 1;
@@ -125,6 +163,23 @@ static inline cudaError_t launch_pdl_cluster(void (*kernel)(KArgs...), dim3 grid
   cfg.attrs = attr;
   cfg.numAttrs = 2;
   return cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
+}
+#endif
+
+#ifdef __CUDACC__
+// Makes this library's CUDA module resident on the current device without launching anything of its own
+// work: the caller does this while the GPU is idle, so that no module is loaded in the middle of a step.
+static __global__ void llmx_touch_kernel(int* p) {
+  if (p) *p = 0;
+}
+extern "C" __attribute__((visibility("default"))) int llmx_touch() {
+  cudaFuncAttributes a;
+  cudaError_t e = cudaFuncGetAttributes(&a, llmx_touch_kernel);
+  if (e != cudaSuccess) return (int)e;
+  llmx_touch_kernel<<<1, 1>>>(nullptr);
+  e = cudaGetLastError();
+  if (e != cudaSuccess) return (int)e;
+  return (int)cudaDeviceSynchronize();
 }
 #endif
 

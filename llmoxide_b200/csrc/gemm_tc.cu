@@ -640,7 +640,7 @@ static int launch_pair(const CUtensorMap& mw, const CUtensorMap& mx, void* Y, in
   attr[0].val.clusterDim.y = 1;
   attr[0].val.clusterDim.z = 1;
   attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-  attr[1].val.programmaticStreamSerializationAllowed = 1;
+  attr[1].val.programmaticStreamSerializationAllowed = llmx_pdl_allowed();
   cfg.attrs = attr;
   // A persistent grid must fit the GPU at once: not every SM can be half of a pair (it depends on how
   // the SMs are grouped), so the number of pairs that run together is asked for, once per kernel.

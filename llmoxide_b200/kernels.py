@@ -73,17 +73,44 @@ def _contig(name, t):
 
 
 _fn_cache: dict = {}
+_libs_ready: set = set()
+
+
+def _library(lib_name: str):
+    """The library, loaded onto the GPU while nothing else runs there.  Loading a CUDA module in the middle
+    of a step (hundreds of kernels launched with programmatic stream serialization still pending: the
+    sampling kernels' first use at the end of a 64-layer model's prompt step) left host and GPU waiting for
+    each other on B200 with driver 580, always with CUDA_MODULE_LOADING=EAGER and now and then without.  So
+    the first use of a library waits for the GPU to drain and makes the module resident (``llmx_touch``)
+    before anything of it is launched."""
+    lib = load_library(lib_name)
+    if lib_name not in _libs_ready:
+        if torch.cuda.is_available() and not torch.cuda.is_current_stream_capturing():
+            torch.cuda.synchronize()
+            touch = getattr(lib, "llmx_touch", None)
+            if touch is not None:
+                touch.restype = c_int
+                _check(touch(), f"loading {lib_name}")
+            torch.cuda.synchronize()
+        _libs_ready.add(lib_name)
+    return lib
 
 
 def _fn(lib_name: str, fn_name: str, argtypes):
     key = (lib_name, fn_name)
     f = _fn_cache.get(key)
     if f is None:
-        f = getattr(load_library(lib_name), fn_name)
+        f = getattr(_library(lib_name), fn_name)
         f.argtypes = argtypes
         f.restype = c_int
         _fn_cache[key] = f
     return f
+
+
+def preload(lib_names) -> None:
+    """Makes the named libraries resident now (an engine does this when it is built, so that no step has to)."""
+    for name in lib_names:
+        _library(name)
 
 
 # ---------------------------------------------------------------------------

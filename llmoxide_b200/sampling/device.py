@@ -6,11 +6,17 @@ already be running (the generation loop launches one step ahead)."""
 
 from __future__ import annotations
 
+import os
+import time
+
 import numpy as np
 import torch
 
 from .. import kernels
-from ..errors import Unsupported
+from ..errors import KernelError, Unsupported
+
+# How long the host waits for a step's tokens before it gives up with an error instead of waiting for ever.
+STEP_TIMEOUT_S = float(os.environ.get("LLMX_STEP_TIMEOUT_S", "120"))
 
 MAX_TOP_K = 1024  # SMP_MAX_K in sampling.cu
 RING = 3          # launches whose results may be unread at the same time
@@ -24,7 +30,18 @@ class SampledTokens:
         self.dev, self._host, self._event, self.n = dev, host, event, n
 
     def tokens(self) -> list:
-        self._event.synchronize()
+        """Waits for the launch (polling, so that a step that never ends becomes an error, not a silent
+        hang) and returns its tokens."""
+        if not self._event.query():
+            start = time.monotonic()
+            while not self._event.query():
+                waited = time.monotonic() - start
+                if waited > STEP_TIMEOUT_S:
+                    raise KernelError(
+                        f"a step did not finish within {STEP_TIMEOUT_S:.0f} s (LLMX_STEP_TIMEOUT_S): a kernel "
+                        f"waits for something that does not come, or the GPU is lost")
+                if waited > 0.05:
+                    time.sleep(0.001)          # a long step (a prompt): stop spinning
         return self._host[: self.n].tolist()
 
 
