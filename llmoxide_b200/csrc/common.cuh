@@ -31,7 +31,30 @@ enum { LLMX_F32 = 0, LLMX_BF16 = 1 };
 // kernels; this overlaps each launch and prologue with the kernel before.
 // ---------------------------------------------------------------------------
 #ifdef __CUDACC__
-#ifndef LLMX_TIMELINE
+#if defined(LLMX_PROGRESS)
+// Built with -DLLMX_PROGRESS, the first thread of every kernel's first CTA, once its dependency wait has
+// returned, writes the wait's source line to the next place of a ring in pinned host memory (set with
+// llmx_progress_host): what a host can still read when a step never ends.  The cost before the wait is nil.
+static __device__ unsigned int* llmx_progress_buf;      // [0] = events so far, then a ring of `cap` lines
+static __device__ unsigned int llmx_progress_cap;
+static __device__ unsigned int llmx_progress_n;
+__device__ __forceinline__ void pdl_wait_at(int line) {
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+  if ((threadIdx.x | threadIdx.y | threadIdx.z | blockIdx.x | blockIdx.y | blockIdx.z) == 0 && llmx_progress_buf) {
+    const unsigned int i = atomicAdd(&llmx_progress_n, 1u);
+    volatile unsigned int* hb = llmx_progress_buf;
+    hb[1 + i % llmx_progress_cap] = (unsigned int)line;
+    hb[0] = i + 1;
+  }
+}
+#define pdl_wait() pdl_wait_at(__LINE__)
+#define LLMX_MARK(id)
+extern "C" __attribute__((visibility("default"))) int llmx_progress_host(unsigned int* host_buf, unsigned int cap) {
+  cudaError_t e = cudaMemcpyToSymbol(llmx_progress_buf, &host_buf, sizeof(host_buf));
+  if (e == cudaSuccess) e = cudaMemcpyToSymbol(llmx_progress_cap, &cap, sizeof(cap));
+  return -(int)e;
+}
+#elif !defined(LLMX_TIMELINE)
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 #define LLMX_MARK(id)
 #else
@@ -117,15 +140,18 @@ extern "C" __attribute__((visibility("default"))) int llmx_timeline_read(unsigne
 #endif
 __device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 
-// LLMX_NO_PDL=1 in the environment orders every kernel fully after the one before (for telling a fault of a
-// kernel from a fault of the overlap between two).
+// Whether a launch may overlap the kernel before it (programmatic stream serialization).  The host switches
+// it per step with llmx_set_pdl(); LLMX_NO_PDL=1 in the environment switches it off for good (for telling a
+// fault of a kernel from a fault of the overlap between two).
+static int g_llmx_pdl_on = 1;
+extern "C" __attribute__((visibility("default"))) void llmx_set_pdl(int on) { g_llmx_pdl_on = on ? 1 : 0; }
 static inline int llmx_pdl_allowed() {
-  static int v = -1;
-  if (v < 0) {
+  static int off = -1;
+  if (off < 0) {
     const char* e = getenv("LLMX_NO_PDL");
-    v = (e && e[0] == '1') ? 0 : 1;
+    off = (e && e[0] == '1') ? 1 : 0;
   }
-  return v;
+  return off ? 0 : g_llmx_pdl_on;
 }
 
 template <typename... KArgs, typename... Args>

@@ -36,7 +36,9 @@ class LoadOptions:
     ``max_tokens``: the most tokens live sequences hold at any time, each
     sequence's count rounded up to a multiple of 64; it sizes the cache.
     ``max_batch``: most sequences alive at once (slots).
-    ``max_step_tokens``: most tokens one step may bring."""
+    ``max_step_tokens``: most tokens one step may bring.
+    ``overlap_prompt_kernels``: let the kernels of a prompt step start before the kernel before them has
+    ended, as those of decode steps always do (off: see ``Engine._step``)."""
 
     dtype: str = "bfloat16"
     max_tokens: int = 16384
@@ -45,6 +47,7 @@ class LoadOptions:
     device: str = "cuda:0"
     tensor_cores: bool = True
     cuda_graphs: bool = True
+    overlap_prompt_kernels: bool = False
 
 
 class Engine:
@@ -58,6 +61,9 @@ class Engine:
         self.rt = Runtime(dtype=options.dtype, device=self.device, max_positions=max_seq,
                           tensor_cores=options.tensor_cores)
         self.model = DecoderModel(self.spec, weights, self.rt)
+        # Every library the model will launch is built and made resident now, while the GPU is idle: a step
+        # never has to stop for one.
+        kernels.preload(sorted(self.model.libraries() | {"sampling"}))
         n_slots = max(1, min(options.max_batch, (options.max_tokens + PAGE - 1) // PAGE))
         self.cache = Cache(self.model.cache_needs(), n_slots, options.max_tokens, self.rt.cache_dtype,
                            self.device, max_seq_len=max_seq)
@@ -123,8 +129,17 @@ class Engine:
         replayed = bool(self.options.cuda_graphs and ctx.is_decode and self.model.graph_safe)
         if replayed:
             logits = self._graphed_forward(lay, ctx)
-        else:
+        elif ctx.is_decode or self.options.overlap_prompt_kernels:
             logits = self.model.forward(ctx, self.cache)
+        else:
+            # A prompt step's kernels are long; overlapping each with the one before gains about one per
+            # cent, and on B200 (driver 580) the prompt step of a 64-layer model (580 launches, 8192 tokens)
+            # stopped making progress in about one run in six with the overlap and in none of 20 without.
+            kernels.set_overlap(False)
+            try:
+                logits = self.model.forward(ctx, self.cache)
+            finally:
+                kernels.set_overlap(True)
         for slot, toks in entries:
             self.cache.alloc.commit(slot, len(toks))
         self.n_steps += 1

@@ -50,6 +50,14 @@ class DecoderModel:
                 raise ValueError(f"layer {call.layer} reads cache entry {call.cache} whose writer has other needs")
         self._writers = writers
 
+    def libraries(self) -> set:
+        """The CUDA libraries this model's parts say they launch (a part without ``libraries()`` says
+        nothing, and its libraries are loaded at their first use)."""
+        libs = {"elementwise"} | self.head.libraries() | getattr(self.final_norm, "libraries", set)()
+        for b in self.blocks:
+            libs |= getattr(b, "libraries", set)()
+        return libs
+
     def cache_needs(self) -> list:
         """Per cache entry: (KVNeed | None, StateNeed | None), from the entry's writer."""
         n = self.spec.n_cache_entries()

@@ -74,6 +74,7 @@ def _contig(name, t):
 
 _fn_cache: dict = {}
 _libs_ready: set = set()
+_overlap = True
 
 
 def _library(lib_name: str):
@@ -93,7 +94,23 @@ def _library(lib_name: str):
                 _check(touch(), f"loading {lib_name}")
             torch.cuda.synchronize()
         _libs_ready.add(lib_name)
+        if hasattr(lib, "llmx_set_pdl"):
+            lib.llmx_set_pdl(int(_overlap))
     return lib
+
+
+def set_overlap(on: bool) -> None:
+    """Whether the kernels launched from now on may start while the kernel before them still runs
+    (programmatic stream serialization; every kernel waits for its inputs itself).  On for decode steps,
+    which are chains of short kernels; the engine switches it off for prompt steps."""
+    global _overlap
+    if on == _overlap:
+        return
+    _overlap = on
+    for name in _libs_ready:
+        lib = load_library(name)
+        if hasattr(lib, "llmx_set_pdl"):
+            lib.llmx_set_pdl(int(on))
 
 
 def _fn(lib_name: str, fn_name: str, argtypes):

@@ -52,6 +52,15 @@ class GQAttention:
     def cache_need(self):
         return KVNeed(self.G, self.D, self.window), None
 
+    def libraries(self) -> set:
+        libs = {"elementwise"} | self.qkv.libraries() | self.o.libraries()
+        if self.rt.dtype == "bfloat16" and self.rt.tensor_cores:
+            libs |= {"attention_decode",
+                     "attention_prefill_tc" if self.D == 128 else "attention_prefill" if self.D == 64 else "attention"}
+        else:
+            libs.add("attention")
+        return libs
+
     def forward(self, x, ctx, view, writes_cache=True):
         H, G, D = self.H, self.G, self.D
         T = x.shape[0]

@@ -30,6 +30,12 @@ class PreNormBlock:
     def cache_need(self):
         return self.mixer.cache_need()
 
+    def libraries(self) -> set:
+        libs = set()
+        for part in (self.mixer_norm, self.ff_norm, self.mixer, self.feed_forward):
+            libs |= getattr(part, "libraries", set)()
+        return libs
+
     def forward(self, h, pending, ctx, view, writes_cache=True):
         x = self.mixer_norm.add_forward(h, pending)
         a = self.mixer.forward(x, ctx, view, writes_cache)

@@ -44,6 +44,9 @@ class GatedMLP:
         del fused
         self.down = Linear(weights.pop(t["down"].name), rt)
 
+    def libraries(self) -> set:
+        return {"elementwise"} | self.gate_up.libraries() | self.down.libraries()
+
     def forward(self, x, ctx):
         tc = self.gate_up._tc
         if tc is not None and x.dtype == torch.bfloat16 and x.shape[0] > FUSE_MIN_TOKENS and kernels.gemm_tc_supports(x, tc.weight):

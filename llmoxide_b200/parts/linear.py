@@ -22,6 +22,9 @@ class Linear:
             from . import linear_tc
             self._tc = linear_tc.plan_for(weight)
 
+    def libraries(self) -> set:
+        return {"gemm_tc", "elementwise"} if self._tc is not None else {"gemm_fma"}
+
     def __call__(self, x: torch.Tensor, out_dtype=None, splits_ok: bool = False) -> torch.Tensor:
         """x [T, in] -> [T, out], or split partials [S, T, out] in float32 when
         ``splits_ok`` and the kernel chose to split the reduction."""

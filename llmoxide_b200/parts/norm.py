@@ -15,6 +15,9 @@ class RMSNorm:
         self.size, self.eps, self.rt = spec["size"], float(spec["eps"]), rt
         self.gain = weights[spec.tensors["gain"].name].to(torch.float32).contiguous()
 
+    def libraries(self) -> set:
+        return {"elementwise"}
+
     def add_forward(self, h, delta, rows=None, write_h=True, out_dtype=None):
         n = h.shape[0] if rows is None else rows.numel()
         out = torch.empty((n, self.size), dtype=out_dtype or self.rt.act_dtype, device=h.device)

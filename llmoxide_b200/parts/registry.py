@@ -24,6 +24,11 @@ Interfaces (``rt`` is the ``Runtime``: device, compute dtype, limits):
     ``cache_need()``; ``forward(h, pending, ctx, view, writes_cache) ->
     pending``: runs one layer on the residual stream ``h`` (float32, updated in
     place); ``pending`` is a delta not yet added to ``h``.
+
+Any part may also offer ``libraries() -> set`` with the names of the CUDA
+libraries it launches (keys of ``csrc.build.LIBRARIES``); the engine builds and
+loads those when it is constructed.  A part that does not say loads its
+libraries at their first use, for which the step waits until the GPU is idle.
 """
 
 from __future__ import annotations
