@@ -115,6 +115,25 @@ def test_temperature_sampling_is_seeded_and_batch_independent(folders):
     assert out[:4] == together[0].tokens[:4] and same >= 12, (out, together[0].tokens)
 
 
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_libraries_are_resident_before_the_first_step_and_prompts_may_overlap(folders, dtype):
+    """The parts name the CUDA libraries they launch and the engine loads them when it is built; a prompt step
+    gives the same tokens with and without the overlap of consecutive kernels."""
+    from llmoxide_b200 import Request, Sampling, kernels
+    from llmoxide_b200.csrc.build import LIBRARIES
+
+    ps = prompts(ALL["D"]["vocab_size"], [70, 3, 140], seed=11)
+    outs = []
+    for overlap in (False, True):
+        session = _session(folders[("D", dtype)], dtype, overlap_prompt_kernels=overlap)
+        named = session.engine.model.libraries()
+        assert named and named <= set(LIBRARIES)
+        assert named | {"sampling"} <= kernels._libs_ready
+        outs.append([o.tokens for o in session.generate([Request(p, 6, Sampling.greedy(), stop_ids=()) for p in ps])])
+        assert kernels._overlap is True          # switched back after the prompt step
+    assert outs[0] == outs[1]
+
+
 def test_forward_and_wipe(folders):
     folder = folders[("A", "float32")]
     s = _session(folder, "float32")
