@@ -63,7 +63,7 @@ class Engine:
         self.model = DecoderModel(self.spec, weights, self.rt)
         # Every library the model will launch is built and made resident now, while the GPU is idle: a step
         # never has to stop for one.
-        kernels.preload(sorted(self.model.libraries() | {"sampling"}))
+        kernels.preload(sorted(self.model.libraries()))
         n_slots = max(1, min(options.max_batch, (options.max_tokens + PAGE - 1) // PAGE))
         self.cache = Cache(self.model.cache_needs(), n_slots, options.max_tokens, self.rt.cache_dtype,
                            self.device, max_seq_len=max_seq)

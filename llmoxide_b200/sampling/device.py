@@ -48,6 +48,7 @@ class SampledTokens:
 class DeviceSampler:
     def __init__(self, device, vocab_size: int, max_rows: int = 64):
         self.device, self.vocab = device, vocab_size
+        kernels.preload(["sampling"])      # before the step whose logits it will read is launched
         self._cap = 0
         self._turn = 0
         self._grow(max_rows)
