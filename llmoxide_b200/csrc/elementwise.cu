@@ -412,6 +412,109 @@ __global__ void qk_norm_rope_cache_kernel(const TIN* __restrict__ qkv, int n_spl
   }
 }
 
+// The same for prompts when everything is bfloat16, the head size is 128 and the rotation is full: half a
+// warp per head, a lane owns eight consecutive dims (one 16-byte load, one 16-byte store); the rotation
+// partner (dim +-64) lives eight lanes away.  A warp takes eight heads of its token, two at a time.
+#define QKV8_PER_WARP 8
+
+__global__ void qk_norm_rope_cache_bf16_d128_kernel(const bf16* __restrict__ qkv, bf16* __restrict__ q_out,
+                                                    bf16* __restrict__ k_cache, bf16* __restrict__ v_cache,
+                                                    const int* __restrict__ block_table, int table_width,
+                                                    const int* __restrict__ token_seq,
+                                                    const int* __restrict__ token_pos,
+                                                    const float* __restrict__ q_gain,
+                                                    const float* __restrict__ k_gain, float eps,
+                                                    const float* __restrict__ cos_t, const float* __restrict__ sin_t,
+                                                    int H, int G, int write_cache) {
+  constexpr int D = 128;
+  pdl_launch_dependents();
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int half = lane >> 4, l16 = lane & 15, d0 = 8 * l16;
+  const unsigned mask = half ? 0xffff0000u : 0x0000ffffu;      // the lanes that share this lane's head
+  const int t = blockIdx.x;
+  const int slot_base = (blockIdx.y * QKV_WARPS + warp) * QKV8_PER_WARP;
+  const int n_slots = write_cache ? H + 2 * G : H;
+  if (slot_base >= n_slots) return;
+  // step inputs and weights first: they do not wait for the kernel before
+  const int pos = token_pos[t];
+  int page = 0;
+  if (slot_base + QKV8_PER_WARP > H) page = block_table[(size_t)token_seq[t] * table_width + pos / LLMX_PAGE];
+  float gq[8], gk[8], cs[8], sn[8];
+  {
+    const float4 one = make_float4(1.f, 1.f, 1.f, 1.f);
+    const float4 a0 = q_gain ? load4(q_gain + d0) : one, a1 = q_gain ? load4(q_gain + d0 + 4) : one;
+    const float4 b0 = k_gain ? load4(k_gain + d0) : one, b1 = k_gain ? load4(k_gain + d0 + 4) : one;
+    const float4 c0 = load4(cos_t + (size_t)pos * 64 + (d0 & 63)), c1 = load4(cos_t + (size_t)pos * 64 + (d0 & 63) + 4);
+    const float4 s0 = load4(sin_t + (size_t)pos * 64 + (d0 & 63)), s1 = load4(sin_t + (size_t)pos * 64 + (d0 & 63) + 4);
+    gq[0] = a0.x; gq[1] = a0.y; gq[2] = a0.z; gq[3] = a0.w; gq[4] = a1.x; gq[5] = a1.y; gq[6] = a1.z; gq[7] = a1.w;
+    gk[0] = b0.x; gk[1] = b0.y; gk[2] = b0.z; gk[3] = b0.w; gk[4] = b1.x; gk[5] = b1.y; gk[6] = b1.z; gk[7] = b1.w;
+    cs[0] = c0.x; cs[1] = c0.y; cs[2] = c0.z; cs[3] = c0.w; cs[4] = c1.x; cs[5] = c1.y; cs[6] = c1.z; cs[7] = c1.w;
+    sn[0] = s0.x; sn[1] = s0.y; sn[2] = s0.z; sn[3] = s0.w; sn[4] = s1.x; sn[5] = s1.y; sn[6] = s1.z; sn[7] = s1.w;
+  }
+  pdl_wait();
+  const bf16* tok = qkv + (size_t)t * (H + 2 * G) * D;
+  uint4 raw[QKV8_PER_WARP / 2];
+#pragma unroll
+  for (int j = 0; j < QKV8_PER_WARP / 2; ++j) {
+    const int slot = slot_base + 2 * j + half;
+    if (slot < n_slots) raw[j] = *reinterpret_cast<const uint4*>(tok + (size_t)slot * D + d0);
+  }
+#pragma unroll
+  for (int j = 0; j < QKV8_PER_WARP / 2; ++j) {
+    const int slot = slot_base + 2 * j + half;                 // the same for the sixteen lanes of a half
+    if (slot >= n_slots) continue;
+    const bool is_q = slot < H, is_k = !is_q && slot < H + G;
+    bf16* dst;
+    if (is_q) {
+      dst = q_out + (size_t)t * H * D + (size_t)slot * D + d0;
+    } else {
+      const int g = is_k ? slot - H : slot - H - G;
+      dst = (is_k ? k_cache : v_cache) + cache_row_offset(page, g, pos % LLMX_PAGE, G, D) + d0;
+    }
+    if (!is_q && !is_k) {                                      // v: stored as it is
+      *reinterpret_cast<uint4*>(dst) = raw[j];
+      continue;
+    }
+    float x[8];
+    {
+      const __nv_bfloat162* h2 = reinterpret_cast<const __nv_bfloat162*>(&raw[j]);
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const float2 f = __bfloat1622float2(h2[i]);
+        x[2 * i] = f.x;
+        x[2 * i + 1] = f.y;
+      }
+    }
+    const float* gain = is_q ? gq : gk;
+    if (is_q ? q_gain != nullptr : k_gain != nullptr) {
+      float ss = 0.f;
+#pragma unroll
+      for (int i = 0; i < 8; ++i) ss += x[i] * x[i];
+#pragma unroll
+      for (int sh = 8; sh > 0; sh >>= 1) ss += __shfl_xor_sync(mask, ss, sh);
+      const float scale = 1.0f / sqrtf(ss / 128.0f + eps);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) x[i] = (x[i] * scale) * gain[i];
+    }
+    uint32_t packed[4];
+#pragma unroll
+    for (int i = 0; i < 8; i += 2) {
+      const float p0 = __shfl_xor_sync(mask, x[i], 8), p1 = __shfl_xor_sync(mask, x[i + 1], 8);
+      float r0, r1;
+      if (l16 < 8) {   // dims i < 64: x_i cos - x_{i+64} sin
+        r0 = x[i] * cs[i] - p0 * sn[i];
+        r1 = x[i + 1] * cs[i + 1] - p1 * sn[i + 1];
+      } else {         // dims i + 64: x_i sin + x_{i+64} cos
+        r0 = p0 * sn[i] + x[i] * cs[i];
+        r1 = p1 * sn[i + 1] + x[i + 1] * cs[i + 1];
+      }
+      __nv_bfloat162 h = __floats2bfloat162_rn(r0, r1);
+      packed[i >> 1] = *reinterpret_cast<uint32_t*>(&h);
+    }
+    *reinterpret_cast<uint4*>(dst) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+  }
+}
+
 LLMX_API int llmx_qk_norm_rope_cache(const void* qkv, int in_dtype, int n_split, long long split_stride, void* q_out,
                                      int act_dtype, void* k_cache, void* v_cache, int cache_dtype,
                                      const int* block_table, int table_width, const int* token_seq,
@@ -422,6 +525,14 @@ LLMX_API int llmx_qk_norm_rope_cache(const void* qkv, int in_dtype, int n_split,
   if (H <= 0 || G <= 0 || D <= 0 || n_rot < 0 || n_rot > D || (n_rot & 1) || n_split < 1) return LLMX_REFUSED(1);
   if (n_rot > 0 && (!cos_t || !sin_t)) return LLMX_REFUSED(4);
   const int n_slots = write_cache ? H + 2 * G : H;
+  if (n_split == 1 && in_dtype == LLMX_BF16 && act_dtype == LLMX_BF16 && cache_dtype == LLMX_BF16 && D == 128 &&
+      n_rot == 128 && n_tokens > 64 && !(((uintptr_t)qkv | (uintptr_t)q_out | (uintptr_t)k_cache | (uintptr_t)v_cache) & 15)) {
+    const int per_cta = QKV_WARPS * QKV8_PER_WARP;
+    launch_pdl(qk_norm_rope_cache_bf16_d128_kernel, dim3(n_tokens, (n_slots + per_cta - 1) / per_cta),
+               dim3(QKV_WARPS * 32), 0, stream, (const bf16*)qkv, (bf16*)q_out, (bf16*)k_cache, (bf16*)v_cache,
+               block_table, table_width, token_seq, token_pos, q_gain, k_gain, eps, cos_t, sin_t, H, G, write_cache);
+    return LLMX_LAUNCH_STATUS();
+  }
   const bool deep = n_split > 2;
   const int per_cta = QKV_WARPS * (deep ? 1 : QKV_SPW);
   dim3 grid(n_tokens, (n_slots + per_cta - 1) / per_cta);
