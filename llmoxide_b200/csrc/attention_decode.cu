@@ -218,7 +218,7 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
         load_tile(tile_lo + issued, issued % DEC_STAGES);
         ++issued;
       }
-      ok = mbar_wait(bars + 8 * stage, (t / DEC_STAGES) & 1);
+      ok = __all_sync(0xffffffffu, mbar_wait(bars + 8 * stage, (t / DEC_STAGES) & 1));   // the warp leaves together
       if (!ok) break;
       const uint32_t sK = sKV + stage * 2 * S::TILE, sV = sK + S::TILE;
       const int key0 = (tile_lo + t) * DEC_TILE;
