@@ -392,6 +392,12 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
   const uint32_t leader_full0 = map_to_cta(full0, 0), leader_acc_empty0 = map_to_cta(acc_empty0, 0);
 
   pdl_launch_dependents();
+  // The whole CTA waits for the kernel before it here, ahead of any set-up.  With the pair's tensor-memory
+  // allocation, its cluster barrier and the first weight tiles going on while the kernel before still ran, the
+  // prompt step of a 64-layer model stopped making progress in every second run (B200, driver 580); with the
+  // wait first, or with this kernel alone launched fully ordered, it never did.  Prompt-sized products lose
+  // next to nothing: their set-up is microseconds against hundreds.
+  pdl_wait();
   if (threadIdx.x == 0) {
     for (int s = 0; s < n_stages; ++s) {
       mbar_init(full0 + 8u * s, 2);        // one expect-tx arrival per CTA (used in the leader only)
@@ -440,8 +446,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
             tma_load_2d_pair(stage, &map_w, j * TC_BK, n0, bar);
             if (MODE == 1) tma_load_2d_pair(stage + A_BYTES, &map_w, j * TC_BK, n0 + F, bar);
           }
-          pdl_wait();
-          waited = true;
+          waited = true;                    // (the CTA waited for the kernel before it at its start)
           for (int j = 0; j < pre; ++j)
             tma_load_2d_pair(base + (uint32_t)j * STAGE_BYTES + N_ACC * A_BYTES, &map_x, j * TC_BK, tx,
                              leader_full0 + 8u * j);

@@ -132,9 +132,10 @@ class Engine:
         elif ctx.is_decode or self.options.overlap_prompt_kernels:
             logits = self.model.forward(ctx, self.cache)
         else:
-            # A prompt step's kernels are long; overlapping each with the one before gains about one per
-            # cent, and on B200 (driver 580) the prompt step of a 64-layer model (580 launches, 8192 tokens)
-            # stopped making progress in about one run in six with the overlap and in none of 20 without.
+            # A prompt step's kernels are long and gain nothing measurable from overlapping the kernel before
+            # them.  With the overlap, the prompt step of a 64-layer model stopped making progress now and
+            # then on B200 (driver 580) until the CTA-pair matrix product waited before its set-up
+            # (gemm_tc.cu); without it, it never did.  Off by default all the same.
             kernels.set_overlap(False)
             try:
                 logits = self.model.forward(ctx, self.cache)
