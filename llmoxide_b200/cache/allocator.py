@@ -135,6 +135,17 @@ class CacheAllocator:
             pages.extend(pool.take(want - len(pages)))
         st.reserved = max(st.reserved, new_len)
 
+    def unreserve(self, slot: int) -> None:
+        """Takes back a reservation that no step will use: pages beyond those the slot's length needs return
+        to their pools (a step that was refused for another sequence of its batch calls this for the
+        sequences it had already reserved for)."""
+        st = self._live(slot)
+        keep = pages_for(st.length)
+        for pool, pages in zip(self.pools, st.pages):
+            pool.give_back([p for p in pages[keep:] if p >= 0])
+            del pages[keep:]
+        st.reserved = st.length
+
     def commit(self, slot: int, n_new: int) -> None:
         """The step wrote n_new positions: the length grows, and groups with a
         window give back the pages no later query can see."""

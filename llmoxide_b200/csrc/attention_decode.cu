@@ -583,9 +583,12 @@ LLMX_API int llmx_attention_decode_noalloc(const void* q, void* out, const void*
                                            cudaStream_t stream) {
   if (B <= 0) return 0;
   if (H <= 0 || G <= 0 || H % G || D <= 0 || n_chunks < 1) return LLMX_REFUSED(1);
-  const unsigned long long need = (unsigned long long)B * H * n_chunks * (unsigned long long)DEC_WS_ROW(D);
-  const unsigned long long groups = (unsigned long long)B * G * ((H / G + DEC_ROWS - 1) / DEC_ROWS);
-  if (need > LLMX_NOALLOC_WS_FLOATS || groups > LLMX_NOALLOC_COUNTERS) return LLMX_NOALLOC_TOO_LARGE;
+  // Up to 8 shares merge inside a thread-block cluster and touch neither array: no limit applies to them.
+  if (n_chunks > 8) {
+    const unsigned long long need = (unsigned long long)B * H * n_chunks * (unsigned long long)DEC_WS_ROW(D);
+    const unsigned long long groups = (unsigned long long)B * G * ((H / G + DEC_ROWS - 1) / DEC_ROWS);
+    if (need > LLMX_NOALLOC_WS_FLOATS || groups > LLMX_NOALLOC_COUNTERS) return LLMX_NOALLOC_TOO_LARGE;
+  }
   int dev = -1;
   cudaError_t e = cudaGetDevice(&dev);
   if (e != cudaSuccess) return (int)e;

@@ -20,9 +20,12 @@
 // allocating library routine.
 //
 // Limits and rules.
-//  * B * H * n_chunks * (D + 4) must not exceed LLMX_NOALLOC_WS_FLOATS, and
-//    B * G * ceil((H/G)/8) must not exceed LLMX_NOALLOC_COUNTERS; a larger
-//    request is refused with LLMX_NOALLOC_TOO_LARGE and nothing is launched.
+//  * With more than 8 shares per sequence (n_chunks > 8), B * H * n_chunks *
+//    (D + 4) must not exceed LLMX_NOALLOC_WS_FLOATS, and B * G * ceil((H/G)/8)
+//    must not exceed LLMX_NOALLOC_COUNTERS; a larger request is refused with
+//    LLMX_NOALLOC_TOO_LARGE and nothing is launched.  With up to 8 shares the
+//    pieces are merged inside a thread-block cluster, neither array is
+//    touched, and no size limit applies.
 //  * The first call on a device looks up the array's device address
 //    (cudaGetSymbolAddress, with that device current) and remembers it; make
 //    that first call outside any stream capture.

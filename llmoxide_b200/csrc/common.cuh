@@ -31,30 +31,7 @@ enum { LLMX_F32 = 0, LLMX_BF16 = 1 };
 // kernels; this overlaps each launch and prologue with the kernel before.
 // ---------------------------------------------------------------------------
 #ifdef __CUDACC__
-#if defined(LLMX_PROGRESS)
-// Built with -DLLMX_PROGRESS, the first thread of every kernel's first CTA, once its dependency wait has
-// returned, writes the wait's source line to the next place of a ring in pinned host memory (set with
-// llmx_progress_host): what a host can still read when a step never ends.  The cost before the wait is nil.
-static __device__ unsigned int* llmx_progress_buf;      // [0] = events so far, then a ring of `cap` lines
-static __device__ unsigned int llmx_progress_cap;
-static __device__ unsigned int llmx_progress_n;
-__device__ __forceinline__ void pdl_wait_at(int line) {
-  asm volatile("griddepcontrol.wait;" ::: "memory");
-  if ((threadIdx.x | threadIdx.y | threadIdx.z | blockIdx.x | blockIdx.y | blockIdx.z) == 0 && llmx_progress_buf) {
-    const unsigned int i = atomicAdd(&llmx_progress_n, 1u);
-    volatile unsigned int* hb = llmx_progress_buf;
-    hb[1 + i % llmx_progress_cap] = (unsigned int)line;
-    hb[0] = i + 1;
-  }
-}
-#define pdl_wait() pdl_wait_at(__LINE__)
-#define LLMX_MARK(id)
-extern "C" __attribute__((visibility("default"))) int llmx_progress_host(unsigned int* host_buf, unsigned int cap) {
-  cudaError_t e = cudaMemcpyToSymbol(llmx_progress_buf, &host_buf, sizeof(host_buf));
-  if (e == cudaSuccess) e = cudaMemcpyToSymbol(llmx_progress_cap, &cap, sizeof(cap));
-  return -(int)e;
-}
-#elif !defined(LLMX_TIMELINE)
+#if !defined(LLMX_TIMELINE)
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 #define LLMX_MARK(id)
 #else
@@ -67,21 +44,6 @@ __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;"
 #define LLMX_TIMELINE_MAX 65536
 static __device__ unsigned long long llmx_timeline_records[3 * LLMX_TIMELINE_MAX];
 static __device__ unsigned int llmx_timeline_count;
-// Optionally the same events also go, as they happen, to pinned host memory that the device can write
-// (llmx_timeline_host): word 0 counts them, then (line, 1 = reached the wait | 2 = the wait returned) pairs.
-// The host can read that while a kernel never ends, which is when it is wanted.
-static __device__ unsigned long long* llmx_timeline_host_buf;
-static __device__ unsigned int llmx_timeline_host_cap;
-__device__ __forceinline__ void llmx_progress(int line, int what) {
-  unsigned long long* hb = llmx_timeline_host_buf;
-  if (!hb) return;
-  const unsigned long long i = atomicAdd(hb, 1ull);
-  if (i < llmx_timeline_host_cap) {
-    hb[1 + 2 * i] = (unsigned long long)line;
-    hb[2 + 2 * i] = (unsigned long long)what;
-  }
-  __threadfence_system();
-}
 __device__ __forceinline__ unsigned long long llmx_global_ns() {
   unsigned long long t;
   asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
@@ -90,14 +52,10 @@ __device__ __forceinline__ unsigned long long llmx_global_ns() {
 __device__ __forceinline__ void pdl_wait_at(int line) {
   const bool rec = (threadIdx.x | threadIdx.y | threadIdx.z | blockIdx.x | blockIdx.y | blockIdx.z) == 0;
   unsigned long long t0 = 0;
-  if (rec) {
-    t0 = llmx_global_ns();
-    llmx_progress(line, 1);
-  }
+  if (rec) t0 = llmx_global_ns();
   asm volatile("griddepcontrol.wait;" ::: "memory");
   if (rec) {
     const unsigned long long t1 = llmx_global_ns();
-    llmx_progress(line, 2);
     const unsigned int i = atomicAdd(&llmx_timeline_count, 1u);
     if (i < LLMX_TIMELINE_MAX) {
       llmx_timeline_records[3 * i] = (unsigned long long)line;
@@ -117,12 +75,6 @@ __device__ __forceinline__ void llmx_mark(int id) {
   }
 }
 #define LLMX_MARK(id) llmx_mark(id)
-// host_buf: pinned host memory of 1 + 2 * cap 64-bit words, zeroed, that the device can address; nullptr: off.
-extern "C" __attribute__((visibility("default"))) int llmx_timeline_host(unsigned long long* host_buf, unsigned int cap) {
-  cudaError_t e = cudaMemcpyToSymbol(llmx_timeline_host_buf, &host_buf, sizeof(host_buf));
-  if (e == cudaSuccess) e = cudaMemcpyToSymbol(llmx_timeline_host_cap, &cap, sizeof(cap));
-  return -(int)e;
-}
 // out: room for 3 * max_records words (line, reached, returned).  Returns the number of records copied, or the
 // negated cudaError_t of a failed call.
 extern "C" __attribute__((visibility("default"))) int llmx_timeline_read(unsigned long long* out, int max_records) {

@@ -392,11 +392,10 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
   const uint32_t leader_full0 = map_to_cta(full0, 0), leader_acc_empty0 = map_to_cta(acc_empty0, 0);
 
   pdl_launch_dependents();
-  // The whole CTA waits for the kernel before it here, ahead of any set-up.  With the pair's tensor-memory
-  // allocation, its cluster barrier and the first weight tiles going on while the kernel before still ran, the
-  // prompt step of a 64-layer model stopped making progress in every second run (B200, driver 580); with the
-  // wait first, or with this kernel alone launched fully ordered, it never did.  Prompt-sized products lose
-  // next to nothing: their set-up is microseconds against hundreds.
+  // Rule: a CTA pair waits for the kernel before it ahead of any set-up.  Its tensor-memory allocation for the
+  // pair, its cluster barrier and its first weight tiles must not be in progress while CTAs of the kernel before
+  // still hold tensor memory and shared memory on the same SMs: two kernels each waiting for what the other
+  // holds do not finish.  Prompt-sized products lose next to nothing: the set-up is microseconds against hundreds.
   pdl_wait();
   if (threadIdx.x == 0) {
     for (int s = 0; s < n_stages; ++s) {

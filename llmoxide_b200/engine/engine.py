@@ -21,7 +21,7 @@ import torch
 from .. import kernels
 from ..cache import PAGE, Cache
 from ..config import read_config
-from ..errors import CacheMisuse, ContextOverflow
+from ..errors import CacheExhausted, CacheMisuse, ContextOverflow
 from ..parts import Runtime
 from ..weights import load_checkpoint, random_tensors_on_device
 from .batch import StepBuffers, build_host_arrays
@@ -38,7 +38,7 @@ class LoadOptions:
     ``max_batch``: most sequences alive at once (slots).
     ``max_step_tokens``: most tokens one step may bring.
     ``overlap_prompt_kernels``: let the kernels of a prompt step start before the kernel before them has
-    ended, as those of decode steps always do (off: see ``Engine._step``)."""
+    ended, as those of decode steps always do (off by default; the rule is stated in ``Engine._step``)."""
 
     dtype: str = "bfloat16"
     max_tokens: int = 16384
@@ -132,10 +132,9 @@ class Engine:
         elif ctx.is_decode or self.options.overlap_prompt_kernels:
             logits = self.model.forward(ctx, self.cache)
         else:
-            # A prompt step's kernels are long and gain nothing measurable from overlapping the kernel before
-            # them.  With the overlap, the prompt step of a 64-layer model stopped making progress now and
-            # then on B200 (driver 580) until the CTA-pair matrix product waited before its set-up
-            # (gemm_tc.cu); without it, it never did.  Off by default all the same.
+            # Rule: the kernels of a prompt step run fully ordered.  They are long, so overlapping a kernel's
+            # start with the end of the one before gains nothing measurable, and kernels that hold tensor
+            # memory and whole SMs must not wait on one another for resources.
             kernels.set_overlap(False)
             try:
                 logits = self.model.forward(ctx, self.cache)
@@ -172,11 +171,17 @@ class Engine:
                     raise ValueError(f"slot {slot}: wanted place {w} is outside its {len(toks)} tokens")
         alloc = self.cache.alloc
         lengths = [alloc.length(slot) for slot, _ in entries]
-        # Reserve for every sequence before anything runs; on failure give the
-        # pages of this step back by leaving lengths untouched (pages stay with
-        # their slots and are freed with them).
-        for slot, toks in entries:
-            alloc.reserve(slot, len(toks))
+        # Reserve for every sequence before anything runs.  When one of them does not fit, the ones before it
+        # give their new pages back, so that a refused step leaves the cache as it found it.
+        reserved = []
+        try:
+            for slot, toks in entries:
+                alloc.reserve(slot, len(toks))
+                reserved.append(slot)
+        except (CacheExhausted, ContextOverflow):
+            for slot in reserved:
+                alloc.unreserve(slot)
+            raise
         n_groups = max(1, self.cache.n_groups())
         page_rows = [[alloc.page_row(slot, g) for slot, _ in entries] for g in range(n_groups)]
         lay, buf, facts = build_host_arrays(entries, want, lengths, page_rows, n_groups)

@@ -213,13 +213,24 @@ class GenerationLoop:
         """Starts a decode step for ``seqs`` (each brings its ``next_token``, or,
         with ``feed``, the token the step before is still computing)."""
         entries = [(s.slot, [0 if feed is not None else s.next_token]) for s in seqs]
+        # A launch that the backend refuses (no room for a token that may not be needed) must leave every
+        # sequence's random stream where it was: the draws are taken back, so that a sequence's tokens do
+        # not depend on how full the cache was.
+        states = [s.rng.state for s in seqs]
         uniforms = [0.0 if s.sampling.is_greedy() else s.rng.next_f32() for s in seqs]
         args = (entries, [s.sampling for s in seqs], [s.out for s in seqs], uniforms)
+        try:
+            if hasattr(self.backend, "launch_step_sample"):
+                handle = self.backend.launch_step_sample(*args, feed=feed)
+            else:
+                handle = _Done(self.backend.step_sample(*args))
+        except BaseException:
+            for s, state in zip(seqs, states):
+                s.rng.state = state
+            raise
         self.timings.steps += 1
         self.timings.decode_tokens += len(seqs)
-        if hasattr(self.backend, "launch_step_sample"):
-            return self.backend.launch_step_sample(*args, feed=feed)
-        return _Done(self.backend.step_sample(*args))
+        return handle
 
     def _can_run_ahead(self, seqs) -> bool:
         """A second step may be launched before the first one's tokens are known

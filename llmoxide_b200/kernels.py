@@ -78,12 +78,11 @@ _overlap = True
 
 
 def _library(lib_name: str):
-    """The library, loaded onto the GPU while nothing else runs there.  Loading a CUDA module in the middle
-    of a step (hundreds of kernels launched with programmatic stream serialization still pending: the
-    sampling kernels' first use at the end of a 64-layer model's prompt step) left host and GPU waiting for
-    each other on B200 with driver 580, always with CUDA_MODULE_LOADING=EAGER and now and then without.  So
-    the first use of a library waits for the GPU to drain and makes the module resident (``llmx_touch``)
-    before anything of it is launched."""
+    """The library, loaded onto the GPU while nothing else runs there.  Rule: no CUDA module is loaded in the
+    middle of a step, because loading one synchronises with the device while hundreds of launches that overlap
+    one another may still be pending.  So the first use of a library waits for the GPU to drain and makes the
+    module resident (``llmx_touch``) before anything of it is launched; an engine names its libraries when it
+    is built (``preload``), so that no step has to."""
     lib = load_library(lib_name)
     if lib_name not in _libs_ready:
         if torch.cuda.is_available() and not torch.cuda.is_current_stream_capturing():

@@ -296,6 +296,62 @@ def test_running_one_step_ahead_changes_no_outcome():
     assert out.tokens == [8, 8] and be3.fed_ahead == 0
 
 
+def test_a_refused_launch_ahead_takes_no_draw():
+    """The step launched ahead may be refused (no room for a token that may never be needed).  The draws taken
+    for it are given back, so every sequence's uniforms are still its own stream in order."""
+
+    class Refusing(AheadBackend):
+        def __init__(self, scripts, n_slots, refuse_at):
+            super().__init__(scripts, n_slots)
+            self.refuse_at, self.calls, self.draws = set(refuse_at), 0, []
+
+        def launch_step_sample(self, entries, samplings, recents, uniforms, feed=None):
+            self.calls += 1
+            if feed is not None and self.calls in self.refuse_at:
+                raise CacheExhausted("scripted: no page for the step ahead")
+            self.draws.append((feed is not None, list(uniforms)))
+            return super().launch_step_sample(entries, samplings, recents, uniforms, feed=feed)
+
+        def step_sample(self, entries, samplings, recents, uniforms):
+            if len(entries[0][1]) > 1 or not self.steps:           # the prompt step (called directly by the loop)
+                self.draws.append((False, list(uniforms)))
+            return super().step_sample(entries, samplings, recents, uniforms)
+
+    scripts = {1: [5] * 9, 2: [6] * 9}
+    lim = Limits(max_batch=2, max_tokens=64 * 8, max_step_tokens=100, max_seq_len=128)
+    samp = Sampling(temperature=0.7, seed=21)
+    reqs = [Request([1, 3], 7, samp), Request([2, 4], 7, samp.with_(seed=22))]
+    for refuse_at in ((), (2,), (2, 3, 5)):
+        be = Refusing(scripts, 2, refuse_at)
+        outs = GenerationLoop(be, lim, Sampling.greedy(), (99,)).run(reqs)
+        assert [o.tokens for o in outs] == [[5] * 7, [6] * 7]
+        # every sampled row's draw, in step order, is the sequence's own stream: nothing skipped, nothing twice
+        r21, r22 = plain.Rng(21), plain.Rng(22)
+        assert [d[0] for _, d in be.draws] == [r21.next_f32() for _ in be.draws], refuse_at
+        assert [d[1] for _, d in be.draws] == [r22.next_f32() for _ in be.draws], refuse_at
+        assert len(be.draws) == 7
+
+
+def test_a_refused_step_leaves_the_cache_as_it_was():
+    """Two sequences in one step, the second does not fit: the first one's new pages go back, and a later
+    smaller step for it still finds a block-table row that matches its length."""
+    a = CacheAllocator(n_slots=2, n_pages=4, windows=[None, 48])
+    s0, s1 = a.acquire(), a.acquire()
+    a.reserve(s0, 10), a.commit(s0, 10)
+    a.reserve(s1, 2 * PAGE), a.commit(s1, 2 * PAGE)
+    held = (a.pages_held(0), a.pages_held(1))
+    a.reserve(s0, PAGE)                       # fits: one more page in each group
+    with pytest.raises(CacheExhausted):
+        a.reserve(s1, 2 * PAGE)               # does not: the step is refused as a whole
+    a.unreserve(s0)
+    assert (a.pages_held(0), a.pages_held(1)) == held
+    assert len(a.page_row(s0, 0)) == pages_for(10) and a.length(s0) == 10
+    a.check_consistent()
+    a.reserve(s0, 1), a.commit(s0, 1)
+    assert len(a.page_row(s0, 0)) == 1
+    a.check_consistent()
+
+
 def test_decode_attention_share_count_depends_on_the_shape_only():
     """Every sequence's keys are cut into as many shares as keep the whole grid resident at once (two CTAs per
     SM), at most 8 (one thread-block cluster) and never more than a full block table has 32-key tiles for."""
