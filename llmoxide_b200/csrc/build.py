@@ -42,6 +42,7 @@ LIBRARIES = {
     "gemm_fma": (["gemm_fma.cu"], []),
     "gemm_tc": (["gemm_tc.cu"], []),
     "sampling": (["sampling.cu"], []),
+    "random_init": (["random_init.cu"], []),
 }
 HEADERS = ["common.cuh", "attention_decode_noalloc.h", "tc_ptx.cuh"]
 

@@ -418,6 +418,19 @@ def gemm_tc_status(reset: bool = True) -> int:
     return f(int(reset))
 
 
+def fill_normal(out: torch.Tensor, stream: int, quantiles: torch.Tensor, mean: float, std: float,
+                storage_dtype: torch.dtype) -> None:
+    """out[i] = mean + std * normal(stream, i), rounded to ``storage_dtype`` first: the counter-based
+    generator of ``weights.random_init`` (same bits as its host version)."""
+    _dev(out, quantiles)
+    _contig("out", out)
+    assert quantiles.dtype == torch.float32 and quantiles.numel() == 65537 and quantiles.is_contiguous()
+    f = _fn("random_init", "llmx_fill_normal",
+            [c_void_p, c_int, c_longlong, ctypes.c_ulonglong, c_void_p, c_float, c_float, c_int, c_void_p])
+    _check(f(_ptr(out), _tag(out), out.numel(), stream & 0xFFFFFFFFFFFFFFFF, _ptr(quantiles), mean, std,
+             _DTYPE_TAG[storage_dtype], _stream()), "fill_normal")
+
+
 def argmax(logits: torch.Tensor, out_tokens: torch.Tensor) -> None:
     """out_tokens[b] = the last index among the maxima of logits[b,:]."""
     _dev(logits, out_tokens)

@@ -55,11 +55,11 @@ def _commit(cache, slots, seq_tokens):
 
 def _weights_of(cfg_raw, seed=3):
     from llmoxide_b200.config import read_config
-    from llmoxide_b200.weights.random_init import _host_tensor
+    from llmoxide_b200.weights.random_init import host_tensor
 
     cfg = read_config(cfg_raw)
     spec = cfg.to_spec()
-    w = {t.name: _host_tensor(t, seed, torch.float32) for t in spec.tensors()}
+    w = {t.name: host_tensor(t, seed, torch.float32) for t in spec.tensors()}
     return cfg, spec, w
 
 
