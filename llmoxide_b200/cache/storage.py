@@ -18,6 +18,7 @@ from typing import Optional
 
 import torch
 
+from ..guard import guarded
 from .allocator import PAGE, CacheAllocator
 
 
@@ -75,11 +76,13 @@ class Cache:
         self.k_store, self.v_store = [], []
         for kv in self.groups:
             shape = (len(members[kv]), n_pages, kv.n_kv_heads, PAGE, kv.head_dim)
-            self.k_store.append(torch.zeros(shape, dtype=dtype, device=device))
-            self.v_store.append(torch.zeros(shape, dtype=dtype, device=device))
+            # (every long-lived buffer carries guard words behind it: guard.py)
+            g = len(self.k_store)
+            self.k_store.append(guarded(shape, dtype, device, f"cache group {g} keys", zero=True))
+            self.v_store.append(guarded(shape, dtype, device, f"cache group {g} values", zero=True))
         self.state_store = [
-            None if st is None else torch.zeros((n_slots, *st.shape), dtype=st.dtype, device=device)
-            for _, st in needs
+            None if st is None else guarded((n_slots, *st.shape), st.dtype, device, f"cache entry {e} state", zero=True)
+            for e, (_, st) in enumerate(needs)
         ]
         self.alloc = CacheAllocator(n_slots, n_pages, [kv.window for kv in self.groups] or [None],
                                     max_seq_len=max_seq_len)

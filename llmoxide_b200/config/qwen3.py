@@ -249,11 +249,17 @@ class Qwen3Config:
         return ModelSpec(
             architecture=self.architectures[0],
             hidden_size=d, vocab_size=self.vocab_size,
-            embedding=TensorSpec("model.embed_tokens.weight", (self.vocab_size, d)),
+            # a plain gather (no scale) and a plain product (no cap), tied when the folder has no lm_head
+            embedding=PartSpec("gather", dict(scale=None),
+                               dict(table=TensorSpec("model.embed_tokens.weight", (self.vocab_size, d)))),
             blocks=tuple(blocks), schedule=default_schedule(self.num_hidden_layers),
             final_norm=PartSpec("rms_norm", dict(size=d, eps=eps),
                                 dict(gain=TensorSpec("model.norm.weight", (d,), "vector"))),
-            head=None if self.tie_word_embeddings else TensorSpec("lm_head.weight", (self.vocab_size, d)),
+            head=(PartSpec("linear", dict(tied=True, softcap=None), {}) if self.tie_word_embeddings else
+                  PartSpec("linear", dict(softcap=None), dict(weight=TensorSpec("lm_head.weight", (self.vocab_size, d))))),
+            # exporters write the rotation's frequencies beside the weights; a tied model's file may still
+            # carry the head (crates/model/src/qwen35/weights.rs:79 decides by presence; here the configuration does)
+            ignored_tensors=("*.rotary_emb.inv_freq",) + (("lm_head.weight",) if self.tie_word_embeddings else ()),
             max_positions=self.max_position_embeddings,
             stop_ids=tuple(self.eos_token_id),
             storage_dtype=self.torch_dtype,

@@ -70,18 +70,37 @@ class LayerCall:
 
 @dataclass(frozen=True)
 class ModelSpec:
+    """``embedding`` and ``head`` are parts like the others (kinds of the embedding and head registries).
+    For the common case a bare ``TensorSpec`` may be given for the embedding (a plain gather of that table)
+    and a ``TensorSpec`` or ``None`` for the head (a plain matrix product with that matrix, or with the
+    embedding's table when None); they are wrapped into the built-in parts."""
+
     architecture: str
     hidden_size: int
     vocab_size: int
-    embedding: TensorSpec
+    embedding: Any                        # PartSpec (or a TensorSpec: the table of a plain gather)
     blocks: Sequence[BlockSpec]
     schedule: Sequence[LayerCall]
     final_norm: PartSpec
-    head: Optional[TensorSpec]            # None: logits use the embedding table
+    head: Any                             # PartSpec (or a TensorSpec / None: a plain product, tied when None)
     max_positions: int
     stop_ids: tuple = ()
     storage_dtype: str = "bfloat16"       # what a random checkpoint is written in
     default_sampling: Mapping[str, Any] = field(default_factory=dict)
+    # Tensors a checkpoint may hold beyond the model's own, which are then left alone: exact names, or
+    # "*suffix" for every name with that ending (buffers that exporters write beside the weights).
+    ignored_tensors: tuple = ()
+
+    def __post_init__(self):
+        if isinstance(self.embedding, TensorSpec):
+            object.__setattr__(self, "embedding", PartSpec("gather", {}, {"table": self.embedding}))
+        if self.head is None:
+            object.__setattr__(self, "head", PartSpec("linear", {"tied": True}, {}))
+        elif isinstance(self.head, TensorSpec):
+            object.__setattr__(self, "head", PartSpec("linear", {}, {"weight": self.head}))
+
+    def is_ignored(self, name: str) -> bool:
+        return any(name.endswith(pat[1:]) if pat.startswith("*") else name == pat for pat in self.ignored_tensors)
 
     def tensors(self) -> list:
         """Every tensor the checkpoint must hold, each once."""
@@ -92,7 +111,8 @@ class ModelSpec:
                 seen.add(t.name)
                 out.append(t)
 
-        add(self.embedding)
+        for t in self.embedding.tensors.values():
+            add(t)
         for b in self.blocks:
             parts = [b.mixer, b.feed_forward, *b.norms.values()]
             if b.position is not None:
@@ -102,7 +122,8 @@ class ModelSpec:
                     add(t)
         for t in self.final_norm.tensors.values():
             add(t)
-        add(self.head)
+        for t in self.head.tensors.values():
+            add(t)
         return out
 
     def n_cache_entries(self) -> int:

@@ -54,6 +54,10 @@
 #define DEC_PANEL (DEC_TILE * 128)           // a tile's 64 head dims as the tensor copy lays them down: 128-byte rows
 
 static __device__ int g_dec_status;          // 0; 1 after a copy that never completed; 2: shared memory not 1024-byte aligned
+__device__ __forceinline__ void dec_report(int code) {
+  atomicExch(&g_dec_status, code);
+  llmx_report(code);
+}
 
 __device__ __forceinline__ void cp_async16(uint32_t dst, const void* src) {
   asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
@@ -140,7 +144,7 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
   uint8_t* wsm = smem + warp * S::WARP;
   const uint32_t sKV = (uint32_t)__cvta_generic_to_shared(wsm);
   const bool misaligned = S::TMA && (sKV & 1023u);   // the swizzled layout is a function of the address: refuse, never guess
-  if (misaligned && threadIdx.x == 0) atomicExch(&g_dec_status, 2);
+  if (misaligned && threadIdx.x == 0) dec_report(2);
   const uint32_t bars = (uint32_t)__cvta_generic_to_shared(smem + S::BARS) + warp * DEC_STAGES * 8;
   if (lane == 0) {
     // a tensor copy's bytes are counted against one announcement; cp.async counts one arrival per lane
@@ -160,7 +164,9 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
   const int tile_hi = min(tile_lo + per_warp - 1, t_last);
   const int n_tiles = misaligned ? 0 : tile_hi - tile_lo + 1;     // <= 0: nothing to do
 
+  const bool withhold = llmx_withhold != 0;       // tests: the first CTA's first warp never asks for its first tile
   auto load_tile = [&](int tile, int stage) {
+    if (withhold && tile == tile_lo && warp == 0 && (blockIdx.x | blockIdx.y | blockIdx.z) == 0) return;
     const int key0 = tile * DEC_TILE;
     const int phys = pages[key0 / LLMX_PAGE];
     const uint32_t sK = sKV + stage * 2 * S::TILE, sV = sK + S::TILE, bar = bars + 8 * stage;
@@ -306,7 +312,7 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
       }
       __syncwarp();   // the stage is refilled by the next iteration's copies
     }
-    if (!ok && lane == 0) atomicExch(&g_dec_status, 1);
+    if (!ok && lane == 0) dec_report(1);
     if (!S::TMA) asm volatile("cp.async.wait_all;" ::: "memory");
 #pragma unroll
     for (int sh = 4; sh < 32; sh <<= 1) {

@@ -37,7 +37,11 @@
 #define AT_KTILE (2 * AT_KPANEL)    // bytes of a [64 keys x 128 dims] tile of K or V
 #define AT_SMEM (AT_TILE + 4 * AT_KTILE + AT_PANEL + 16 * 8 + 64)   // Q, K[2], V[2], P, barriers
 
-__device__ int g_at_status = 0;
+__device__ int g_at_status = 0;    // 0, or which bounded wait ran out (1..10 below), 20: shared memory not 1024-byte aligned
+__device__ __forceinline__ void at_report(int code) {
+  atomicExch(&g_at_status, code);
+  llmx_report(code);
+}
 
 
 // instruction descriptors: bf16 x bf16 -> f32, M = 128
@@ -68,7 +72,6 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
   const int first_lo = (window > 0 && pos_lo - (window - 1) > 0) ? pos_lo - (window - 1) : 0;
   const int tile_first = first_lo / AT_KEYS, tile_last = pos_hi / AT_KEYS;
   const int n_tiles = tile_last - tile_first + 1;
-  const int last_page = pos_hi / LLMX_PAGE;                  // pages past this one are never read
   const int* pages = block_table + (size_t)b * table_width;
 
   // shared memory: Q (32 KB), K[2], V[2] (16 KB each), P (16 KB), then barriers
@@ -76,7 +79,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
   // 1024-byte boundary (it does when the kernel has no static shared memory); otherwise nothing runs.
   const uint32_t base = smem_u32(smem_raw);
   if (base & 1023u) {
-    if (threadIdx.x == 0) atomicExch(&g_at_status, 20);
+    if (threadIdx.x == 0) at_report(20);
     return;
   }
   uint8_t* base_ptr = smem_raw;
@@ -127,11 +130,11 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
         const int st = j & 1;
         const uint32_t parity = ((j >> 1) & 1) ^ 1;
         const int row = (pages[tile_first + j] * G + g) * LLMX_PAGE;      // the tile is one page of one kv head
-        if (!mbar_wait(k_empty0 + 8u * st, parity)) { atomicExch(&g_at_status, 1); break; }
+        if (!mbar_wait(k_empty0 + 8u * st, parity)) { at_report(1); break; }
         mbar_expect_tx(k_full0 + 8u * st, AT_KTILE);
         tma_load_2d(sK0 + (uint32_t)st * AT_KTILE, &map_k, 0, row, k_full0 + 8u * st);
         tma_load_2d(sK0 + (uint32_t)st * AT_KTILE + AT_KPANEL, &map_k, 64, row, k_full0 + 8u * st);
-        if (!mbar_wait(v_empty0 + 8u * st, parity)) { atomicExch(&g_at_status, 2); break; }
+        if (!mbar_wait(v_empty0 + 8u * st, parity)) { at_report(2); break; }
         mbar_expect_tx(v_full0 + 8u * st, AT_KTILE);
         tma_load_2d(sV0 + (uint32_t)st * AT_KTILE, &map_v, 0, row, v_full0 + 8u * st);
         tma_load_2d(sV0 + (uint32_t)st * AT_KTILE + AT_KPANEL, &map_v, 64, row, v_full0 + 8u * st);
@@ -142,11 +145,11 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
     if (lane == 0) {
       constexpr uint32_t idesc_s = at_idesc(false, AT_KEYS), idesc_o = at_idesc(true, AT_D);
       bool ok = mbar_wait(q_full, 0);
-      if (!ok) atomicExch(&g_at_status, 3);
+      if (!ok) at_report(3);
       auto issue_pv = [&](int j) {       // O += P_j V_j
         const int st = j & 1;
-        if (!mbar_wait(p_ready, j & 1)) { atomicExch(&g_at_status, 5); return false; }
-        if (!mbar_wait(v_full0 + 8u * st, (j >> 1) & 1)) { atomicExch(&g_at_status, 6); return false; }
+        if (!mbar_wait(p_ready, j & 1)) { at_report(5); return false; }
+        if (!mbar_wait(v_full0 + 8u * st, (j >> 1) & 1)) { at_report(6); return false; }
         tc_fence_after();
         const uint32_t v = sV0 + (uint32_t)st * AT_KTILE;
 #pragma unroll
@@ -161,7 +164,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
       };
       for (int j = 0; j < n_tiles && ok; ++j) {
         const int st = j & 1;
-        if (!mbar_wait(k_full0 + 8u * st, (j >> 1) & 1)) { atomicExch(&g_at_status, 4); ok = false; break; }
+        if (!mbar_wait(k_full0 + 8u * st, (j >> 1) & 1)) { at_report(4); ok = false; break; }
         tc_fence_after();
         const uint32_t k = sK0 + (uint32_t)st * AT_KTILE;
 #pragma unroll
@@ -171,7 +174,8 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
           umma_bf16(tS0 + (uint32_t)st * AT_KEYS, umma_desc(sQ + qoff), umma_desc(k + koff), idesc_s, ks > 0 ? 1u : 0u);
         }
         umma_commit(k_empty0 + 8u * st);
-        umma_commit(s_full0 + 8u * st);
+        if (!(j == 0 && llmx_withhold))     // (tests: the first tile's scores are never announced)
+          umma_commit(s_full0 + 8u * st);
         if (j >= 1) ok = issue_pv(j - 1);
       }
       if (ok) issue_pv(n_tiles - 1);
@@ -190,7 +194,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
     for (int j = 0; j < n_tiles && ok; ++j) {
       const int st = j & 1;
       ok = mbar_wait(s_full0 + 8u * st, (j >> 1) & 1);
-      if (!ok && lane == 0) atomicExch(&g_at_status, 7);
+      if (!ok && lane == 0) at_report(7);
       ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
       if (!ok) break;
       tc_fence_after();
@@ -245,7 +249,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
       // The P buffer, and O, belong to P V of the tile before until it is done.
       if (j >= 1) {
         ok = mbar_wait(pv_done, (j - 1) & 1);
-        if (!ok && lane == 0) atomicExch(&g_at_status, 8);
+        if (!ok && lane == 0) at_report(8);
         ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
         if (!ok) break;
         // O is rescaled only when some row of the warp needs it.
@@ -272,7 +276,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
       // the last tile: rows of V past the newest key were never written (or belong to another owner of the page)
       if (key0 + AT_KEYS - 1 > pos_hi) {
         ok = mbar_wait(v_full0 + 8u * st, (j >> 1) & 1);
-        if (!ok && lane == 0) atomicExch(&g_at_status, 9);
+        if (!ok && lane == 0) at_report(9);
         ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
         if (!ok) break;
         const int valid = pos_hi - key0 + 1;
@@ -290,7 +294,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
     // ---------------- normalise and store ----------------
     if (ok) {
       ok = mbar_wait(pv_done, (n_tiles - 1) & 1);
-      if (!ok && lane == 0) atomicExch(&g_at_status, 10);
+      if (!ok && lane == 0) at_report(10);
       ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
     }
     if (ok) {

@@ -90,6 +90,30 @@ extern "C" __attribute__((visibility("default"))) int llmx_timeline_read(unsigne
   return e == cudaSuccess ? (int)n : -(int)e;
 }
 #endif
+// ---------------------------------------------------------------------------
+// Failure reports.  A kernel whose bounded wait ran out (or that met something it cannot do) says so in one
+// word per library, which lives in host memory that the device can write (llmx_set_status_word): the host
+// reads it without a copy whenever it has waited for a step anyway.  The first report since the host last
+// cleared the word stays.
+// ---------------------------------------------------------------------------
+static __device__ int* llmx_status_word;
+__device__ __forceinline__ void llmx_report(int code) {
+  volatile int* p = llmx_status_word;
+  if (p && *p == 0) {
+    *p = code;
+    __threadfence_system();
+  }
+}
+// host_word: one int of page-locked host memory (nullptr: reports stay in the library)
+extern "C" __attribute__((visibility("default"))) int llmx_set_status_word(int* host_word) {
+  void* dev_ptr = nullptr;
+  if (host_word) {
+    cudaError_t e = cudaHostGetDevicePointer(&dev_ptr, host_word, 0);
+    if (e != cudaSuccess) return (int)e;
+  }
+  return (int)cudaMemcpyToSymbol(llmx_status_word, &dev_ptr, sizeof(dev_ptr));
+}
+
 __device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 
 // Whether a launch may overlap the kernel before it (programmatic stream serialization).  The host switches

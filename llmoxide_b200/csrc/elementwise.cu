@@ -27,11 +27,12 @@ __device__ __forceinline__ void store4(bf16* p, float4 v) {
 
 
 // ---------------------------------------------------------------------------
-// Embedding gather: h[t,:] = E[tok_t,:] widened to float32 (no scale).
+// Embedding gather: h[t,:] = E[tok_t,:] widened to float32, times `scale` (1 for the dense Qwen3 decoder,
+// which has none; a product with 1 is exact).
 // ---------------------------------------------------------------------------
 template <typename TW>
 __global__ void embed_kernel(const TW* __restrict__ table, const int* __restrict__ tokens,
-                             float* __restrict__ h, int d, int vocab) {
+                             float* __restrict__ h, int d, int vocab, float scale) {
   pdl_launch_dependents();
   pdl_wait();
   const int t = blockIdx.x;
@@ -42,21 +43,24 @@ __global__ void embed_kernel(const TW* __restrict__ table, const int* __restrict
   if ((d & 3) == 0) {
     // four elements per load, four loads in flight per thread: the row is cold in DRAM
 #pragma unroll 4
-    for (int i = threadIdx.x * 4; i < d; i += blockDim.x * 4) store4(out + i, load4(row + i));
+    for (int i = threadIdx.x * 4; i < d; i += blockDim.x * 4) {
+      float4 v = load4(row + i);
+      store4(out + i, make_float4(v.x * scale, v.y * scale, v.z * scale, v.w * scale));
+    }
     return;
   }
-  for (int i = threadIdx.x; i < d; i += blockDim.x) out[i] = to_f32(row[i]);
+  for (int i = threadIdx.x; i < d; i += blockDim.x) out[i] = to_f32(row[i]) * scale;
 }
 
 LLMX_API int llmx_embed(const void* table, int table_dtype, const int* tokens, float* h,
-                        int n_tokens, int d, int vocab, cudaStream_t stream) {
+                        int n_tokens, int d, int vocab, float scale, cudaStream_t stream) {
   if (n_tokens <= 0) return 0;
   if (d <= 0 || vocab <= 0) return LLMX_REFUSED(1);
   const int threads = d >= 1024 ? 256 : 128;
   if (table_dtype == LLMX_F32)
-    launch_pdl(embed_kernel<float>, dim3(n_tokens), dim3(threads), 0, stream, (const float*)table, tokens, h, d, vocab);
+    launch_pdl(embed_kernel<float>, dim3(n_tokens), dim3(threads), 0, stream, (const float*)table, tokens, h, d, vocab, scale);
   else if (table_dtype == LLMX_BF16)
-    launch_pdl(embed_kernel<bf16>, dim3(n_tokens), dim3(threads), 0, stream, (const bf16*)table, tokens, h, d, vocab);
+    launch_pdl(embed_kernel<bf16>, dim3(n_tokens), dim3(threads), 0, stream, (const bf16*)table, tokens, h, d, vocab, scale);
   else
     return LLMX_REFUSED(2);
   return LLMX_LAUNCH_STATUS();
@@ -639,5 +643,25 @@ LLMX_API int llmx_sum_splits(const void* in, int in_dtype, int n_split, long lon
   else if (in_dtype == LLMX_BF16 && out_dtype == LLMX_F32) CASE(bf16, float);
   else return LLMX_REFUSED(2);
 #undef CASE
+  return LLMX_LAUNCH_STATUS();
+}
+
+// ---------------------------------------------------------------------------
+// Soft cap of logits, in place: x = cap * tanh(x / cap), float32.
+// ---------------------------------------------------------------------------
+__global__ void softcap_kernel(float* __restrict__ x, size_t n, float cap) {
+  pdl_launch_dependents();
+  pdl_wait();
+  for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x)
+    x[i] = cap * tanhf(x[i] / cap);
+}
+
+LLMX_API int llmx_softcap(float* x, long long n, float cap, cudaStream_t stream) {
+  if (n <= 0) return 0;
+  if (!(cap > 0.f)) return LLMX_REFUSED(1);
+  const int threads = 256;
+  const long long want = (n + threads - 1) / threads;
+  const int blocks = (int)(want < 148 * 16 ? want : 148 * 16);
+  launch_pdl(softcap_kernel, dim3(blocks), dim3(threads), 0, stream, x, (size_t)n, cap);
   return LLMX_LAUNCH_STATUS();
 }

@@ -32,6 +32,11 @@
 #define TC_THREADS 192
 
 __device__ int g_tc_status = 0;   // 0, or which bounded wait ran out: 1 producer, 2 MMA, 3 epilogue, 4 MMA on the accumulator
+                                  // (11..14: the same roles of the CTA-pair kernel)
+__device__ __forceinline__ void tc_report(int code) {
+  atomicExch(&g_tc_status, code);
+  llmx_report(code);
+}
 
 // Instruction descriptor: bf16 x bf16 -> f32, both operands K-major, M = 128.
 __host__ __device__ constexpr uint32_t umma_idesc(int n) {
@@ -198,7 +203,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
         for (; i < n_kb; ++i, ++it) {
           const int s = it % n_stages;
           const uint32_t parity = ((it / n_stages) & 1) ^ 1;
-          if (!mbar_wait(empty0 + 8u * s, parity)) { atomicExch(&g_tc_status, 1); ok = false; break; }
+          if (!mbar_wait(empty0 + 8u * s, parity)) { tc_report(1); ok = false; break; }
           const uint32_t stage = base + (uint32_t)s * STAGE_BYTES;
           const uint32_t bar = full0 + 8u * s;
           mbar_expect_tx(bar, STAGE_BYTES);
@@ -221,12 +226,12 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
         const int buf = j % ACC_BUFS, use = j / ACC_BUFS;
         const uint32_t acc_addr = tmem_base + (uint32_t)buf * ACC_COLS;
         // the epilogue must have drained this accumulator set (ACC_BUFS units ago)
-        if (!mbar_wait(acc_empty0 + 8u * buf, (use & 1) ^ 1)) { atomicExch(&g_tc_status, 4); ok = false; break; }
+        if (!mbar_wait(acc_empty0 + 8u * buf, (use & 1) ^ 1)) { tc_report(4); ok = false; break; }
         tc_fence_after();
         for (int i = 0; i < n_kb; ++i, ++it) {
           const int s = it % n_stages;
           const uint32_t parity = (it / n_stages) & 1;
-          if (!mbar_wait(full0 + 8u * s, parity)) { atomicExch(&g_tc_status, 2); ok = false; break; }
+          if (!mbar_wait(full0 + 8u * s, parity)) { tc_report(2); ok = false; break; }
           tc_fence_after();
           const uint32_t stage = base + (uint32_t)s * STAGE_BYTES;
 #pragma unroll
@@ -238,7 +243,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
           }
           umma_commit(empty0 + 8u * s);   // the stage is free once these MMAs have read it
         }
-        umma_commit(acc_full0 + 8u * buf);  // this unit's accumulator is complete once every MMA has finished
+        // (tests: with llmx_withhold the first unit's accumulator is never announced, and the epilogue's wait runs out)
+        if (!(j == 0 && llmx_withhold))
+          umma_commit(acc_full0 + 8u * buf);  // this unit's accumulator is complete once every MMA has finished
       }
     }
   } else {
@@ -253,7 +260,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
       const int buf = j % ACC_BUFS, use = j / ACC_BUFS;
       if (!failed) {
         bool ok = mbar_wait(acc_full0 + 8u * buf, use & 1);
-        if (!ok && lane == 0) atomicExch(&g_tc_status, 3);
+        if (!ok && lane == 0) tc_report(3);
         failed = __shfl_sync(0xffffffffu, ok ? 0 : 1, 0) != 0;
       }
       if (failed && MODE != 2) break;   // MODE 2 keeps walking (without loads or stores): its warps meet at a barrier
@@ -319,9 +326,9 @@ __device__ __forceinline__ bool mbar_try_wait_cluster(uint32_t bar, uint32_t par
 }
 __device__ __forceinline__ bool mbar_wait_cluster(uint32_t bar, uint32_t parity) {
   if (mbar_try_wait_cluster(bar, parity)) return true;
-  const long long t0 = clock64();
+  const long long t0 = clock64(), limit = llmx_wait_cycles;
   while (!mbar_try_wait_cluster(bar, parity)) {
-    if (clock64() - t0 > TC_WAIT_CYCLES) return false;
+    if (clock64() - t0 > limit) return false;
   }
   return true;
 }
@@ -455,7 +462,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
         for (; i < total_kb; ++i, ++it) {
           const int s = it % n_stages;
           const uint32_t parity = ((it / n_stages) & 1) ^ 1;
-          if (!mbar_wait_cluster(empty0 + 8u * s, parity)) { atomicExch(&g_tc_status, 11); ok = false; break; }
+          if (!mbar_wait_cluster(empty0 + 8u * s, parity)) { tc_report(11); ok = false; break; }
           const uint32_t stage = base + (uint32_t)s * STAGE_BYTES, bar = leader_full0 + 8u * s;
           mbar_remote_expect_tx(bar, STAGE_BYTES);
           tma_load_2d_pair(stage, &map_w, i * TC_BK, n0, bar);
@@ -473,11 +480,11 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
       for (int u = pair; u < n_units && ok; u += n_pairs, ++j) {
         const int buf = j % ACC_BUFS, use = j / ACC_BUFS;
         const uint32_t acc_addr = tmem_base + (uint32_t)buf * ACC_COLS;
-        if (!mbar_wait_cluster(acc_empty0 + 8u * buf, (use & 1) ^ 1)) { atomicExch(&g_tc_status, 14); ok = false; break; }
+        if (!mbar_wait_cluster(acc_empty0 + 8u * buf, (use & 1) ^ 1)) { tc_report(14); ok = false; break; }
         tc_fence_after();
         for (int i = 0; i < total_kb; ++i, ++it) {
           const int s = it % n_stages;
-          if (!mbar_wait_cluster(full0 + 8u * s, (it / n_stages) & 1)) { atomicExch(&g_tc_status, 12); ok = false; break; }
+          if (!mbar_wait_cluster(full0 + 8u * s, (it / n_stages) & 1)) { tc_report(12); ok = false; break; }
           tc_fence_after();
           const uint32_t stage = base + (uint32_t)s * STAGE_BYTES;
 #pragma unroll
@@ -490,7 +497,8 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
           }
           umma_commit_pair(empty0 + 8u * s);
         }
-        umma_commit_pair(acc_full0 + 8u * buf);
+        if (!(j == 0 && llmx_withhold))     // (tests: the first unit's accumulator is never announced)
+          umma_commit_pair(acc_full0 + 8u * buf);
       }
     }
   } else {
@@ -505,7 +513,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
       const int buf = j % ACC_BUFS, use = j / ACC_BUFS;
       if (!failed) {
         bool ok = mbar_wait_cluster(acc_full0 + 8u * buf, use & 1);
-        if (!ok && lane == 0) atomicExch(&g_tc_status, 13);
+        if (!ok && lane == 0) tc_report(13);
         failed = __shfl_sync(0xffffffffu, ok ? 0 : 1, 0) != 0;
       }
       if (failed && MODE != 2) break;

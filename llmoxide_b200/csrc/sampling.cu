@@ -107,7 +107,7 @@ sample_kernel(float* __restrict__ logits, long long ld, int V, const float* __re
   if (k <= 0 || k >= V) {
     // ---- whole vocabulary, id order (needs top_p >= 1) -------------------
     if (tp < 1.0f && V > SMP_MAX_K) {
-      if (tid == 0) { out_tokens[b] = arg_best; atomicExch(status, 1); }
+      if (tid == 0) { out_tokens[b] = arg_best; *(volatile int*)status = 1; }
       return;
     }
     if (V > SMP_MAX_K) {
@@ -166,7 +166,7 @@ sample_kernel(float* __restrict__ logits, long long ld, int V, const float* __re
     k = V;  // small vocabulary: the sorted algorithm covers it
   }
   if (k > SMP_MAX_K) {
-    if (tid == 0) { out_tokens[b] = arg_best; atomicExch(status, 2); }
+    if (tid == 0) { out_tokens[b] = arg_best; *(volatile int*)status = 2; }
     return;
   }
   if (k > n_finite) k = n_finite;

@@ -9,6 +9,19 @@
 
 #define TC_WAIT_CYCLES 4000000000ll   // about two seconds: far beyond any legitimate wait
 
+// The limit of every bounded wait, and a switch for tests: with llmx_withhold non-zero one role of a kernel
+// leaves out a single arrival, so that the wait for it runs out, is reported, and the kernel winds down through
+// its normal exit (nothing traps, faults or spins past the limit).  llmx_test_waits(cycles, withhold) sets both;
+// cycles <= 0 puts the default back.
+static __device__ long long llmx_wait_cycles = TC_WAIT_CYCLES;
+static __device__ int llmx_withhold = 0;
+extern "C" __attribute__((visibility("default"))) int llmx_test_waits(long long cycles, int withhold) {
+  if (cycles <= 0) cycles = TC_WAIT_CYCLES;
+  cudaError_t e = cudaMemcpyToSymbol(llmx_wait_cycles, &cycles, sizeof(cycles));
+  if (e == cudaSuccess) e = cudaMemcpyToSymbol(llmx_withhold, &withhold, sizeof(withhold));
+  return (int)e;
+}
+
 // ---------------------------------------------------------------------------
 // PTX wrappers
 // ---------------------------------------------------------------------------
@@ -34,9 +47,9 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
 // Bounded wait: false when the limit ran out.
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
   if (mbar_try_wait(bar, parity)) return true;
-  const long long t0 = clock64();
+  const long long t0 = clock64(), limit = llmx_wait_cycles;
   while (!mbar_try_wait(bar, parity)) {
-    if (clock64() - t0 > TC_WAIT_CYCLES) return false;
+    if (clock64() - t0 > limit) return false;
   }
   return true;
 }

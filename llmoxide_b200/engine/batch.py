@@ -18,6 +18,7 @@ import numpy as np
 import torch
 
 from ..cache import PAGE
+from ..guard import guarded
 
 
 def _align(n: int, a: int = 4) -> int:
@@ -133,7 +134,7 @@ class StepBuffers:
         self.hosts = [torch.empty(capacity, dtype=torch.int32).pin_memory() for _ in range(self.RING)]
         self.events = [None] * self.RING
         self.turn = 0
-        self.dev = torch.empty(capacity, dtype=torch.int32, device=self.device)
+        self.dev = guarded((capacity,), torch.int32, self.device, "step buffer")
 
     def upload(self, lay: StepLayout, buf: np.ndarray, facts: dict) -> StepContext:
         if lay.total > self.capacity:

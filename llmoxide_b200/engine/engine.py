@@ -128,7 +128,7 @@ class Engine:
             ctx.tokens.copy_(feed_tokens)      # on the stream, after the step buffer's copy
         replayed = bool(self.options.cuda_graphs and ctx.is_decode and self.model.graph_safe)
         if replayed:
-            logits = self._graphed_forward(lay, ctx)
+            logits = self._graphed_forward(lay, ctx, [slot for slot, _ in entries])
         elif ctx.is_decode or self.options.overlap_prompt_kernels:
             logits = self.model.forward(ctx, self.cache)
         else:
@@ -187,18 +187,25 @@ class Engine:
         lay, buf, facts = build_host_arrays(entries, want, lengths, page_rows, n_groups)
         return lay, self.buffers.upload(lay, buf, facts)
 
-    def _graphed_forward(self, lay, ctx):
+    def _graphed_forward(self, lay, ctx, slots):
         """Decode steps are launch-bound, so the whole forward of a decode
         step is captured once per batch shape as a CUDA graph and replayed.
         The step's inputs live in the step buffer at offsets that depend on
-        the shape alone, so a replay reads the new step's data.  Running the
-        same step again is harmless (it rewrites the same cache rows), which
-        lets the first occurrence run eagerly, then under capture, then as a
-        replay."""
+        the shape alone, so a replay reads the new step's data.  The first
+        occurrence of a shape runs eagerly once (libraries load, workspaces
+        get their sizes), is then captured (which executes nothing) and
+        replayed.  Running a step twice rewrites the same keys and values,
+        which is harmless, but would advance per-sequence state of fixed
+        size twice: the state rows of the step's slots are put back after
+        the eager run."""
         key = (lay.key(), self.buffers.dev.data_ptr())
         entry = self._graphs.get(key)
         if entry is None:
+            rows = torch.as_tensor(slots, dtype=torch.long, device=self.device)
+            saved = [(st, st[rows].clone()) for st in self.cache.state_store if st is not None]
             self.model.forward(ctx, self.cache)            # warm-up: loads libraries, sizes workspaces
+            for st, old_rows in saved:
+                st[rows] = old_rows
             torch.cuda.current_stream().synchronize()
             before = kernels.launch_count
             graph = torch.cuda.CUDAGraph()
@@ -242,6 +249,12 @@ class Engine:
                 raise ValueError("a fed step takes one token per sequence of the step before")
             logits, _ = self._step(entries, feed_tokens=feed.dev[: feed.n])
         return self._sampler.launch(logits, samplings, recents, uniforms)
+
+    def check_status(self) -> None:
+        """Raises ``KernelError`` if a kernel of an earlier step reported a failure (a bounded wait that ran
+        out).  ``step`` returns without waiting for the GPU, so a caller asks once it has read the step's
+        logits; the generation loop and trace replay do."""
+        kernels.check_status()
 
     # ---- facts -------------------------------------------------------------------
 

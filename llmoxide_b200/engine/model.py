@@ -3,38 +3,37 @@ registries, run in the order of the spec's schedule.  Nothing here names an
 architecture.
 
 Forward of one step, in the reference's order
-(crates/model/src/qwen35/cpu.rs:129-136,138-400,406-416): embedding gather
-without scale; the scheduled layer calls on the float32 residual stream;
-final norm and head on the wanted rows only (the reference takes the last
-row, cpu.rs:410-414)."""
+(crates/model/src/qwen35/cpu.rs:129-136,138-400,406-416): the embedding part
+fills the float32 residual stream; the scheduled layer calls run on it; the
+final norm and the head part run on the wanted rows only (the reference takes
+the last row, cpu.rs:410-414)."""
 
 from __future__ import annotations
 
 import torch
 
-from .. import kernels
 from ..cache import Cache
 from ..config.spec import ModelSpec
-from ..parts import Linear, Runtime, build_block
+from ..parts import Runtime, build_block
 from ..parts.block import build_part
-from ..parts.registry import NORMS
+from ..parts.registry import EMBEDDINGS, HEADS, NORMS
 
 
 class DecoderModel:
     def __init__(self, spec: ModelSpec, weights: dict, rt: Runtime):
         """``weights``: name -> device tensor; the parts take theirs out of it."""
         self.spec, self.rt = spec, rt
-        self.embedding = weights[spec.embedding.name]
-        head = weights.pop(spec.head.name) if spec.head is not None else self.embedding
+        self.embedding = build_part(EMBEDDINGS, "embedding", spec.embedding, weights, rt)
         self.blocks = [build_block(b, weights, rt) for b in spec.blocks]
         self.final_norm = build_part(NORMS, "norm", spec.final_norm, weights, rt)
-        self.head = Linear(head, rt)
-        weights.pop(spec.embedding.name, None)
+        self.head = build_part(HEADS, "head", spec.head, weights, rt, self.embedding)
+        for t in spec.embedding.tensors.values():       # the embedding left its tensors in for a tied head
+            weights.pop(t.name, None)
         self._check_schedule()
         # A part that reads device data on the host during its forward (it says
         # so with ``graph_safe = False``) keeps decode steps out of CUDA graphs.
-        self.graph_safe = all(getattr(p, "graph_safe", True)
-                              for b in self.blocks for p in vars(b).values())
+        self.graph_safe = (all(getattr(p, "graph_safe", True) for b in self.blocks for p in vars(b).values())
+                           and all(getattr(p, "graph_safe", True) for p in (self.embedding, self.head, self.final_norm)))
 
     def _check_schedule(self):
         writers = {}
@@ -53,7 +52,9 @@ class DecoderModel:
     def libraries(self) -> set:
         """The CUDA libraries this model's parts say they launch (a part without ``libraries()`` says
         nothing, and its libraries are loaded at their first use)."""
-        libs = {"elementwise"} | self.head.libraries() | getattr(self.final_norm, "libraries", set)()
+        libs = {"elementwise"}
+        for part in (self.embedding, self.head, self.final_norm):
+            libs |= getattr(part, "libraries", set)()
         for b in self.blocks:
             libs |= getattr(b, "libraries", set)()
         return libs
@@ -70,7 +71,7 @@ class DecoderModel:
         """float32 logits [n_want, vocab] at ``ctx.want_rows``."""
         d = self.spec.hidden_size
         h = torch.empty((ctx.n_tokens, d), dtype=torch.float32, device=self.rt.device)
-        kernels.embed(self.embedding, ctx.tokens, h)
+        self.embedding.forward(ctx.tokens, h)
         pending = None
         for call in self.spec.schedule:
             pending = self.blocks[call.layer].forward(h, pending, ctx, cache.view(call.cache), call.writes_cache)
@@ -78,8 +79,4 @@ class DecoderModel:
         if n_want == 0:
             return torch.empty((0, self.spec.vocab_size), dtype=torch.float32, device=self.rt.device)
         x = self.final_norm.add_forward(h, pending, rows=ctx.want_rows, write_h=False)
-        logits = self.head(x, out_dtype=torch.float32, splits_ok=True)
-        if logits.dim() == 3:       # split partials of the reduction
-            parts, logits = logits, torch.empty(logits.shape[1:], dtype=torch.float32, device=self.rt.device)
-            kernels.sum_splits(parts, logits)
-        return logits
+        return self.head.forward(x)

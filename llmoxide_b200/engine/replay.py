@@ -43,6 +43,7 @@ class Replayer:
             logits = self.engine.step(entries, want)
             if logits.shape[0] > 0:
                 arr = logits.detach().cpu().numpy().astype("<f4", copy=False)
+                self.engine.check_status()        # the copy waited for the step: its kernels' reports are in
                 tmp = self.out / f".{step}.f32.tmp"
                 arr.tofile(tmp)
                 tmp.replace(self.out / f"{step}.f32")

@@ -74,4 +74,6 @@ class ExtensionMissing(LlmoxideError):
 
 
 class KernelError(LlmoxideError):
-    """A kernel launch failed, or a kernel reported that a bounded wait ran out."""
+    """A kernel launch failed, or a kernel reported a failure in its library's status word (a bounded
+    wait that ran out, a request it could not serve); ``kernels.check_status`` raises it when the host
+    has waited for the step."""

@@ -13,6 +13,7 @@ from ctypes import c_float, c_int, c_longlong, c_void_p
 
 import torch
 
+from . import guard
 from .csrc.build import load_library
 from .errors import ExtensionMissing, KernelError, Unsupported
 
@@ -83,6 +84,7 @@ def _library(lib_name: str):
     one another may still be pending.  So the first use of a library waits for the GPU to drain and makes the
     module resident (``llmx_touch``) before anything of it is launched; an engine names its libraries when it
     is built (``preload``), so that no step has to."""
+    global launch_count
     lib = load_library(lib_name)
     if lib_name not in _libs_ready:
         if torch.cuda.is_available() and not torch.cuda.is_current_stream_capturing():
@@ -91,11 +93,79 @@ def _library(lib_name: str):
             if touch is not None:
                 touch.restype = c_int
                 _check(touch(), f"loading {lib_name}")
+                launch_count -= 1
             torch.cuda.synchronize()
-        _libs_ready.add(lib_name)
+            if lib_name in _STATUS_SLOTS and hasattr(lib, "llmx_set_status_word"):
+                lib.llmx_set_status_word.argtypes = [c_void_p]
+                lib.llmx_set_status_word.restype = c_int
+                _check(lib.llmx_set_status_word(c_void_p(status_word(lib_name).data_ptr())),
+                       f"registering the status word of {lib_name}")
+                launch_count -= 1
+            _libs_ready.add(lib_name)
         if hasattr(lib, "llmx_set_pdl"):
             lib.llmx_set_pdl(int(_overlap))
     return lib
+
+
+# ---- failure reports -------------------------------------------------------
+# One word per library in page-locked host memory that its kernels can write: a bounded wait that ran out,
+# or a request a kernel could not serve, leaves a code there.  The host looks at the words whenever it has
+# waited for a step anyway (no copy, no extra synchronisation).
+
+_STATUS_SLOTS = {"gemm_tc": 0, "attention_prefill_tc": 1, "attention_decode": 2, "sampling": 3}
+_STATUS_MEANING = {
+    "gemm_tc": {1: "the producer's wait for a free stage ran out", 2: "the MMA issuer's wait for a stage's data ran out",
+                3: "the epilogue's wait for an accumulator ran out", 4: "the MMA issuer's wait for a drained accumulator ran out",
+                11: "CTA pair: the producer's wait for a free stage ran out", 12: "CTA pair: the MMA issuer's wait for a stage's data ran out",
+                13: "CTA pair: the epilogue's wait for an accumulator ran out",
+                14: "CTA pair: the MMA issuer's wait for a drained accumulator ran out"},
+    "attention_prefill_tc": {20: "its shared memory is not 1024-byte aligned"},
+    "attention_decode": {1: "a copy into shared memory never completed", 2: "its shared memory is not 1024-byte aligned"},
+    "sampling": {1: "top_p < 1 over more candidates than the kernel sorts", 2: "top_k beyond what the kernel sorts"},
+}
+_status_host = None
+
+
+def status_words() -> torch.Tensor:
+    """The page-locked int32 words, one per library that reports (see ``_STATUS_SLOTS``)."""
+    global _status_host
+    if _status_host is None:
+        _status_host = torch.zeros(8, dtype=torch.int32).pin_memory()
+    return _status_host
+
+
+def status_word(lib_name: str) -> torch.Tensor:
+    i = _STATUS_SLOTS[lib_name]
+    return status_words()[i : i + 1]
+
+
+def check_status() -> None:
+    """Raises ``KernelError`` if a kernel has left a report since the last call, and clears it.  Meaningful
+    once the host has waited for the work in question (the words are written as the failure happens)."""
+    if _status_host is None:
+        return
+    words = _status_host.numpy()
+    if not words.any():
+        return
+    found = []
+    for name, i in _STATUS_SLOTS.items():
+        code = int(words[i])
+        if code:
+            what = _STATUS_MEANING.get(name, {}).get(code, "a bounded wait ran out")
+            found.append(f"{name}: {what} (code {code})")
+    words[:] = 0
+    raise KernelError("a kernel reported a failure; the step's results are not to be used: " + "; ".join(found))
+
+
+def test_waits(lib_name: str, cycles: int = 0, withhold: bool = False) -> None:
+    """For tests of the failure path: the limit of the library's bounded waits in clock cycles (0: the default
+    of about two seconds) and whether one role leaves out one arrival, so that a wait runs out, is reported
+    and the kernel winds down through its normal exit."""
+    f = _fn(lib_name, "llmx_test_waits", [c_longlong, c_int])
+    torch.cuda.synchronize()
+    code = f(int(cycles), int(withhold))
+    if code:
+        raise KernelError(f"{lib_name}: CUDA error {code} setting the wait limit")
 
 
 def set_overlap(on: bool) -> None:
@@ -132,15 +202,24 @@ def preload(lib_names) -> None:
 # ---------------------------------------------------------------------------
 
 
-def embed(table: torch.Tensor, tokens: torch.Tensor, out: torch.Tensor) -> None:
-    """out[t,:] = float32(table[tokens[t],:]).  tokens int32 [T]; out float32 [T,d]."""
+def embed(table: torch.Tensor, tokens: torch.Tensor, out: torch.Tensor, scale: float = 1.0) -> None:
+    """out[t,:] = float32(table[tokens[t],:]) * scale.  tokens int32 [T]; out float32 [T,d]."""
     _dev(table, tokens, out)
     _contig("table", table), _contig("out", out)
     assert tokens.dtype == torch.int32 and out.dtype == torch.float32
     f = _fn("elementwise", "llmx_embed",
-            [c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p])
+            [c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_float, c_void_p])
     _check(f(_ptr(table), _tag(table), _ptr(tokens), _ptr(out), tokens.numel(), table.shape[1],
-             table.shape[0], _stream()), "embed")
+             table.shape[0], scale, _stream()), "embed")
+
+
+def softcap(x: torch.Tensor, cap: float) -> None:
+    """x = cap * tanh(x / cap) in place; x float32, contiguous."""
+    _dev(x)
+    _contig("x", x)
+    assert x.dtype == torch.float32 and cap > 0
+    f = _fn("elementwise", "llmx_softcap", [c_void_p, c_longlong, c_float, c_void_p])
+    _check(f(_ptr(x), x.numel(), cap, _stream()), "softcap")
 
 
 def add_rms_norm(h: torch.Tensor, delta, gain: torch.Tensor, eps: float, out, rows=None,
@@ -241,21 +320,24 @@ def attention_paged(q, out, k_cache, v_cache, block_table, token_seq, token_pos,
              int(window or 0), scale, _stream()), "attention_paged")
 
 
-N_SM = 148
+def n_sm(device=None) -> int:
+    """Streaming multiprocessors of the device (asked once)."""
+    from .parts.runtime import kernels_n_sm
+    return kernels_n_sm(device if device is not None else "cuda")
 
 
-def decode_chunks(n_seqs: int, n_kv_heads: int, group: int, n_pages: int) -> int:
+def decode_chunks(n_seqs: int, n_kv_heads: int, group: int, n_pages: int, sms: int = 148) -> int:
     """Into how many shares the decode attention kernel cuts every sequence's
     visible keys.  A CTA (two warps) takes one share of one (sequence, kv head,
     8 query heads); two CTAs fit an SM, and the whole grid should be resident
-    at once, so the shares are as many as that allows, up to 8 (the CTAs of a
-    sequence and kv head then merge as one thread-block cluster), and never
-    more than would leave a warp without a 32-key tile of a full block table.  It depends
-    on the batch's shape only (not on its lengths), so a captured graph stays
-    valid while the shape does; each sequence's own length is divided on the
-    device."""
+    at once, so the shares are as many as that allows on ``sms`` multiprocessors,
+    up to 8 (the CTAs of a sequence and kv head then merge as one thread-block
+    cluster), and never more than would leave a warp without a 32-key tile of a
+    full block table.  It depends on the batch's shape only (not on its
+    lengths), so a captured graph stays valid while the shape does; each
+    sequence's own length is divided on the device."""
     base = n_seqs * n_kv_heads * ((group + 7) // 8)
-    return max(1, min(2 * N_SM // base, n_pages, 8))
+    return max(1, min(2 * sms // base, n_pages, 8))
 
 
 _decode_counters: dict = {}
@@ -266,7 +348,7 @@ def _counters(device, n: int):
     every launch leaves them zero, so one buffer per device serves all calls."""
     buf = _decode_counters.get(device)
     if buf is None or buf.numel() < n:
-        buf = torch.zeros(max(n, 16384), dtype=torch.int32, device=device)
+        buf = guard.guarded((max(n, 16384),), torch.int32, device, "decode attention counters", zero=True)
         _decode_counters[device] = buf
     return buf
 
@@ -287,10 +369,11 @@ def attention_decode(q, out, k_cache, v_cache, block_table, seq_past, n_heads: i
     if window:
         n_pages = min(n_pages, (window + PAGE - 2) // PAGE + 1)
     group = n_heads // n_kv_heads
-    n_chunks = n_chunks or decode_chunks(B, n_kv_heads, group, n_pages)
+    n_chunks = n_chunks or decode_chunks(B, n_kv_heads, group, n_pages, n_sm(q.device))
     ws = counters = None
     if n_chunks > 8:
-        ws = torch.empty(B * n_heads * n_chunks * (head_dim + 4), dtype=torch.float32, device=q.device)
+        ws = guard.scratch((B * n_heads * n_chunks * (head_dim + 4),), torch.float32, q.device,
+                           "decode attention workspace")
         counters = _counters(q.device, B * n_kv_heads * ((group + 7) // 8))
     f = _fn("attention_decode", "llmx_attention_decode",
             [c_void_p, c_void_p, c_void_p, c_void_p, c_longlong, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int,
@@ -443,9 +526,12 @@ def argmax(logits: torch.Tensor, out_tokens: torch.Tensor) -> None:
 def sample(logits, temperature, top_k, top_p, repeat_penalty, recent, uniform, out_tokens, status) -> None:
     """One token per row of float32 ``logits`` [B,V] (changed in place by the
     repetition penalty).  Per-row parameters are device tensors [B]; ``recent``
-    is int32 [B,W] with -1 for no token, or None.  ``status`` int32 [1] is set
-    non-zero when a row asked for what the kernel cannot do."""
-    _dev(logits, temperature, top_k, top_p, repeat_penalty, recent, uniform, out_tokens, status)
+    is int32 [B,W] with -1 for no token, or None.  ``status`` int32 [1] (on the
+    device or page-locked on the host) is set non-zero when a row asked for what
+    the kernel cannot do."""
+    _dev(logits, temperature, top_k, top_p, repeat_penalty, recent, uniform, out_tokens)
+    if not (status.is_cuda or status.is_pinned()):
+        raise KernelError("the sampler's status word must be on the GPU or in page-locked host memory")
     assert logits.dtype == torch.float32 and logits.stride(1) == 1
     assert temperature.dtype == torch.float32 and top_p.dtype == torch.float32 and uniform.dtype == torch.float32
     assert top_k.dtype == torch.int32 and out_tokens.dtype == torch.int32 and status.dtype == torch.int32

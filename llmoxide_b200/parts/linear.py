@@ -20,7 +20,7 @@ class Linear:
         self._tc = None
         if rt.tensor_cores and weight.dtype == torch.bfloat16 and rt.dtype == "bfloat16":
             from . import linear_tc
-            self._tc = linear_tc.plan_for(weight)
+            self._tc = linear_tc.plan_for(weight, rt.n_sm)
 
     def libraries(self) -> set:
         return {"gemm_tc", "elementwise"} if self._tc is not None else {"gemm_fma"}

@@ -12,18 +12,18 @@ from __future__ import annotations
 import torch
 
 from .. import kernels
+from ..guard import scratch
 
-N_SM = 148
 TILE_ROWS = 128
 CTAS_PER_SM = 2               # what the kernel fits per SM at decode tile sizes
 MIN_KBLOCKS_PER_SPLIT = 4     # 64-element blocks of K per split, at least
 PAIR_MIN_TOKENS = 128         # above this, CTA pairs (tcgen05 cta_group::2) share each token tile
 
 
-def choose_splits(n_rows: int, k: int, n_tokens: int, max_splits: int = 16) -> int:
+def choose_splits(n_rows: int, k: int, n_tokens: int, n_sm: int = 148, max_splits: int = 16) -> int:
     """How many ways to split the reduction over K at ``n_tokens`` tokens, from
     a small time model of the streaming kernel (microseconds): CTAs run in
-    rounds of N_SM * CTAS_PER_SM; a CTA streams its share of the weights at
+    rounds of n_sm * CTAS_PER_SM; a CTA streams its share of the weights at
     the HBM rate divided by the CTAs running, but never faster than one CTA
     can pull; every round costs a fixed start and drain; float32 partials are
     written once and read once by the kernel that consumes them."""
@@ -31,7 +31,7 @@ def choose_splits(n_rows: int, k: int, n_tokens: int, max_splits: int = 16) -> i
         return 1
     tiles = (n_rows + TILE_ROWS - 1) // TILE_ROWS
     k_blocks = (k + 63) // 64
-    slots = N_SM * CTAS_PER_SM
+    slots = n_sm * CTAS_PER_SM
     hbm, one_cta, fixed = 6.5e6, 2.5e4, 4.0          # bytes per microsecond; microseconds
     best, best_t = 1, None
     for s in range(1, min(max_splits, max(1, k_blocks // MIN_KBLOCKS_PER_SPLIT)) + 1):
@@ -47,8 +47,8 @@ def choose_splits(n_rows: int, k: int, n_tokens: int, max_splits: int = 16) -> i
 
 
 class TensorCoreLinear:
-    def __init__(self, weight: torch.Tensor):
-        self.weight = weight
+    def __init__(self, weight: torch.Tensor, n_sm: int = 148):
+        self.weight, self.n_sm = weight, n_sm
         self.N, self.K = weight.shape
 
     def __call__(self, x, out_dtype, splits_ok):
@@ -57,24 +57,24 @@ class TensorCoreLinear:
             out = torch.empty((T, self.N), dtype=out_dtype, device=x.device)
             kernels.gemm_fma(x, self.weight, out)
             return out
-        s = choose_splits(self.N, self.K, T) if splits_ok else 1
+        s = choose_splits(self.N, self.K, T, self.n_sm) if splits_ok else 1
         if s > 1:
-            out = torch.empty((s, T, self.N), dtype=torch.float32, device=x.device)
+            out = scratch((s, T, self.N), torch.float32, x.device, "split partials of a matrix product")
             kernels.gemm_tc(x, self.weight, out, n_split=s)
             return out
-        out = torch.empty((T, self.N), dtype=out_dtype, device=x.device)
+        out = scratch((T, self.N), out_dtype, x.device, "output of a matrix product")
         kernels.gemm_tc(x, self.weight, out, pair=T > PAIR_MIN_TOKENS)
         return out
 
     def gated(self, x, out_dtype, block: int = 0):
         """silu(gate x) * (up x), [T, N/2]; ``block`` = 0 for weight = [gate rows; up rows], 64 for
         blocks of 64 gate rows each followed by the 64 up rows of the same features."""
-        out = torch.empty((x.shape[0], self.N // 2), dtype=out_dtype, device=x.device)
+        out = scratch((x.shape[0], self.N // 2), out_dtype, x.device, "output of the gated matrix product")
         kernels.gemm_tc(x, self.weight, out, gated=2 if block == 64 else 1, pair=x.shape[0] > PAIR_MIN_TOKENS)
         return out
 
 
-def plan_for(weight: torch.Tensor):
+def plan_for(weight: torch.Tensor, n_sm: int = 148):
     if weight.dtype != torch.bfloat16 or weight.stride(1) != 1 or weight.shape[1] % 8 or weight.stride(0) % 8:
         return None
-    return TensorCoreLinear(weight)
+    return TensorCoreLinear(weight, n_sm)

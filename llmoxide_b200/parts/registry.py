@@ -4,6 +4,13 @@ test can register a toy part without touching this package).
 
 Interfaces (``rt`` is the ``Runtime``: device, compute dtype, limits):
 
+``Embedding(spec, weights, rt)``
+    ``forward(tokens, h)``: writes the float32 residual stream ``h`` [T,d] for
+    the int32 token ids [T]; ``table`` is the matrix a tied head may share
+    (None if there is none to share).
+``Head(spec, weights, rt, embedding)``
+    ``forward(x) -> logits``: float32 [n, vocab] for the normalised rows ``x``
+    [n,d] in the compute dtype; ``embedding`` is the model's embedding part.
 ``Norm(spec, weights, rt)``
     ``add_forward(h, delta, rows=None, write_h=True) -> x``: adds ``delta``
     (None, [T,d] or split partials [S,T,d]) to the float32 residual stream
@@ -35,6 +42,8 @@ from __future__ import annotations
 
 from ..errors import ConfigError
 
+EMBEDDINGS: dict = {}
+HEADS: dict = {}
 MIXERS: dict = {}
 FEED_FORWARDS: dict = {}
 NORMS: dict = {}
@@ -52,6 +61,8 @@ def _register(table, family):
     return deco_factory
 
 
+register_embedding = _register(EMBEDDINGS, "embedding")
+register_head = _register(HEADS, "head")
 register_mixer = _register(MIXERS, "mixer")
 register_feed_forward = _register(FEED_FORWARDS, "feed-forward")
 register_norm = _register(NORMS, "norm")

@@ -14,6 +14,7 @@ import torch
 
 from .. import kernels
 from ..errors import KernelError, Unsupported
+from ..guard import guarded
 
 # How long the host waits for a step's tokens before it gives up with an error instead of waiting for ever.
 STEP_TIMEOUT_S = float(os.environ.get("LLMX_STEP_TIMEOUT_S", "120"))
@@ -42,6 +43,7 @@ class SampledTokens:
                         f"waits for something that does not come, or the GPU is lost")
                 if waited > 0.05:
                     time.sleep(0.001)          # a long step (a prompt): stop spinning
+        kernels.check_status()      # a kernel of the step may have reported that a bounded wait ran out
         return self._host[: self.n].tolist()
 
 
@@ -52,15 +54,16 @@ class DeviceSampler:
         self._cap = 0
         self._turn = 0
         self._grow(max_rows)
-        self.status = torch.zeros(1, dtype=torch.int32, device=device)
+        # what a sampling kernel cannot do is reported in the library's word, which the host reads with the tokens
+        self.status = kernels.status_word("sampling")
 
     def _grow(self, rows: int, width: int = 64):
         torch.cuda.current_stream().synchronize()      # nothing in flight may still use the old buffers
         self._cap, self._width = rows, width
         n = rows * (5 + width)
         self._params_host = [torch.empty(n, dtype=torch.int32).pin_memory() for _ in range(RING)]
-        self._params_dev = [torch.empty(n, dtype=torch.int32, device=self.device) for _ in range(RING)]
-        self._tokens_dev = [torch.empty(rows, dtype=torch.int32, device=self.device) for _ in range(RING)]
+        self._params_dev = [guarded((n,), torch.int32, self.device, f"sampler parameters {i}") for i in range(RING)]
+        self._tokens_dev = [guarded((rows,), torch.int32, self.device, f"sampled tokens {i}") for i in range(RING)]
         self._tokens_host = [torch.empty(rows, dtype=torch.int32).pin_memory() for _ in range(RING)]
         self._events = [None] * RING
 

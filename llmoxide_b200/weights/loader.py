@@ -23,8 +23,6 @@ from ..config.spec import ModelSpec
 from ..errors import WeightsError
 from .safetensors_io import open_checkpoint
 
-# Buffers that exporters write beside the weights and that carry no parameter.
-_IGNORED_SUFFIXES = (".rotary_emb.inv_freq",)
 _FLOATS = ("F32", "F16", "BF16")
 _INTS = ("I64", "I32", "I16", "I8", "U8")
 
@@ -36,11 +34,12 @@ def check_checkpoint(spec: ModelSpec, entries: dict, where="") -> list:
     missing = [n for n in expected if n not in entries]
     unexpected, notes = [], []
     for n in entries:
-        if n in expected or n.endswith(_IGNORED_SUFFIXES):
+        if n in expected:
             continue
-        if spec.head is None and n == "lm_head.weight":
-            # tie_word_embeddings with a head in the file: the table is used.
-            notes.append("lm_head.weight is present but the configuration ties the head to the embedding; ignored")
+        if spec.is_ignored(n):
+            # the description names tensors a file may carry that the model does not use
+            if n in spec.ignored_tensors:
+                notes.append(f"{n} is present but the configuration does not use it; ignored")
             continue
         unexpected.append(n)
     wrong = []

@@ -22,3 +22,18 @@ def pytest_collection_modifyitems(config, items):
     for item in items:
         if "gpu" in item.keywords:
             item.add_marker(skip)
+
+
+@pytest.fixture(autouse=True)
+def _guard_words(request):
+    """After every GPU test: no kernel wrote past the end of a guarded device buffer (the step buffer, the
+    cache groups, per-sequence state, sampler buffers, counters).  Buffers whose owner the test has dropped
+    are held until this check has seen them."""
+    if "gpu" not in request.keywords:
+        yield
+        return
+    from llmoxide_b200 import guard
+
+    guard.hold_until_checked(True)
+    yield
+    guard.check_all()

@@ -68,6 +68,37 @@ def trace_batches(requests, batch_size, prompt_frac=0.5):
     return steps
 
 
+def trace_chunks(requests, chunk, batch_size, tail=8, mixed=False):
+    """Prompts fed in several multi-token steps (a later chunk of a prompt attends over the cache and the
+    chunk itself), several requests per step, then the last ``tail`` tokens one by one.  With ``mixed`` a
+    request goes on to single tokens as soon as its own prompt is through, so a step may hold one request's
+    chunk beside another's single token; without it, the requests that are through wait for the others."""
+    steps, n = [], 0
+    items = list(requests.items())
+    for b in range(0, len(items), batch_size):
+        group = items[b : b + batch_size]
+        fed = {rid: 0 for rid, _ in group}
+        cut = {rid: max(1, len(t) - tail) for rid, t in group}
+        live = list(group)
+        while live:
+            in_prompt = [rid for rid, _ in live if fed[rid] < cut[rid]]
+            entries = []
+            for rid, t in live:
+                if fed[rid] < cut[rid]:
+                    m = min(chunk, cut[rid] - fed[rid])
+                elif mixed or not in_prompt:
+                    m = 1
+                else:
+                    continue
+                entries.append(dict(id=rid, tokens=t[fed[rid] : fed[rid] + m], want=list(range(m))))
+                fed[rid] += m
+            ends = [rid for rid, t in live if fed[rid] == len(t)]
+            steps.append(dict(step=n, entries=entries, end=ends))
+            n += 1
+            live = [(rid, t) for rid, t in live if fed[rid] < len(t)]
+    return steps
+
+
 def collect(steps, out_dir, vocab):
     """{request id: [len, vocab] logits} put together from the step files."""
     got = {}

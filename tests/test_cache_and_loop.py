@@ -355,13 +355,14 @@ def test_a_refused_step_leaves_the_cache_as_it_was():
 def test_decode_attention_share_count_depends_on_the_shape_only():
     """Every sequence's keys are cut into as many shares as keep the whole grid resident at once (two CTAs per
     SM), at most 8 (one thread-block cluster) and never more than a full block table has 32-key tiles for."""
-    from llmoxide_b200.kernels import N_SM, decode_chunks
+    from llmoxide_b200.kernels import decode_chunks
 
-    for n_seqs in (1, 2, 8, 16, 64, 300):
-        for n_kv, group in ((8, 4), (1, 5), (2, 12), (8, 8)):
-            for n_pages in (1, 3, 64, 640):
-                n = decode_chunks(n_seqs, n_kv, group, n_pages)
-                base = n_seqs * n_kv * ((group + 7) // 8)
-                assert 1 <= n <= min(8, n_pages)
-                assert n == 1 or base * n <= 2 * N_SM
+    for n_sm in (148, 132, 20):
+        for n_seqs in (1, 2, 8, 16, 64, 300):
+            for n_kv, group in ((8, 4), (1, 5), (2, 12), (8, 8)):
+                for n_pages in (1, 3, 64, 640):
+                    n = decode_chunks(n_seqs, n_kv, group, n_pages, n_sm)
+                    base = n_seqs * n_kv * ((group + 7) // 8)
+                    assert 1 <= n <= min(8, n_pages)
+                    assert n == 1 or base * n <= 2 * n_sm
     assert decode_chunks(8, 8, 4, 64) == 4 and decode_chunks(64, 8, 4, 64) == 1 and decode_chunks(1, 8, 4, 64) == 8

@@ -102,17 +102,53 @@ def test_temperature_sampling_is_seeded_and_batch_independent(folders):
         assert a.tokens == b.tokens == c.tokens
     other = s.generate([Request(ps[0], 16, samp.with_(seed=99), stop_ids=())])[0]
     assert other.tokens != together[0].tokens
-    # against the plain sampler on the plain implementation's logits
+    # against the plain sampler, step by step, on the plain logits of the engine's own prefix
     cfg, w = plain.read_model(folder)
-    rng, ids, out = plain.Rng(21), list(ps[0]), []
-    for _ in range(16):
+    for i, o in enumerate(together):
+        _check_sampled(cfg, w, ps[i], o.tokens, samp.with_(seed=21 + i))
+
+
+def _check_sampled(cfg, w, prompt, tokens, samp):
+    """Every token is what the plain sampler picks, with the sequence's next draw, from the plain
+    implementation's logits after the prompt and the engine's own tokens before it."""
+    rng, ids = plain.Rng(samp.seed), list(prompt)
+    for n, tok in enumerate(tokens):
         logits = plain.forward(cfg, w, ids)[-1].numpy()
-        tok = plain.sample(logits, out, temperature=0.9, top_k=40, top_p=0.9, repeat_penalty=1.1,
-                           repeat_window=64, u=rng.next_f32())
-        out.append(tok)
+        want = plain.sample(logits, tokens[:n], temperature=samp.temperature, top_k=samp.top_k, top_p=samp.top_p,
+                            repeat_penalty=samp.repeat_penalty, repeat_window=samp.repeat_window, u=rng.next_f32())
+        assert tok == want, (n, tok, want, tokens)
         ids.append(tok)
-    same = sum(a == b for a, b in zip(out, together[0].tokens))
-    assert out[:4] == together[0].tokens[:4] and same >= 12, (out, together[0].tokens)
+
+
+def test_sampling_while_running_one_step_ahead(folders):
+    """Without a repetition penalty the loop launches each decode step before it has read the tokens of the
+    step before, so a sequence's draws are taken a step early, and on the survivors of a batch that loses a
+    neighbour.  Three requests, one of which stops early (after its third token or later) on a stop token of
+    its own."""
+    from llmoxide_b200 import Request, Sampling
+
+    folder = folders[("B", "float32")]
+    cfg, w = plain.read_model(folder)
+    ps = prompts(ALL["B"]["vocab_size"], [12, 5, 40], seed=6)
+    samp = Sampling(temperature=0.8, top_k=30, top_p=0.95, repeat_penalty=1.0, seed=50)
+    s = _session(folder, "float32")
+    ahead = []
+    launch = s.engine.launch_step_sample
+    s.engine.launch_step_sample = lambda *a, feed=None: (ahead.append(feed is not None), launch(*a, feed=feed))[1]
+    reqs = [Request(p, 14, samp.with_(seed=50 + i), stop_ids=()) for i, p in enumerate(ps)]
+    free = s.generate(reqs)
+    assert sum(ahead) >= 10                              # steps really were launched ahead
+    for i, o in enumerate(free):
+        assert o.generated == 14
+        _check_sampled(cfg, w, ps[i], o.tokens, samp.with_(seed=50 + i))
+    # the second request now stops at its fourth token; the others go on in a smaller batch, unchanged
+    k = next(k for k in range(2, 14) if free[1].tokens[k] not in free[1].tokens[:k])
+    reqs[1] = Request(ps[1], 14, samp.with_(seed=51), stop_ids=(free[1].tokens[k],))
+    outs = s.generate(reqs)
+    assert outs[1].tokens == free[1].tokens[: k + 1] and outs[1].reason == "stop"
+    assert outs[0].tokens == free[0].tokens and outs[2].tokens == free[2].tokens
+    s.engine.cache.alloc.check_consistent()
+    assert s.engine.cache.alloc.pages_held() == 0
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])

@@ -505,3 +505,84 @@ def test_attention_decode_many_sequences_one_share_each():
     assert not out.isnan().any()
     for i in range(len(pasts)):
         assert rel(out[i], want[i]) < 1.2e-2, (i, pasts[i])
+
+
+# ---- the window's edge in the bfloat16 kernels ----------------------------------------------------
+
+def _edge_case(D, past, n_new, window, rows):
+    """One sequence, one head.  For every tested new token (``rows``, indices among the new tokens) the key
+    just outside its window is loud and marks one output dim, the key just inside is a little less loud and
+    marks another; each tested row listens on a dim of its own, so that the rows' edges (which may be
+    neighbours) do not disturb one another.  Seeing the outside key, or missing the inside one, changes
+    the marked outputs from (0, 1) to (1, 0) or (0, 0)."""
+    n = past + n_new
+    q = torch.zeros(n, 1, D)
+    k = torch.zeros(n, 1, D)
+    v = torch.zeros(n, 1, D)
+    marks = []
+    for j, r in enumerate(rows):
+        pos = past + r
+        inside, outside = pos - (window - 1), pos - window
+        assert outside >= 0
+        q[pos, 0, j] = 8.0
+        k[outside, 0, j] = 50.0
+        k[inside, 0, j] = 40.0
+        v[outside, 0, 8 + 2 * j] = 1.0
+        v[inside, 0, 9 + 2 * j] = 1.0
+        marks.append((r, 8 + 2 * j, 9 + 2 * j))
+    kc, vc, table = _paged([(k, v)], 1, D, torch.bfloat16, n_pages=(n + PAGE - 1) // PAGE + 3)
+    return q[past:].reshape(n_new, D).bfloat16(), kc, vc, table, marks
+
+
+def _assert_edge(out, marks, what):
+    out = out.float().cpu()
+    for r, dim_out, dim_in in marks:
+        assert float(out[r, dim_out]) < 1e-3, (what, r, "the key just outside the window was seen")
+        assert float(out[r, dim_in]) > 0.999, (what, r, "the key just inside the window was missed")
+
+
+@pytest.mark.parametrize("off", [0, 31, 63])
+@pytest.mark.parametrize("D", [128, 64, 48])
+def test_window_edge_decode_attention(D, off):
+    from llmoxide_b200 import kernels
+    p = 700
+    window = p - (128 + off) + 1                     # the first visible key sits at offset `off` of a page
+    q, kc, vc, table, marks = _edge_case(D, p, 1, window, [0])
+    for n_chunks in (1, 3, 8, 11):
+        out = torch.full((1, D), float("nan"), dtype=torch.bfloat16, device=DEV)
+        kernels.attention_decode(q.to(DEV), out, kc.to(DEV), vc.to(DEV), table.to(DEV),
+                                 torch.tensor([p], dtype=torch.int32, device=DEV), 1, 1, D, window, 1 / math.sqrt(D),
+                                 n_chunks=n_chunks)
+        _assert_edge(out, marks, f"decode, {n_chunks} shares, offset {off}")
+
+
+@pytest.mark.parametrize("off", [0, 31, 63])
+@pytest.mark.parametrize("n_new", [2, 129])
+@pytest.mark.parametrize("kernel, D", [("tcgen05", 128), ("tiled", 128), ("tiled", 64)])
+def test_window_edge_prompt_attention(kernel, D, n_new, off):
+    """A later portion of a prompt (``past`` > 0) of 2 tokens (the edge in the first key tile) and of 129
+    (rows of two query tiles; the edge falls in tiles that only some rows mask)."""
+    from llmoxide_b200 import kernels
+    past = 400
+    window = past - (128 + off) + 1
+    rows = sorted({0, n_new - 1, n_new // 2})
+    q, kc, vc, table, marks = _edge_case(D, past, n_new, window, rows)
+    out = torch.full((n_new, D), float("nan"), dtype=torch.bfloat16, device=DEV)
+    fn = kernels.attention_prefill_tc if kernel == "tcgen05" else kernels.attention_prefill
+    fn(q.to(DEV), out, kc.to(DEV), vc.to(DEV), table.to(DEV), torch.tensor([0, n_new], dtype=torch.int32, device=DEV),
+       torch.tensor([past], dtype=torch.int32, device=DEV), 1, n_new, 1, 1, D, window, 1 / math.sqrt(D))
+    assert not out.isnan().any()
+    _assert_edge(out, marks, f"{kernel} D={D}, {n_new} new tokens, offset {off}")
+
+
+def test_softcap_and_scaled_embedding():
+    from llmoxide_b200 import kernels
+    x = torch.randn(7, 333) * 40
+    d = x.to(DEV)
+    kernels.softcap(d, 30.0)
+    assert rel(d, 30.0 * torch.tanh(x / 30.0)) < 2e-6
+    table = torch.randn(50, 72)
+    toks = torch.tensor([3, 49, 0], dtype=torch.int32)
+    out = torch.empty(3, 72, dtype=torch.float32, device=DEV)
+    kernels.embed(table.to(DEV), toks.to(DEV), out, 8.5)
+    assert torch.equal(out.cpu(), table[toks.long()] * 8.5)

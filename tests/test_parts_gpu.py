@@ -216,14 +216,25 @@ def test_layer_named_twice_and_shared_cache(tmp_path):
 
 def _register_toys():
     from llmoxide_b200.cache import StateNeed
-    from llmoxide_b200.parts import register_feed_forward, register_mixer, register_position
+    from llmoxide_b200.parts import (register_embedding, register_feed_forward, register_mixer,
+                                     register_position)
+
+    @register_embedding("toy_scaled_table")
+    class ScaledTable:
+        """h = table[token] * scale: an embedding with a scale (the dense Qwen3 decoder has none)."""
+
+        def __init__(self, spec, weights, rt):
+            self.table = weights[spec.tensors["table"].name]        # left in: the tied head shares it
+            self.scale = float(spec["scale"])
+
+        def forward(self, tokens, h):
+            h.copy_(self.table[tokens.long()].float() * self.scale)
 
     @register_mixer("toy_running_mean")
     class RunningMean:
-        """y_t = W * mean(x_0..x_t): its state is the running sum and the count,
-        per sequence, of fixed size, kept in the cache's state area."""
-
-        graph_safe = False      # forward reads the batch's layout on the host
+        """y_t = W * mean(x_0..x_t): its state is the running sum and the count, per sequence, of fixed
+        size, kept in the cache's state area.  Everything is computed on the device from the step's own
+        index arrays (no host read), so decode steps with this mixer are captured as CUDA graphs."""
 
         def __init__(self, spec, position, weights, rt):
             self.d = spec["hidden_size"]
@@ -233,17 +244,20 @@ def _register_toys():
             return None, StateNeed((self.d + 1,))
 
         def forward(self, x, ctx, view, writes_cache=True):
-            out = torch.empty_like(x, dtype=torch.float32)
-            starts, slots = ctx.seq_start.tolist(), ctx.seq_slot.tolist()
-            for i, slot in enumerate(slots):
-                seg = x[starts[i] : starts[i + 1]].float()
-                st = view.state[slot]
-                sums = st[: self.d] + seg.cumsum(0)
-                counts = st[self.d] + torch.arange(1, len(seg) + 1, device=x.device)
-                out[starts[i] : starts[i + 1]] = (sums / counts[:, None]) @ self.w.t()
-                if writes_cache:
-                    st[: self.d], st[self.d] = sums[-1], counts[-1]
-            return out
+            d, T = self.d, x.shape[0]
+            seq = ctx.token_seq.long()                               # token -> sequence of the step
+            start = ctx.seq_start.long()
+            idx = torch.arange(T, device=x.device)
+            # running sums inside each sequence's run of tokens (float64, so that the cut does not show)
+            cs = torch.cat([torch.zeros(1, d, dtype=torch.float64, device=x.device), x.double().cumsum(0)])
+            within = (cs[idx + 1] - cs[start[seq]]).float()
+            n_within = (idx - start[seq] + 1).float()
+            state = view.state[ctx.seq_slot.long()[seq]]             # [T, d + 1]: each token's sequence state
+            sums, counts = state[:, :d] + within, state[:, d] + n_within
+            if writes_cache:
+                last = start[1:] - 1                                 # every sequence's last token
+                view.state.index_copy_(0, ctx.seq_slot.long(), torch.cat([sums[last], counts[last, None]], dim=1))
+            return (sums / counts[:, None]) @ self.w.t()
 
     @register_feed_forward("toy_routed")
     class Routed:
@@ -267,13 +281,14 @@ def _register_toys():
 
         def __init__(self, spec, weights, rt):
             self.n_rot, self.base, self.rt = spec["n_rot"], spec["base"], rt
-
-        def rotary_tables(self):
             half = self.n_rot // 2
             pos = torch.arange(self.rt.max_positions, dtype=torch.float64) / 2
             freq = self.base ** (-2.0 * torch.arange(half, dtype=torch.float64) / self.n_rot)
             ang = pos[:, None] * freq[None, :]
-            return ang.cos().float().to(DEV), ang.sin().float().to(DEV), self.n_rot
+            self.tables = ang.cos().float().to(DEV), ang.sin().float().to(DEV), self.n_rot
+
+        def rotary_tables(self):      # made once: a step, which may be captured as a CUDA graph, only reads them
+            return self.tables
 
 
 def test_toy_parts_register_build_and_step(tmp_path):
@@ -314,13 +329,17 @@ def test_toy_parts_register_build_and_step(tmp_path):
                           dict(mixer=norm("l1.n1"), feed_forward=norm("l1.n2")),
                           PartSpec("toy_half_speed", dict(n_rot=D, base=100.0))),
             )
-            return ModelSpec("ToyLM", d, V, TensorSpec("emb", (V, d)), blocks, default_schedule(2),
-                             norm("final"), None, max_positions=512, storage_dtype="float32")
+            return ModelSpec("ToyLM", d, V,
+                             PartSpec("toy_scaled_table", dict(scale=3.0), dict(table=TensorSpec("emb", (V, d)))),
+                             blocks, default_schedule(2), norm("final"),
+                             PartSpec("linear", dict(tied=True, softcap=5.0), {}),
+                             max_positions=512, storage_dtype="float32")
 
     register_architecture("ToyLM", ToyConfig)
     folder = write_model_folder(tmp_path / "toy", ToyConfig(dict(architectures=["ToyLM"])), 9)
     eng = Engine.load(folder, LoadOptions(dtype="float32", max_tokens=512, max_batch=2))
     assert eng.cache.state_store[0].shape == (2, d + 1) and eng.cache.state_store[1] is None
+    assert eng.model.graph_safe and eng.options.cuda_graphs      # decode steps of this model replay CUDA graphs
 
     rng = np.random.default_rng(0)
     seqs = [rng.integers(0, V, n).tolist() for n in (37, 80, 5)]
@@ -352,3 +371,8 @@ def test_toy_parts_register_build_and_step(tmp_path):
     assert rel(torch.cat(rows_a), ref[0]) < 1e-5
     assert rel(torch.cat(rows_b), ref[1]) < 1e-5
     assert rel(torch.cat(rows_c), ref[2]) < 1e-5
+    assert len(eng._graphs) >= 2 and eng.options.cuda_graphs     # batch shapes of 2 and 1 were captured
+    # the parts of the test's own are in the result: the embedding's scale and the head's cap
+    assert float(ref[0].abs().max()) <= 5.0
+    emb = eng.model.embedding
+    assert type(emb).__name__ == "ScaledTable" and eng.model.head.linear.weight.data_ptr() == emb.table.data_ptr()

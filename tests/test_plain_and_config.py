@@ -31,7 +31,8 @@ def test_config_reads_every_size_from_its_keys():
         assert math.isclose(cfg.attn_scale, 1 / math.sqrt(raw["head_dim"]))
         spec = cfg.to_spec()
         assert len(spec.blocks) == raw["num_hidden_layers"]
-        assert (spec.head is None) == raw["tie_word_embeddings"]
+        assert bool(spec.head.get("tied")) == raw["tie_word_embeddings"]
+        assert ("lm_head.weight" in {t.name for t in spec.tensors()}) != raw["tie_word_embeddings"]
         assert cfg.summary()
 
 

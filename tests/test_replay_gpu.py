@@ -46,7 +46,11 @@ def test_three_cuttings_match_the_plain_implementation(folders, tmp_path, name, 
     for what, steps in (("whole", ru.trace_whole(reqs)),
                         ("last 32 one by one", ru.trace_tail_decode(reqs, 32)),
                         ("unequal batches", ru.trace_batches(reqs, 4)),
-                        ("unequal batches of 3, short prompts", ru.trace_batches(reqs, 3, 0.2))):
+                        ("unequal batches of 3, short prompts", ru.trace_batches(reqs, 3, 0.2)),
+                        ("prompts in chunks of 48", ru.trace_chunks(reqs, 48, 3)),
+                        ("prompts in chunks of 64", ru.trace_chunks(reqs, 64, 4)),
+                        ("chunks of 48 beside single tokens", ru.trace_chunks(reqs, 48, 3, mixed=True)),
+                        ("chunks of 100 beside single tokens", ru.trace_chunks(reqs, 100, 6, tail=40, mixed=True))):
         out = tmp_path / what.replace(" ", "_").replace(",", "")
         ru.run_in_process(eng, steps, out)
         got = ru.collect(steps, out, vocab)
@@ -100,7 +104,9 @@ def test_layer_sizes_of_qwen3_8b(tmp_path_factory, dtype):
     want = ru.expected_logits(folder, reqs)
     eng = _engine(folder, dtype, max_tokens=1024)
     for what, steps in (("whole", ru.trace_whole(reqs)), ("last 32 one by one", ru.trace_tail_decode(reqs, 32)),
-                        ("unequal batch", ru.trace_batches(reqs, 3, 0.8))):
+                        ("unequal batch", ru.trace_batches(reqs, 3, 0.8)),
+                        ("prompts in chunks of 48", ru.trace_chunks(reqs, 48, 3)),
+                        ("chunks of 64 beside single tokens", ru.trace_chunks(reqs, 64, 3, tail=40, mixed=True))):
         out = tmp_path_factory.mktemp("o")
         ru.run_in_process(eng, steps, out)
         got = ru.collect(steps, out, 1536)
