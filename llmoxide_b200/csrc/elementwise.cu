@@ -276,6 +276,66 @@ LLMX_API int llmx_add_rms_norm(float* h, const void* delta, int delta_dtype, int
 }
 
 // ---------------------------------------------------------------------------
+// Residual add and the first half of the RMSNorm, spread over many CTAs, for a step of few tokens.  One CTA
+// per (token, slice of ADD_SLICE columns):
+//   v = h[t,:] + sum_s delta[s][t,:]  (in the order s = 0..S-1, as add_rms_norm);  h[t,:] = v
+//   x[t,:] = bf16(v * gain);  sumsq[slice][t] = sum of v^2 over the slice
+// The matrix product that reads x multiplies its output row t by 1/sqrt(sum_slices sumsq / d + eps) (gemm_tc.cu,
+// TcScale), which completes the norm.  With one CTA per row (add_rms_norm) a decode step's partial sums are
+// loaded by as many SMs as the batch has tokens; here every SM takes part and no CTA waits for another.
+// ---------------------------------------------------------------------------
+#define ADD_SLICE 512
+
+template <typename TD>
+__global__ void __launch_bounds__(ADD_SLICE / 4)
+add_gain_sumsq_kernel(float* __restrict__ h, const TD* __restrict__ delta, int n_split, size_t split_stride,
+                      const float* __restrict__ gain, bf16* __restrict__ x, float* __restrict__ sumsq,
+                      int sumsq_stride, int d) {
+  __shared__ float red[32];
+  pdl_launch_dependents();
+  const int t = blockIdx.y, i = (blockIdx.x * (ADD_SLICE / 4) + threadIdx.x) * 4;
+  const bool live = i < d;
+  const float4 zero = make_float4(0.f, 0.f, 0.f, 0.f);
+  const float4 g = live ? load4(gain + i) : zero;      // a weight: fetched while the kernel before still runs
+  pdl_wait();
+  float4 v = zero;
+  if (live) {
+    float* hp = h + (size_t)t * d + i;
+    v = load4(hp);
+    if (delta) {
+      add_partials4<16>(v, delta + (size_t)t * d + i, n_split, split_stride);
+      store4(hp, v);
+    }
+    store4(x + (size_t)t * d + i, make_float4(v.x * g.x, v.y * g.y, v.z * g.z, v.w * g.w));
+  }
+  float ss = v.x * v.x;
+  ss += v.y * v.y;
+  ss += v.z * v.z;
+  ss += v.w * v.w;
+  const float total = block_sum(ss, red);
+  if (threadIdx.x == 0) sumsq[(size_t)blockIdx.x * sumsq_stride + t] = total;
+}
+
+// h float32 [T,d] (d a multiple of 4); delta nullptr or [n_split][T,d]; x bf16 [T,d];
+// sumsq float32 [ceil(d/ADD_SLICE)][sumsq_stride >= T].
+LLMX_API int llmx_add_gain_sumsq(float* h, const void* delta, int delta_dtype, int n_split, long long split_stride,
+                                 const float* gain, void* x, float* sumsq, int sumsq_stride, int n_tokens, int d,
+                                 cudaStream_t stream) {
+  if (n_tokens <= 0) return 0;
+  if (d <= 0 || (d & 3) || n_tokens > 65535 || sumsq_stride < n_tokens || (delta && n_split < 1)) return LLMX_REFUSED(1);
+  dim3 grid((d + ADD_SLICE - 1) / ADD_SLICE, n_tokens);
+  if (delta_dtype == LLMX_F32)
+    launch_pdl(add_gain_sumsq_kernel<float>, grid, dim3(ADD_SLICE / 4), 0, stream, h, (const float*)delta, n_split,
+               (size_t)split_stride, gain, (bf16*)x, sumsq, sumsq_stride, d);
+  else if (delta_dtype == LLMX_BF16)
+    launch_pdl(add_gain_sumsq_kernel<bf16>, grid, dim3(ADD_SLICE / 4), 0, stream, h, (const bf16*)delta, n_split,
+               (size_t)split_stride, gain, (bf16*)x, sumsq, sumsq_stride, d);
+  else
+    return LLMX_REFUSED(2);
+  return LLMX_LAUNCH_STATUS();
+}
+
+// ---------------------------------------------------------------------------
 // Per-head RMSNorm of q and k, NeoX rotation of both, and the cache write of
 // k and v.  Input qkv [T, (H+2G)*D]: q heads, then k heads, then v heads.
 // One warp per (token, head).  The normalised head is staged in shared memory

@@ -38,6 +38,17 @@ __device__ __forceinline__ void tc_report(int code) {
   llmx_report(code);
 }
 
+// Row scales in the epilogue, for a step of few tokens (T <= 64).  The norm before a product may hand over
+// x~ = bf16(h * gain) and partial sums of squares of h instead of normalised rows (elementwise.cu,
+// add_gain_sumsq): rmsnorm(h) * gain = x~ * r with r[t] = 1 / sqrt(mean(h[t]^2) + eps), and a product is linear
+// in its input rows, so r[t] multiplies the accumulator's column t in the epilogue, before any activation
+// (crates/model/src/ops.rs:40-59 is the norm).  The partial sums are added in a fixed order.
+struct TcScale {
+  const float* sumsq;          // [parts][stride]; nullptr: no scaling
+  int parts, stride;
+  float eps, d;
+};
+
 // Instruction descriptor: bf16 x bf16 -> f32, both operands K-major, M = 128.
 __host__ __device__ constexpr uint32_t umma_idesc(int n) {
   return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(TC_BM >> 4) << 24);
@@ -54,11 +65,12 @@ __host__ __device__ constexpr uint32_t umma_idesc(int n) {
 //         whatever happened before, so the barrier cannot be left waiting.
 // ---------------------------------------------------------------------------
 #define TC_XBUF_FLOATS (2 * 64 * 17)
+#define TC_FUSE_BYTES (64 * 4)                    // row scales
 
 template <int BN, int MODE, typename TY>
 __device__ __forceinline__ void epilogue_tile(uint32_t acc_addr, bool have_acc, bool store, TY* __restrict__ out,
                                               int n0, int t0, int T, int n_limit, long long ldy, int quad, int lane,
-                                              float* xbuf) {
+                                              float* xbuf, const float* row_scale = nullptr) {
   const int row = quad * 32 + lane;
   const int n = MODE == 2 ? (n0 >> 1) + (row & 63) : n0 + row;
 #pragma unroll 1
@@ -71,6 +83,14 @@ __device__ __forceinline__ void epilogue_tile(uint32_t acc_addr, bool have_acc, 
     } else {
 #pragma unroll
       for (int e = 0; e < 16; ++e) v[e] = g[e] = 0.f;
+    }
+    if (row_scale) {            // column t of the accumulator times r[t] (tokens past T are never stored)
+#pragma unroll
+      for (int e = 0; e < 16; ++e) {
+        const float r = row_scale[min(t0 + c + e, 63)];
+        v[e] *= r;
+        if (MODE == 1) g[e] *= r;
+      }
     }
     if (MODE == 2) {
       float* xb = xbuf + ((c >> 4) & 1) * (64 * 17);
@@ -112,7 +132,8 @@ template <int BN, int MODE, typename TY>
 __global__ void __launch_bounds__(TC_THREADS)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
                TY* __restrict__ Y, int T, int N, int K, long long ldy, int k_blocks_per_split,
-               long long split_stride, int F, int n_stages, int row_tiles, int token_tiles, int n_units) {
+               long long split_stride, int F, int n_stages, int row_tiles, int token_tiles, int n_units,
+               const TcScale sc) {
   extern __shared__ uint8_t smem_raw[];
   constexpr int N_ACC = MODE == 1 ? 2 : 1;   // MODE 2 has one accumulator: gate and up rows share a tile
   constexpr uint32_t A_BYTES = TC_BM * TC_BK * 2;
@@ -133,6 +154,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
   const uint32_t acc_full0 = empty0 + 8u * n_stages, acc_empty0 = acc_full0 + 16u;
   uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(bars + 2 * n_stages + 4);
   float* xbuf = reinterpret_cast<float*>(bars + 2 * n_stages + 6);   // MODE 2 only
+  float* row_scales = xbuf + (MODE == 2 ? TC_XBUF_FLOATS : 0);       // [64] r[t]
 
   pdl_launch_dependents();
   if (threadIdx.x == 0) {
@@ -253,6 +275,20 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
     const int quad = warp & 3;          // the quarter of tensor memory this warp may read
     const int n_limit = MODE == 0 ? N : F;
     bool waited = false, failed = false;
+    const float* row_scale = nullptr;
+    if (sc.sumsq) {
+      // r[t] for the step's tokens (T <= 64): the partial sums of squares come from the kernel before
+      pdl_wait();
+      waited = true;
+      for (int t = quad; t < T && t < 64; t += 4) {
+        float a = 0.f;
+        for (int p = lane; p < sc.parts; p += 32) a += __ldcg(sc.sumsq + (size_t)p * sc.stride + t);
+        a = warp_sum(a);
+        if (lane == 0) row_scales[t] = 1.0f / sqrtf(a / sc.d + sc.eps);
+      }
+      asm volatile("bar.sync 2, 128;" ::: "memory");
+      row_scale = row_scales;
+    }
     int j = 0;
     for (int u = blockIdx.x; u < n_units; u += gridDim.x, ++j) {
       int n0, t0, kb_begin, n_kb, split;
@@ -271,7 +307,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
       }
       TY* out = Y + (MODE == 0 ? (size_t)split * split_stride : 0);
       const uint32_t acc_addr = tmem_base + (uint32_t)buf * ACC_COLS + ((uint32_t)(quad * 32) << 16);
-      epilogue_tile<BN, MODE, TY>(acc_addr, n_kb > 0 && !failed, !failed, out, n0, t0, T, n_limit, ldy, quad, lane, xbuf);
+      epilogue_tile<BN, MODE, TY>(acc_addr, n_kb > 0 && !failed, !failed, out, n0, t0, T, n_limit, ldy, quad, lane, xbuf,
+                                  row_scale);
       // hand the accumulator set back to the MMA warp
       tc_fence_before();
       __syncwarp();
@@ -548,7 +585,7 @@ static int sm_count() {
 
 template <int BN, int MODE, typename TY>
 static int launch(const CUtensorMap& mw, const CUtensorMap& mx, void* Y, int T, int N, int K, long long ldy,
-                  int n_split, long long split_stride, int F, cudaStream_t stream) {
+                  int n_split, long long split_stride, int F, const TcScale& sc, cudaStream_t stream) {
   constexpr int N_ACC = MODE == 1 ? 2 : 1;
   constexpr size_t STAGE = (size_t)N_ACC * TC_BM * TC_BK * 2 + (size_t)BN * TC_BK * 2;
   const int total_kb = (K + TC_BK - 1) / TC_BK;
@@ -560,7 +597,8 @@ static int launch(const CUtensorMap& mw, const CUtensorMap& mx, void* Y, int T, 
   int stages = (int)(budget / STAGE);
   if (stages > 12) stages = 12;
   if (stages < 2) stages = 2;
-  const size_t smem = 1024 + (size_t)stages * STAGE + (2 * stages + 6) * 8 + (MODE == 2 ? TC_XBUF_FLOATS * 4 : 0);
+  const size_t smem = 1024 + (size_t)stages * STAGE + (2 * stages + 6) * 8 + (MODE == 2 ? TC_XBUF_FLOATS * 4 : 0) +
+                      TC_FUSE_BYTES;
   auto kernel = gemm_tc_kernel<BN, MODE, TY>;
   static bool attr_set = false;
   if (!attr_set) {
@@ -575,7 +613,7 @@ static int launch(const CUtensorMap& mw, const CUtensorMap& mx, void* Y, int T, 
   const int max_ctas = sm_count() * ctas_per_sm;
   const int grid = n_units < max_ctas ? (int)n_units : max_ctas;
   launch_pdl(kernel, dim3(grid), dim3(TC_THREADS), smem, stream, mw, mx, (TY*)Y, T, N, K, ldy, per_split,
-             split_stride, F, stages, row_tiles, token_tiles, (int)n_units);
+             split_stride, F, stages, row_tiles, token_tiles, (int)n_units, sc);
   return LLMX_LAUNCH_STATUS();
 }
 
@@ -584,10 +622,29 @@ static int launch(const CUtensorMap& mw, const CUtensorMap& mx, void* Y, int T, 
 // mode 1: W = [gate rows; up rows] with N = 2F; Y = act [T,F] of y_dtype.
 // mode 2: W = blocks of 128 rows, each 64 gate rows then the 64 up rows of the same features (N = 2F, F % 64 == 0);
 //         Y = act [T,F] bf16.
+// The same with row scales applied in the epilogue (see TcScale): in_sumsq [in_parts][in_stride >= T], T <= 64.
+LLMX_API int llmx_gemm_tc_scaled(const void* X, const void* W, void* Y, int y_dtype, int T, int N, int K, long long ldx,
+                                 long long ldw, long long ldy, int n_split, long long split_stride, int mode,
+                                 const float* in_sumsq, int in_parts, int in_stride, float in_eps, int in_d,
+                                 cudaStream_t stream);
+
 LLMX_API int llmx_gemm_tc(const void* X, const void* W, void* Y, int y_dtype, int T, int N, int K, long long ldx,
                           long long ldw, long long ldy, int n_split, long long split_stride, int mode,
                           cudaStream_t stream) {
+  return llmx_gemm_tc_scaled(X, W, Y, y_dtype, T, N, K, ldx, ldw, ldy, n_split, split_stride, mode, nullptr, 0, 0, 0.f,
+                             1, stream);
+}
+
+LLMX_API int llmx_gemm_tc_scaled(const void* X, const void* W, void* Y, int y_dtype, int T, int N, int K, long long ldx,
+                                 long long ldw, long long ldy, int n_split, long long split_stride, int mode,
+                                 const float* in_sumsq, int in_parts, int in_stride, float in_eps, int in_d,
+                                 cudaStream_t stream) {
   if (T <= 0 || N <= 0) return 0;
+  TcScale sc = {};
+  if (in_sumsq) {
+    if (T > 64 || in_parts <= 0 || in_stride < T || in_d <= 0) return LLMX_REFUSED(1);
+    sc.sumsq = in_sumsq, sc.parts = in_parts, sc.stride = in_stride, sc.eps = in_eps, sc.d = (float)in_d;
+  }
   if (K <= 0 || (K % 8) || (ldx % 8) || (ldw % 8) || ((uintptr_t)X & 15) || ((uintptr_t)W & 15)) return LLMX_REFUSED(1);
   if (n_split < 1 || (n_split > 1 && (mode != 0 || y_dtype != LLMX_F32))) return LLMX_REFUSED(1);
   if (mode < 0 || mode > 2 || (mode == 1 && (N % 2)) || (mode == 2 && (N % 128))) return LLMX_REFUSED(1);
@@ -597,7 +654,7 @@ LLMX_API int llmx_gemm_tc(const void* X, const void* W, void* Y, int y_dtype, in
   CUtensorMap mw, mx;
   if (make_map(&mw, W, (uint64_t)N, (uint64_t)K, (uint64_t)ldw, TC_BM, true)) return LLMX_REFUSED(4);
   if (make_map(&mx, X, (uint64_t)T, (uint64_t)K, (uint64_t)ldx, (uint32_t)bn, false)) return LLMX_REFUSED(4);
-#define GO(BN, MODE, TY) return launch<BN, MODE, TY>(mw, mx, Y, T, N, K, ldy, n_split, split_stride, F, stream)
+#define GO(BN, MODE, TY) return launch<BN, MODE, TY>(mw, mx, Y, T, N, K, ldy, n_split, split_stride, F, sc, stream)
 #define BY_BN(MODE, TY)                    \
   switch (bn) {                            \
     case 16: GO(16, MODE, TY);             \

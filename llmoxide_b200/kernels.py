@@ -250,6 +250,34 @@ def add_rms_norm(h: torch.Tensor, delta, gain: torch.Tensor, eps: float, out, ro
              _tag(out) if out is not None else F32, d, int(write_h), _stream()), "add_rms_norm")
 
 
+ADD_SLICE = 512  # columns per CTA of add_gain_sumsq; the same constant as in elementwise.cu
+
+
+def add_gain_sumsq(h: torch.Tensor, delta, gain: torch.Tensor, x_out: torch.Tensor, sumsq: torch.Tensor) -> None:
+    """The residual add and the first half of an RMSNorm for a step of few tokens: h float32 [T,d] += delta
+    (None, [T,d] or split partials [S,T,d], added in order); x_out = bfloat16(h * gain); sumsq[s, t] = the sum
+    of squares of h[t] over the s-th slice of ``ADD_SLICE`` columns.  The matrix product that reads ``x_out``
+    applies the scale (``gemm_tc(scale=...)``)."""
+    _dev(h, delta, gain, x_out, sumsq)
+    _contig("h", h), _contig("x_out", x_out)
+    T, d = h.shape
+    assert h.dtype == torch.float32 and gain.dtype == torch.float32 and gain.shape == (d,)
+    assert x_out.shape == (T, d) and x_out.dtype == torch.bfloat16 and d % 4 == 0
+    n_slices = (d + ADD_SLICE - 1) // ADD_SLICE
+    assert sumsq.dtype == torch.float32 and sumsq.shape[0] >= n_slices and sumsq.stride(0) >= T and sumsq.stride(1) == 1
+    n_split, stride, dtag = 1, 0, F32
+    if delta is not None:
+        _contig("delta", delta)
+        if delta.dim() == 2:
+            delta = delta.unsqueeze(0)
+        assert delta.shape[1:] == h.shape
+        n_split, stride, dtag = delta.shape[0], delta.stride(0), _tag(delta)
+    f = _fn("elementwise", "llmx_add_gain_sumsq",
+            [c_void_p, c_void_p, c_int, c_int, c_longlong, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p])
+    _check(f(_ptr(h), _ptr(delta), dtag, n_split, stride, _ptr(gain), _ptr(x_out), _ptr(sumsq), sumsq.stride(0), T, d,
+             _stream()), "add_gain_sumsq")
+
+
 def qk_norm_rope_cache(qkv, q_out, k_cache, v_cache, block_table, token_seq, token_pos, q_gain, k_gain,
                        eps: float, cos, sin, n_rot: int, n_heads: int, n_kv_heads: int, head_dim: int,
                        write_cache: bool = True) -> None:
@@ -458,13 +486,16 @@ def gemm_tc_supports(x: torch.Tensor, w: torch.Tensor) -> bool:
 
 
 def gemm_tc(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, n_split: int = 1, gated=False,
-            pair: bool = False) -> None:
+            pair: bool = False, scale=None) -> None:
     """bfloat16 x [T,K] times w [N,K]^T on tcgen05.  ``out`` is [T,N] (bfloat16
     or float32), or float32 partials [n_split,T,N] of a split reduction, or,
     with ``gated``, [T,N/2] = silu(gate) * up: ``gated=True`` (or 1) for
     w = [gate rows; up rows], ``gated=2`` for w in blocks of 64 gate rows each
     followed by the 64 up rows of the same features (N/2 a multiple of 64).
-    ``pair`` runs the CTA-pair kernel (prompt-sized T > 128, no split)."""
+    ``pair`` runs the CTA-pair kernel (prompt-sized T > 128, no split).
+    ``scale = (sumsq, parts, eps, d)``, for T <= 64: output row t is multiplied
+    by 1/sqrt(sum(sumsq[:parts, t]) / d + eps) before any activation (the
+    second half of an RMSNorm whose first half is ``add_gain_sumsq``)."""
     gated = int(gated)
     _dev(x, w, out)
     T, K = x.shape
@@ -480,18 +511,28 @@ def gemm_tc(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, n_split: int = 
         assert out.shape == (T, N)
         ldy, stride = N, 0
     if pair:
-        assert n_split == 1 and T > 128
+        assert n_split == 1 and T > 128 and scale is None
         f = _fn("gemm_tc", "llmx_gemm_tc_pair",
                 [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_longlong, c_longlong, c_longlong, c_int,
                  c_void_p])
         _check(f(_ptr(x), _ptr(w), _ptr(out), _tag(out), T, N, K, x.stride(0), w.stride(0), ldy,
                  gated, _stream()), "gemm_tc_pair")
         return
-    f = _fn("gemm_tc", "llmx_gemm_tc",
+    if scale is None:
+        f = _fn("gemm_tc", "llmx_gemm_tc",
+                [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_longlong, c_longlong, c_longlong, c_int,
+                 c_longlong, c_int, c_void_p])
+        _check(f(_ptr(x), _ptr(w), _ptr(out), _tag(out), T, N, K, x.stride(0), w.stride(0), ldy, n_split, stride,
+                 gated, _stream()), "gemm_tc")
+        return
+    sumsq, parts, eps, d = scale
+    _dev(sumsq)
+    assert T <= 64 and sumsq.dtype == torch.float32 and sumsq.shape[0] >= parts and sumsq.stride(1) == 1
+    f = _fn("gemm_tc", "llmx_gemm_tc_scaled",
             [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_longlong, c_longlong, c_longlong, c_int,
-             c_longlong, c_int, c_void_p])
-    _check(f(_ptr(x), _ptr(w), _ptr(out), _tag(out), T, N, K, x.stride(0), w.stride(0), ldy, n_split, stride,
-             gated, _stream()), "gemm_tc")
+             c_longlong, c_int, c_void_p, c_int, c_int, c_float, c_int, c_void_p])
+    _check(f(_ptr(x), _ptr(w), _ptr(out), _tag(out), T, N, K, x.stride(0), w.stride(0), ldy, n_split, stride, gated,
+             _ptr(sumsq), parts, sumsq.stride(0), eps, d, _stream()), "gemm_tc (row scales)")
 
 
 def gemm_tc_status(reset: bool = True) -> int:

@@ -52,6 +52,11 @@ class GQAttention:
     def cache_need(self):
         return KVNeed(self.G, self.D, self.window), None
 
+    @property
+    def takes_row_scales(self) -> bool:
+        """Its first products (q|k|v) can apply a norm's row scales in their epilogue."""
+        return self.qkv.takes_row_scales and self.q_only.takes_row_scales
+
     def libraries(self) -> set:
         libs = {"elementwise"} | self.qkv.libraries() | self.o.libraries()
         if self.rt.dtype == "bfloat16" and self.rt.tensor_cores:
@@ -64,6 +69,7 @@ class GQAttention:
     def forward(self, x, ctx, view, writes_cache=True):
         H, G, D = self.H, self.G, self.D
         T = x.shape[0]
+        dev = x.device
         tables = self.position.rotary_tables() if self.position is not None else None
         cos, sin, n_rot = tables if tables is not None else (None, None, 0)
         block_table = ctx.block_tables[view.group]
@@ -72,9 +78,9 @@ class GQAttention:
         else:
             # A call that reads another call's cache entry makes only queries.
             q_part = self.q_only(x)
-            qkv = torch.empty((T, (H + 2 * G) * D), dtype=q_part.dtype, device=x.device)
+            qkv = torch.empty((T, (H + 2 * G) * D), dtype=q_part.dtype, device=dev)
             qkv[:, : H * D] = q_part
-        q = torch.empty((T, H * D), dtype=self.rt.act_dtype, device=x.device)
+        q = torch.empty((T, H * D), dtype=self.rt.act_dtype, device=dev)
         kernels.qk_norm_rope_cache(qkv, q, view.k, view.v, block_table, ctx.token_seq, ctx.token_pos,
                                    self.q_gain, self.k_gain, self.eps, cos, sin, n_rot, H, G, D, writes_cache)
         out = torch.empty_like(q)

@@ -37,10 +37,18 @@ class PreNormBlock:
         return libs
 
     def forward(self, h, pending, ctx, view, writes_cache=True):
-        x = self.mixer_norm.add_forward(h, pending)
+        x = _norm(self.mixer_norm, h, pending, self.mixer)
         a = self.mixer.forward(x, ctx, view, writes_cache)
-        x = self.ff_norm.add_forward(h, a)
+        x = _norm(self.ff_norm, h, a, self.feed_forward)
         return self.feed_forward.forward(x, ctx)
+
+
+def _norm(norm, h, delta, consumer):
+    """h += delta; x = norm(h).  Where both sides can, the norm is done in two halves: the norm part leaves the
+    scale to the consumer's first products (``takes_row_scales`` on the consumer, ``row_scales_ok`` on the norm)."""
+    if getattr(consumer, "takes_row_scales", False) and getattr(norm, "ROW_SCALE_MAX_TOKENS", 0):
+        return norm.add_forward(h, delta, row_scales_ok=True)
+    return norm.add_forward(h, delta)
 
 
 def rt_shared_position(spec, weights, rt):

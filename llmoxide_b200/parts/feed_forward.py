@@ -8,6 +8,7 @@ import torch
 
 from .. import kernels
 from ..errors import Unsupported
+from .row_scaled import RowScaled
 from .linear import Linear
 from .registry import register_feed_forward
 
@@ -47,13 +48,22 @@ class GatedMLP:
     def libraries(self) -> set:
         return {"elementwise"} | self.gate_up.libraries() | self.down.libraries()
 
+    @property
+    def takes_row_scales(self) -> bool:
+        """The gate|up product can apply a norm's row scales in its epilogue, ahead of the activation."""
+        return self.gate_up._tc is not None
+
     def forward(self, x, ctx):
         tc = self.gate_up._tc
-        if tc is not None and x.dtype == torch.bfloat16 and x.shape[0] > FUSE_MIN_TOKENS and kernels.gemm_tc_supports(x, tc.weight):
+        scaled = isinstance(x, RowScaled)
+        n_tokens = x.shape[0]
+        if tc is not None and x.dtype == torch.bfloat16 and n_tokens > FUSE_MIN_TOKENS and (
+                scaled or kernels.gemm_tc_supports(x, tc.weight)):
             # the activation is the epilogue of the gate/up product
             act = tc.gated(x, self.rt.act_dtype, self.block)
         else:
+            assert not scaled
             gu = self.gate_up(x, splits_ok=True)
-            act = torch.empty((x.shape[0], self.F), dtype=self.rt.act_dtype, device=x.device)
+            act = torch.empty((n_tokens, self.F), dtype=self.rt.act_dtype, device=x.device)
             kernels.silu_gate(gu, act, self.block)
         return self.down(act, splits_ok=True)

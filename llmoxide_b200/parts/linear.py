@@ -9,6 +9,7 @@ from __future__ import annotations
 import torch
 
 from .. import kernels
+from .row_scaled import RowScaled
 from .runtime import Runtime
 
 
@@ -25,12 +26,17 @@ class Linear:
     def libraries(self) -> set:
         return {"gemm_tc", "elementwise"} if self._tc is not None else {"gemm_fma"}
 
-    def __call__(self, x: torch.Tensor, out_dtype=None, splits_ok: bool = False) -> torch.Tensor:
+    def __call__(self, x, out_dtype=None, splits_ok: bool = False):
         """x [T, in] -> [T, out], or split partials [S, T, out] in float32 when
-        ``splits_ok`` and the kernel chose to split the reduction."""
+        ``splits_ok`` and the kernel chose to split the reduction.  ``x`` may be
+        ``RowScaled`` (tensor-core path only; see ``parts.row_scaled``)."""
         out_dtype = out_dtype or self.rt.act_dtype
-        if self._tc is not None and x.dtype == torch.bfloat16:
+        if self._tc is not None and (isinstance(x, RowScaled) or x.dtype == torch.bfloat16):
             return self._tc(x, out_dtype, splits_ok)
         out = torch.empty((x.shape[0], self.out_features), dtype=out_dtype, device=x.device)
         kernels.gemm_fma(x, self.weight, out)
         return out
+
+    @property
+    def takes_row_scales(self) -> bool:
+        return self._tc is not None

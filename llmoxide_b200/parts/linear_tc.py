@@ -13,6 +13,7 @@ import torch
 
 from .. import kernels
 from ..guard import scratch
+from .row_scaled import RowScaled
 
 TILE_ROWS = 128
 CTAS_PER_SM = 2               # what the kernel fits per SM at decode tile sizes
@@ -52,27 +53,37 @@ class TensorCoreLinear:
         self.N, self.K = weight.shape
 
     def __call__(self, x, out_dtype, splits_ok):
+        x, scale = self._unpack(x)
         T = x.shape[0]
         if not kernels.gemm_tc_supports(x, self.weight):
+            assert scale is None
             out = torch.empty((T, self.N), dtype=out_dtype, device=x.device)
             kernels.gemm_fma(x, self.weight, out)
             return out
         s = choose_splits(self.N, self.K, T, self.n_sm) if splits_ok else 1
         if s > 1:
             out = scratch((s, T, self.N), torch.float32, x.device, "split partials of a matrix product")
-            kernels.gemm_tc(x, self.weight, out, n_split=s)
+            kernels.gemm_tc(x, self.weight, out, n_split=s, scale=scale)
             return out
         out = scratch((T, self.N), out_dtype, x.device, "output of a matrix product")
-        kernels.gemm_tc(x, self.weight, out, pair=T > PAIR_MIN_TOKENS)
+        kernels.gemm_tc(x, self.weight, out, pair=T > PAIR_MIN_TOKENS, scale=scale)
         return out
+
+    @staticmethod
+    def _unpack(x):
+        """Plain rows, or rows whose norm's scale is still to be applied (``RowScaled``)."""
+        if isinstance(x, RowScaled):
+            return x.x, (x.sumsq, x.n_parts, x.eps, x.d)
+        return x, None
 
     def gated(self, x, out_dtype, block: int = 0):
         """silu(gate x) * (up x), [T, N/2]; ``block`` = 0 for weight = [gate rows; up rows], 64 for
         blocks of 64 gate rows each followed by the 64 up rows of the same features."""
+        x, scale = self._unpack(x)
         out = scratch((x.shape[0], self.N // 2), out_dtype, x.device, "output of the gated matrix product")
-        kernels.gemm_tc(x, self.weight, out, gated=2 if block == 64 else 1, pair=x.shape[0] > PAIR_MIN_TOKENS)
+        kernels.gemm_tc(x, self.weight, out, gated=2 if block == 64 else 1, pair=x.shape[0] > PAIR_MIN_TOKENS,
+                        scale=scale)
         return out
-
 
 def plan_for(weight: torch.Tensor, n_sm: int = 148):
     if weight.dtype != torch.bfloat16 or weight.stride(1) != 1 or weight.shape[1] % 8 or weight.stride(0) % 8:

@@ -586,3 +586,48 @@ def test_softcap_and_scaled_embedding():
     out = torch.empty(3, 72, dtype=torch.float32, device=DEV)
     kernels.embed(table.to(DEV), toks.to(DEV), out, 8.5)
     assert torch.equal(out.cpu(), table[toks.long()] * 8.5)
+
+
+@pytest.mark.parametrize("T, d, N2", [(8, 512, 768), (1, 200, 256), (64, 1152, 384), (37, 4096, 256), (5, 8200, 128)])
+def test_norm_in_two_halves(T, d, N2):
+    """The residual add + RMSNorm of a step of few tokens as two halves: sums of squares per slice from one
+    kernel, the scale in the epilogue of the product that follows; against the same in plain float32.  The
+    residual stream is bit-equal to what the one-kernel norm gives."""
+    from llmoxide_b200 import kernels
+    g = torch.Generator().manual_seed(T + d)
+    w2 = (torch.randn(N2, d, generator=g) / math.sqrt(d)).bfloat16()
+    h0 = torch.randn(T, d, generator=g) * 3
+    gain = 1 + 0.1 * torch.randn(d, generator=g)
+    eps = 1e-5
+    w2d, gd = w2.to(DEV), gain.to(DEV)
+    parts = (d + kernels.ADD_SLICE - 1) // kernels.ADD_SLICE
+    for n_split, ddtype in ((0, None), (1, torch.bfloat16), (3, torch.float32), (9, torch.float32), (16, torch.float32)):
+        delta = None if n_split == 0 else torch.randn(n_split, T, d, generator=g).to(ddtype)
+        want_h = h0 if delta is None else h0 + delta.float().sum(0)
+        want_y = plain.rms_norm(want_h, gain, eps) @ w2.float().t()
+        dd = None if delta is None else delta.to(DEV)
+        h = h0.to(DEV)
+        x = torch.full((T, d), float("nan"), dtype=torch.bfloat16, device=DEV)
+        sumsq = torch.full((parts, max(T, 8)), float("nan"), dtype=torch.float32, device=DEV)
+        kernels.add_gain_sumsq(h, dd, gd, x, sumsq)
+        h_ref, x_ref = h0.to(DEV), torch.empty((T, d), dtype=torch.bfloat16, device=DEV)
+        kernels.add_rms_norm(h_ref, dd, gd, eps, x_ref)
+        assert torch.equal(h, h_ref), n_split
+        assert rel(sumsq[:, :T].sum(0), (want_h * want_h).sum(1)) < 1e-5
+        assert rel(x, want_h * gain) < 6e-3
+        y = torch.empty((T, N2), dtype=torch.float32, device=DEV)
+        kernels.gemm_tc(x, w2d, y, scale=(sumsq, parts, eps, d))
+        assert rel(y, want_y) < 6e-3, n_split
+        if d // 64 >= 2:
+            y2 = torch.empty((2, T, N2), dtype=torch.float32, device=DEV)
+            kernels.gemm_tc(x, w2d, y2, n_split=2, scale=(sumsq, parts, eps, d))
+            assert rel(y2.sum(0), want_y) < 6e-3
+        if N2 % 128 == 0:        # the gated epilogue scales before the activation
+            F = N2 // 2
+            act = torch.empty((T, F), dtype=torch.bfloat16, device=DEV)
+            kernels.gemm_tc(x, w2d, act, gated=True, scale=(sumsq, parts, eps, d))
+            assert rel(act, plain.silu(want_y[:, :F]) * want_y[:, F:]) < 1e-2
+            blocks = want_y.view(T, N2 // 128, 2, 64)
+            kernels.gemm_tc(x, w2d, act, gated=2, scale=(sumsq, parts, eps, d))
+            assert rel(act, (plain.silu(blocks[:, :, 0]) * blocks[:, :, 1]).reshape(T, F)) < 1e-2
+    assert kernels.gemm_tc_status() == 0
