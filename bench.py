@@ -4,12 +4,16 @@ B200.  A "step" is one decode step of a batch of 8 sequences from depth 2048
 (context 4096 per sequence).  Prints ONE JSON line.
 
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--layers L] [--impl reference]
+    python bench.py --cpu-baseline      # the plain implementation of tests/ on the CPU, tiny configurations
 
 ``value`` is device-timed (CUDA events around K steps queued back to back);
 ``e2e`` is the same metric through ``Session.generate`` with host token ids in
 and out, every step copying its inputs from pinned host memory and reading
-the sampled tokens back.  Weights (16 GB) and cache are far larger than L2,
-so nothing is flushed between steps.
+the sampled tokens back, over at least 256 steps.  ``points`` has the same at
+batch 1 and 64 and the prefill rate at other lengths (tokens per second);
+``point_details`` has their milliseconds, roofline fractions, end-to-end rates
+and the host's microseconds per step.  Weights (16 GB) and cache are far
+larger than L2, so nothing is flushed between steps.
 """
 
 from __future__ import annotations
@@ -187,6 +191,8 @@ def main() -> int:
     ap.add_argument("--timeline", action="store_true",
                     help="instead of the benchmark: build the kernels with their in-place timers and print, for "
                          "one replayed decode step, when each kernel's dependency resolved")
+    ap.add_argument("--cpu-baseline", action="store_true",
+                    help="instead of the benchmark: time the plain implementation of tests/ on the CPU (tiny configurations)")
     ap.add_argument("--cuda-profiler", choices=["decode", "prefill"], default=None,
                     help="bracket that region with cudaProfilerStart/Stop (for ncu --profile-from-start off)")
     args = ap.parse_args()
@@ -196,6 +202,8 @@ def main() -> int:
                           "bigmah/llmoxide is a Rust workspace over wgpu; no Rust toolchain and no graphics stack "
                           "here, so pip cannot install it and its GPU path cannot run"}))
         return 0
+    if args.cpu_baseline:
+        return cpu_baseline()
     if args.gpus != 1:
         print(json.dumps({"note": f"this library runs on one GPU; --gpus {args.gpus} is not supported", "n_gpus": args.gpus}))
         return 2
@@ -217,7 +225,8 @@ def main() -> int:
     big_b = 1 if args.no_points else 64
     max_b = max(B, big_b)
     opts = LoadOptions(dtype="bfloat16", max_tokens=max_b * args.context, max_batch=max_b,
-                       max_step_tokens=max(args.prefill_tokens, B * args.depth), cuda_graphs=not args.no_graphs)
+                       max_step_tokens=max(args.prefill_tokens, B * args.depth, 0 if args.no_points else 16 * 2048),
+                       cuda_graphs=not args.no_graphs)
     t_load = time.time()
     session = Session.random(cfg, seed=0, options=opts)
     eng = session.engine
@@ -241,25 +250,34 @@ def main() -> int:
 
     # ---- prefill: one prompt of 2,048 tokens ----------------------------------
     T = args.prefill_tokens
-    prompt = rng.integers(0, V, T).tolist()
 
-    def one_prefill():
-        slot = eng.acquire()
-        eng.step([(slot, prompt)])
-        eng.release(slot)
+    def prefill_time(lengths, profile=False):
+        """Median milliseconds of one prompt step over sequences of these lengths (slots taken and given back)."""
+        prompts = [rng.integers(0, V, n).tolist() for n in lengths]
 
-    for _ in range(3):
-        one_prefill()
-    if args.cuda_profiler == "prefill":
-        torch.cuda.profiler.start()
-        one_prefill()
-        torch.cuda.synchronize()
-        torch.cuda.profiler.stop()
-    prefill_ms = statistics.median(event_time(one_prefill) for _ in range(5))
-    prefill = dict(value=T / prefill_ms * 1e3, tokens=T, ms=prefill_ms,
-                   frac=prefill_flops(T) / (prefill_ms * 1e-3) / (pk["bf16_tflops"] * 1e12),
-                   tflops=prefill_flops(T) / (prefill_ms * 1e-3) / 1e12)
-    print(f"[bench] prefill {T} tokens: {prefill_ms:.2f} ms", file=sys.stderr)
+        def one():
+            slots = [eng.acquire() for _ in prompts]
+            eng.step(list(zip(slots, prompts)))
+            for s in slots:
+                eng.release(s)
+
+        for _ in range(3):
+            one()
+        if profile:
+            torch.cuda.profiler.start()
+            one()
+            torch.cuda.synchronize()
+            torch.cuda.profiler.stop()
+        return statistics.median(event_time(one) for _ in range(5))
+
+    def prefill_point(lengths, profile=False):
+        ms = prefill_time(lengths, profile)
+        flops = sum(prefill_flops(n) for n in lengths)
+        return dict(value=sum(lengths) / ms * 1e3, tokens=sum(lengths), ms=ms,
+                    frac=flops / (ms * 1e-3) / (pk["bf16_tflops"] * 1e12), tflops=flops / (ms * 1e-3) / 1e12)
+
+    prefill = prefill_point([T], profile=args.cuda_profiler == "prefill")
+    print(f"[bench] prefill {T} tokens: {prefill['ms']:.2f} ms", file=sys.stderr)
 
     # ---- decode: B sequences at depth, K steps ----------------------------------
     def decode_rate(batch, steps, warmup, sampler=None):
@@ -286,31 +304,54 @@ def main() -> int:
         launches = kernels.launch_count - launches
         for s in slots:
             eng.release(s)
-        return batch * steps / ms * 1e3, ms / steps, launches, clocks
+        mean_depth = args.depth + warmup + steps / 2
+        step_bytes = weight_bytes + batch * mean_depth * kv_per_token
+        gbs = step_bytes / (ms / steps * 1e-3) / 1e9
+        return dict(value=batch * steps / ms * 1e3, ms_per_step=ms / steps, gb_per_s=gbs, frac=gbs / pk["hbm_gbs"],
+                    launches=launches, clocks=clocks)
 
-    value, ms_per_step, launches, clocks = decode_rate(B, K, max(W, 3), ClockSampler())
-    mean_depth = args.depth + max(W, 3) + K / 2
-    step_bytes = weight_bytes + B * mean_depth * kv_per_token
-    achieved = step_bytes / (ms_per_step * 1e-3) / 1e9
+    main_pt = decode_rate(B, K, max(W, 3), ClockSampler())
+    value, ms_per_step, launches, clocks = main_pt["value"], main_pt["ms_per_step"], main_pt["launches"], main_pt["clocks"]
+    achieved = main_pt["gb_per_s"]
     print(f"[bench] decode b{B}: {ms_per_step:.3f} ms/step, {value:.0f} tok/s, {achieved:.0f} GB/s", file=sys.stderr)
 
     # ---- end to end through the Python entry point --------------------------------
-    reqs = [Request(rng.integers(0, V, args.depth).tolist(), max_tokens=K + 1, sampling=Sampling.greedy(),
-                    stop_ids=()) for _ in range(B)]
     session.loop.stop_ids = frozenset()
-    session.generate([Request(r.prompt[:64], max_tokens=4, sampling=Sampling.greedy()) for r in reqs])  # warm
-    t0 = session.timings.decode_seconds, session.timings.decode_tokens
-    session.generate(reqs)
-    e2e_s = session.timings.decode_seconds - t0[0]
-    e2e_tok = session.timings.decode_tokens - t0[1]
-    lay_ints = 3 * B + (B + 1) + 2 * B + B + B * max(8, -(-((args.depth + K + 64) // 64) // 8) * 8)
-    e2e = dict(value=e2e_tok / e2e_s, unit="tokens/s", h2d_bytes_per_step=4 * lay_ints, d2h_bytes_per_step=4 * B)
-    print(f"[bench] e2e decode b{B}: {e2e['value']:.0f} tok/s", file=sys.stderr)
 
-    points = {}
+    def e2e_rate(batch, steps):
+        """Decoded tokens per second through Session.generate (host ids in, host ids out), and the host's own
+        time per step.  A short run over the same prompts first, so that the batch's shape has its CUDA graph."""
+        prompts = [rng.integers(0, V, args.depth).tolist() for _ in range(batch)]
+        session.generate([Request(p, max_tokens=3, sampling=Sampling.greedy(), stop_ids=()) for p in prompts])
+        t0 = session.timings.decode_seconds, session.timings.decode_tokens, eng.host_seconds, eng.n_steps
+        session.generate([Request(p, max_tokens=steps + 1, sampling=Sampling.greedy(), stop_ids=()) for p in prompts])
+        secs = session.timings.decode_seconds - t0[0]
+        toks = session.timings.decode_tokens - t0[1]
+        host_us = (eng.host_seconds - t0[2]) / max(1, eng.n_steps - t0[3] - 1) * 1e6
+        return toks / secs, host_us
+
+    e2e_steps = max(K, 256)
+    e2e_value, host_us = e2e_rate(B, e2e_steps)
+    lay_ints = 3 * B + (B + 1) + 2 * B + B + B * max(8, -(-((args.depth + e2e_steps + 64) // 64) // 8) * 8)
+    e2e = dict(value=e2e_value, unit="tokens/s", steps=e2e_steps, h2d_bytes_per_step=4 * lay_ints,
+               d2h_bytes_per_step=4 * B, host_us_per_step=host_us)
+    print(f"[bench] e2e decode b{B}: {e2e_value:.0f} tok/s over {e2e_steps} steps, host {host_us:.0f} us/step", file=sys.stderr)
+
+    points, details = {}, {}
     if not args.no_points:
-        points["decode_b1"] = decode_rate(1, max(16, K // 2), 3)[0]
-        points["decode_b64"] = decode_rate(64, max(8, K // 4), 3)[0]
+        for batch, steps in ((1, max(16, K // 2)), (64, max(8, K // 4))):
+            pt = decode_rate(batch, steps, 3)
+            rate, h_us = e2e_rate(batch, 256 if batch == 1 else 96)
+            points[f"decode_b{batch}"] = pt["value"]
+            details[f"decode_b{batch}"] = dict(ms_per_step=pt["ms_per_step"], gb_per_s=pt["gb_per_s"], frac=pt["frac"],
+                                               e2e=rate, e2e_frac_of_device=rate / pt["value"], host_us_per_step=h_us)
+        details[f"decode_b{B}"] = dict(ms_per_step=ms_per_step, gb_per_s=achieved, frac=main_pt["frac"], e2e=e2e_value,
+                                       e2e_frac_of_device=e2e_value / value, host_us_per_step=host_us)
+        lens16 = rng.integers(64, 2049, 16).tolist()       # an unequal batch: 16 prompts of 64..2048 tokens
+        for name, lengths in (("prefill_512", [512]), ("prefill_8192", [8192]), ("prefill_16_unequal", lens16)):
+            pp = prefill_point(lengths)
+            points[name] = pp["value"]
+            details[name] = dict(tokens=pp["tokens"], ms=pp["ms"], frac=pp["frac"], tflops=pp["tflops"])
 
     line = dict(
         metric="decode tok/s at batch 8 from depth 2048, Qwen3-8B layer sizes, bf16", value=value, unit="tokens/s",
@@ -325,9 +366,40 @@ def main() -> int:
                     cuda_graphs=not args.no_graphs, peaks=pk_src),
         prefill=prefill,
         roofline=dict(bound="hbm", achieved=achieved, peak=pk["hbm_gbs"], unit="GB/s", frac=achieved / pk["hbm_gbs"]),
-        points=points, e2e=e2e, gpu_launches=launches, clocks=clocks,
+        points=points, point_details=details, e2e=e2e, gpu_launches=launches, clocks=clocks,
     )
     print(json.dumps(line))
+    return 0
+
+
+def cpu_baseline() -> int:
+    """Tokens per second of the plain implementation (tests/plain_qwen3.py: float32, whole sequences, no cache)
+    on this machine's CPU, on the tiny configurations A and B: a prompt step over BASELINE.json's prompts and
+    greedy decoding that recomputes the whole sequence for every token.  It is the oracle of the tests, timed
+    for orientation; the reference's own CPU path cannot be built here."""
+    import tempfile
+
+    sys.path.insert(0, str(ROOT))
+    sys.path.insert(0, str(ROOT / "tests"))
+    import plain_qwen3 as plain
+    from tiny_configs import make_folder, prompts
+
+    out = {}
+    with tempfile.TemporaryDirectory() as tmp:
+        for name, lengths, n_new in (("A", [5, 9, 13], 8), ("B", [1, 7, 16, 31], 12)):
+            cfg, w = plain.read_model(make_folder(tmp, name, "float32"))
+            ps = prompts(cfg["vocab_size"], lengths, seed=1)
+            t0 = time.perf_counter()
+            for p in ps:
+                plain.forward(cfg, w, p)
+            t_prefill = time.perf_counter() - t0
+            t0 = time.perf_counter()
+            for p in ps:
+                plain.greedy_generate(cfg, w, p, n_new)
+            t_decode = time.perf_counter() - t0 - t_prefill
+            out[f"tiny_{name}"] = dict(prefill_tokens_per_s=sum(lengths) / t_prefill,
+                                       decode_tokens_per_s=len(ps) * n_new / max(t_decode, 1e-9))
+    print(json.dumps(dict(impl="plain implementation on the CPU (tests/plain_qwen3.py)", unit="tokens/s", **out)))
     return 0
 
 

@@ -321,6 +321,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
     tc_fence_after();
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
   }
+  if (threadIdx.x == 0) LLMX_MARK(21);      // (timeline builds only: when this CTA was done)
 }
 
 // ---------------------------------------------------------------------------

@@ -73,6 +73,7 @@ class Engine:
         want = 4 * min(options.max_step_tokens, options.max_tokens) + 4 * n_slots + min(n_slots, 256) * width + 64
         self.buffers = StepBuffers(self.device, capacity=max(1 << 14, min(want, 1 << 22)))
         self.n_steps = 0
+        self.host_seconds = 0.0
         self._sampler = None
         self._graphs: dict = {}
         self._graph_pool = torch.cuda.graph_pool_handle() if options.cuda_graphs else None
@@ -123,6 +124,15 @@ class Engine:
         return logits.clone() if replayed else logits
 
     def _step(self, entries, want=None, feed_tokens=None):
+        t_host = time.perf_counter()
+        try:
+            return self._step_inner(entries, want, feed_tokens)
+        finally:
+            # the host's own time in steps (checks, step buffer, launches; no waiting for the GPU except
+            # where a launch queue is full)
+            self.host_seconds += time.perf_counter() - t_host
+
+    def _step_inner(self, entries, want=None, feed_tokens=None):
         lay, ctx = self._prepare(entries, want)
         if feed_tokens is not None:
             ctx.tokens.copy_(feed_tokens)      # on the stream, after the step buffer's copy

@@ -86,20 +86,21 @@ def _pages(n_tokens: int) -> int:
 
 def plan_batches(prompt_lens, new_lens, limits: Limits) -> list:
     """Requests in arrival order, cut into batches that start together: at
-    most max_batch sequences, whose pages at their final lengths fit the
-    cache, and whose prompts fit one step.  A request too large for either
-    limit alone still gets a batch of its own (its prompt is then fed in
-    several steps, or the cache refuses it)."""
-    batches, cur, pages, toks = [], [], 0, 0
+    most max_batch sequences whose pages at their final lengths fit the cache.
+    Prompts that do not fit one step together are fed in several steps (each
+    sequence's tokens in order), after which the whole batch decodes together:
+    the step limit bounds a step, not the width of a batch.  A request too
+    large for the cache alone still gets a batch of its own (the cache then
+    refuses it)."""
+    batches, cur, pages = [], [], 0
     budget = _pages(limits.max_tokens)
     for i, (p, n) in enumerate(zip(prompt_lens, new_lens)):
         need = _pages(p + max(0, n - 1))
-        if cur and (len(cur) >= limits.max_batch or pages + need > budget or toks + p > limits.max_step_tokens):
+        if cur and (len(cur) >= limits.max_batch or pages + need > budget):
             batches.append(cur)
-            cur, pages, toks = [], 0, 0
+            cur, pages = [], 0
         cur.append(i)
         pages += need
-        toks += p
     if cur:
         batches.append(cur)
     return batches

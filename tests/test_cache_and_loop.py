@@ -197,11 +197,27 @@ def test_callback_cancels_one_sequence_only():
     assert (0, 5) in seen and (1, 9) in seen
 
 
-def test_plan_batches_respects_pages_and_step_tokens():
+def test_plan_batches_respects_pages_and_slots():
     lim = Limits(max_batch=8, max_tokens=64 * 4, max_step_tokens=100, max_seq_len=512)
-    assert plan_batches([60, 60, 60], [1, 1, 1], lim) == [[0], [1], [2]]           # step tokens
+    assert plan_batches([60, 60, 60], [1, 1, 1], lim) == [[0, 1, 2]]               # one batch, prompts over two steps
     assert plan_batches([10, 10, 10], [120, 120, 10], lim) == [[0], [1, 2]]        # pages: 3 + 3 > 4, 3 + 1 fit
-    assert plan_batches([300], [1], lim) == [[0]]                                  # alone, fed in chunks
+    assert plan_batches([300], [1], lim) == [[0]]                                  # alone (the cache refuses it)
+    wide = Limits(max_batch=8, max_tokens=64 * 64, max_step_tokens=4, max_seq_len=512)
+    assert plan_batches([1] * 20, [1] * 20, wide) == [list(range(8)), list(range(8, 16)), list(range(16, 20))]
+
+
+def test_prompts_beyond_one_step_are_fed_over_several_and_decode_together():
+    scripts = {1: [5, 5, 5], 2: [6, 6, 6], 3: [7, 7, 7]}
+    lim = Limits(max_batch=3, max_tokens=64 * 8, max_step_tokens=10, max_seq_len=128)
+    be, loop = _loop(scripts, lim)
+    reqs = [Request([1] + [20] * 6, max_tokens=3), Request([2] + [21] * 7, max_tokens=3), Request([3, 22], max_tokens=3)]
+    outs = loop.run(reqs)
+    assert [o.tokens for o in outs] == [[5, 5, 5], [6, 6, 6], [7, 7, 7]]
+    # 7 + 8 + 2 prompt tokens under a step limit of 10: two prompt steps, then the three decode as one batch
+    assert [sum(len(t) for _, t in st) for st in be.steps[:2]] == [10, 7]
+    assert [len(st) for st in be.steps[2:]] == [3, 3]
+    fed = {f[0]: f for _, f in be.released}
+    assert fed[1][:7] == [1] + [20] * 6 and fed[2][:8] == [2] + [21] * 7 and fed[3][:2] == [3, 22]
 
 
 def test_long_prompt_is_fed_in_chunks_and_sampled_once():

@@ -355,7 +355,9 @@ def test_gemm_tc(T, N, K):
 
 
 @pytest.mark.parametrize("T, N, K", [(129, 256, 64), (300, 520, 320), (2048, 1024, 512), (600, 20480, 192),
-                                     (1000, 200, 1000), (257, 4096 + 128, 4096)])
+                                     (1000, 200, 1000), (257, 4096 + 128, 4096),
+                                     # more units than CTA pairs, and not a multiple of them: a last round partly empty
+                                     (2048, 4096, 1024), (700, 9728, 520), (2048, 6144, 4096), (1500, 2560, 72)])
 def test_gemm_tc_pair(T, N, K):
     """The CTA-pair (cta_group::2) kernel against float64, plain and gated."""
     from llmoxide_b200 import kernels
@@ -370,6 +372,9 @@ def test_gemm_tc_pair(T, N, K):
     kernels.gemm_tc(xd, wd, out32, pair=True)
     assert kernels.gemm_tc_status() == 0
     assert rel(out32, want) < 1e-5
+    again = torch.full((T, N), float("nan"), dtype=torch.float32, device=DEV)
+    kernels.gemm_tc(xd, wd, again, pair=True)          # the same bits every time
+    assert torch.equal(again, out32)
     out16 = torch.empty(T, N, dtype=torch.bfloat16, device=DEV)
     kernels.gemm_tc(xd, wd, out16, pair=True)
     assert rel(out16, want) < 6e-3
