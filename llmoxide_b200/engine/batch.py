@@ -71,6 +71,7 @@ class StepContext:
     want_rows: torch.Tensor
     block_tables: list
     widths: tuple
+    probe: object = None     # callable(name, tensor) for named intermediates of the step, or None
 
 
 def build_host_arrays(entries, wants, lengths, page_rows, n_groups):

@@ -113,30 +113,34 @@ class Engine:
 
     # ---- the step --------------------------------------------------------------
 
-    def step(self, entries, want=None) -> torch.Tensor:
+    def step(self, entries, want=None, probe=None) -> torch.Tensor:
         """``entries``: [(slot, token ids)]; every sequence brings at least one
         token, appended at its current length.  ``want``: per entry the places
         among its tokens whose logits are asked for (default: the last).
         Returns float32 logits [wanted, vocab] on the device, in the order of
-        the entries and of ``want``."""
-        logits, replayed = self._step(entries, want)
+        the entries and of ``want``.  ``probe(name, tensor)`` is called with the
+        step's named intermediates over its packed tokens (the reference traces
+        the same stages, crates/model/src/qwen35/cpu.rs:136-415); such a step
+        runs eagerly, with every norm as one kernel."""
+        logits, replayed = self._step(entries, want, probe=probe)
         # A replayed graph writes its logits to the same memory every time.
         return logits.clone() if replayed else logits
 
-    def _step(self, entries, want=None, feed_tokens=None):
+    def _step(self, entries, want=None, feed_tokens=None, probe=None):
         t_host = time.perf_counter()
         try:
-            return self._step_inner(entries, want, feed_tokens)
+            return self._step_inner(entries, want, feed_tokens, probe)
         finally:
             # the host's own time in steps (checks, step buffer, launches; no waiting for the GPU except
             # where a launch queue is full)
             self.host_seconds += time.perf_counter() - t_host
 
-    def _step_inner(self, entries, want=None, feed_tokens=None):
+    def _step_inner(self, entries, want=None, feed_tokens=None, probe=None):
         lay, ctx = self._prepare(entries, want)
+        ctx.probe = probe
         if feed_tokens is not None:
             ctx.tokens.copy_(feed_tokens)      # on the stream, after the step buffer's copy
-        replayed = bool(self.options.cuda_graphs and ctx.is_decode and self.model.graph_safe)
+        replayed = bool(self.options.cuda_graphs and ctx.is_decode and self.model.graph_safe and probe is None)
         if replayed:
             logits = self._graphed_forward(lay, ctx, [slot for slot, _ in entries])
         elif ctx.is_decode or self.options.overlap_prompt_kernels:

@@ -12,6 +12,7 @@ from __future__ import annotations
 
 import torch
 
+from .. import kernels
 from ..cache import Cache
 from ..config.spec import ModelSpec
 from ..parts import Runtime, build_block
@@ -72,11 +73,25 @@ class DecoderModel:
         d = self.spec.hidden_size
         h = torch.empty((ctx.n_tokens, d), dtype=torch.float32, device=self.rt.device)
         self.embedding.forward(ctx.tokens, h)
+        probe = ctx.probe
+        if probe:
+            probe("model.input_embed", h)
         pending = None
-        for call in self.spec.schedule:
+        for i, call in enumerate(self.spec.schedule):
+            if probe:
+                # a block reports by stage; the stage of the residual stream entering call i is the output of call i-1
+                ctx.probe = (lambda name, t, i=i: probe(f"{name}-{i}", t) if name != "resid_in"
+                             else (probe(f"l_out-{i - 1}", t) if i else None))
             pending = self.blocks[call.layer].forward(h, pending, ctx, cache.view(call.cache), call.writes_cache)
+        ctx.probe = probe
+        if probe and pending is not None:
+            kernels.add_rms_norm(h, pending, self.final_norm.gain, self.final_norm.eps, None)     # h += the last delta
+            pending = None
+            probe(f"l_out-{len(self.spec.schedule) - 1}", h)
         n_want = ctx.want_rows.numel()
         if n_want == 0:
             return torch.empty((0, self.spec.vocab_size), dtype=torch.float32, device=self.rt.device)
         x = self.final_norm.add_forward(h, pending, rows=ctx.want_rows, write_h=False)
+        if probe:
+            probe("result_norm", x)
         return self.head.forward(x)

@@ -25,7 +25,10 @@ from .engine import Engine, LoadOptions
 
 
 class Replayer:
-    def __init__(self, engine: Engine, out_dir):
+    def __init__(self, engine: Engine, out_dir, dump: bool = False):
+        """With ``dump`` every step also writes its named intermediates, ``<step>.<name>.f32`` as float32
+        [tokens of the step, width], for finding the first stage at which two runs part."""
+        self.dump = dump
         self.engine, self.out = engine, Path(out_dir)
         self.out.mkdir(parents=True, exist_ok=True)
         self.slots: dict = {}
@@ -40,7 +43,11 @@ class Replayer:
             entries.append((self.slots[rid], list(e["tokens"])))
             want.append(list(e.get("want", [])))
         if entries:
-            logits = self.engine.step(entries, want)
+            probe = None
+            if self.dump:
+                def probe(name, t, step=step):
+                    t.detach().float().cpu().numpy().astype("<f4").tofile(self.out / f"{step}.{name}.f32")
+            logits = self.engine.step(entries, want, probe=probe)
             if logits.shape[0] > 0:
                 arr = logits.detach().cpu().numpy().astype("<f4", copy=False)
                 self.engine.check_status()        # the copy waited for the step: its kernels' reports are in
@@ -62,12 +69,14 @@ def main(argv=None) -> int:
     ap.add_argument("--out", required=True, help="folder that receives <step>.f32")
     ap.add_argument("--max-tokens", type=int, required=True,
                     help="most tokens live requests hold at any time, each rounded up to a multiple of 64")
+    ap.add_argument("--dump", action="store_true",
+                    help="also write every step's named intermediates as <step>.<name>.f32")
     args = ap.parse_args(argv)
     opts = LoadOptions(dtype=args.dtype, max_tokens=args.max_tokens,
                        max_batch=max(1, (args.max_tokens + 63) // 64),
                        max_step_tokens=max(args.max_tokens, 64))
     engine = Engine.load(args.model, opts)
-    rp = Replayer(engine, args.out)
+    rp = Replayer(engine, args.out, dump=args.dump)
     for line in sys.stdin:
         line = line.strip()
         if not line:

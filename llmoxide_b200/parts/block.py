@@ -9,6 +9,9 @@ adding it itself."""
 
 from __future__ import annotations
 
+import torch
+
+from .. import kernels
 from .registry import (ARRANGEMENTS, FEED_FORWARDS, MIXERS, NORMS, POSITIONS, lookup, register_arrangement)
 
 
@@ -37,16 +40,36 @@ class PreNormBlock:
         return libs
 
     def forward(self, h, pending, ctx, view, writes_cache=True):
-        x = _norm(self.mixer_norm, h, pending, self.mixer)
+        probe = getattr(ctx, "probe", None)
+        x = _norm(self.mixer_norm, h, pending, self.mixer, plain=probe is not None)
+        if probe:
+            probe("resid_in", h), probe("attn_norm", x)      # names after crates/model/src/qwen35/cpu.rs:136-401
         a = self.mixer.forward(x, ctx, view, writes_cache)
-        x = _norm(self.ff_norm, h, a, self.feed_forward)
-        return self.feed_forward.forward(x, ctx)
+        if probe:
+            probe("attn_output", _summed(a))
+        x = _norm(self.ff_norm, h, a, self.feed_forward, plain=probe is not None)
+        if probe:
+            probe("attn_residual", h), probe("attn_post_norm", x)
+        out = self.feed_forward.forward(x, ctx)
+        if probe:
+            probe("ffn_out", _summed(out))
+        return out
 
 
-def _norm(norm, h, delta, consumer):
+def _summed(delta):
+    """A delta as one tensor: split partials [S,T,d] are added in order."""
+    if delta.dim() == 2:
+        return delta
+    out = torch.empty(delta.shape[1:], dtype=torch.float32, device=delta.device)
+    kernels.sum_splits(delta, out)
+    return out
+
+
+def _norm(norm, h, delta, consumer, plain=False):
     """h += delta; x = norm(h).  Where both sides can, the norm is done in two halves: the norm part leaves the
-    scale to the consumer's first products (``takes_row_scales`` on the consumer, ``row_scales_ok`` on the norm)."""
-    if getattr(consumer, "takes_row_scales", False) and getattr(norm, "ROW_SCALE_MAX_TOKENS", 0):
+    scale to the consumer's first products (``takes_row_scales`` on the consumer, ``row_scales_ok`` on the norm);
+    not when the step's intermediates are asked for (``plain``), which wants the normalised rows themselves."""
+    if not plain and getattr(consumer, "takes_row_scales", False) and getattr(norm, "ROW_SCALE_MAX_TOKENS", 0):
         return norm.add_forward(h, delta, row_scales_ok=True)
     return norm.add_forward(h, delta)
 

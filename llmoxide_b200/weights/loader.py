@@ -20,7 +20,7 @@ import sys
 import torch
 
 from ..config.spec import ModelSpec
-from ..errors import WeightsError
+from ..errors import CheckpointFormatError, WeightsError
 from .safetensors_io import open_checkpoint
 
 _FLOATS = ("F32", "F16", "BF16")
@@ -66,9 +66,25 @@ def target_dtype(stored: torch.dtype, compute: str) -> torch.dtype:
     return torch.bfloat16
 
 
+VERIFY_SPAN = 256      # elements read back at the head and at the tail of every uploaded tensor
+
+
+def _verify_upload(name: str, host: torch.Tensor, dev: torch.Tensor) -> None:
+    """Reads the first and last elements of an uploaded tensor back and compares them with what was sent
+    (the reference checks head and tail spans of every buffer it uploads, crates/gpu/src/lib.rs:700-712)."""
+    flat_h, flat_d = host.reshape(-1), dev.reshape(-1)
+    n = flat_h.numel()
+    for lo, hi in ((0, min(n, VERIFY_SPAN)), (max(0, n - VERIFY_SPAN), n)):
+        want = flat_h[lo:hi].to(flat_d.dtype)
+        got = flat_d[lo:hi].cpu()
+        if not torch.equal(got.view(torch.uint8), want.contiguous().view(torch.uint8)):
+            raise CheckpointFormatError(f"{name}: elements {lo}..{hi} read back from the device differ from the file")
+
+
 def load_checkpoint(folder, spec: ModelSpec, dtype: str = "bfloat16", device="cuda",
-                    progress=None) -> dict:
-    """name -> tensor on ``device`` for every tensor of ``spec``."""
+                    progress=None, verify: bool = True) -> dict:
+    """name -> tensor on ``device`` for every tensor of ``spec``; with ``verify`` the head and the tail of
+    every tensor are read back and compared."""
     if dtype not in ("bfloat16", "float32"):
         raise ValueError(f"dtype {dtype!r}: expected 'bfloat16' or 'float32'")
     entries = open_checkpoint(folder)
@@ -80,6 +96,8 @@ def load_checkpoint(folder, spec: ModelSpec, dtype: str = "bfloat16", device="cu
         e = entries[name]
         host = e.file.tensor(name)
         out[name] = host.to(device=device, dtype=target_dtype(host.dtype, dtype), copy=True)
+        if verify:
+            _verify_upload(name, host, out[name])
         if progress is not None:
             progress(i + 1, len(names), name)
     return out

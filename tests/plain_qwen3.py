@@ -183,12 +183,23 @@ def swiglu_ffn(x, lw):
     return linear(silu(gate) * up, lw["mlp.down_proj.weight"])
 
 
-def block(h, lw, cfg, positions, window):
-    """h += mixer(norm(h)); h += ffn(norm(h)).
-    crates/model/src/qwen35/cpu.rs:141-146,374-400"""
+def block(h, lw, cfg, positions, window, trace=None, il=0):
+    """h += mixer(norm(h)); h += ffn(norm(h)).  ``trace(name, tensor)`` gets the stages under the reference's
+    names.  crates/model/src/qwen35/cpu.rs:141-146,374-400 (trace names :147,:369,:377,:384,:396,:401)"""
     eps = cfg["rms_norm_eps"]
-    h = h + attention_mixer(rms_norm(h, lw["input_layernorm.weight"], eps), lw, cfg, positions, window)
-    h = h + swiglu_ffn(rms_norm(h, lw["post_attention_layernorm.weight"], eps), lw)
+    t = trace or (lambda name, x: None)
+    x = rms_norm(h, lw["input_layernorm.weight"], eps)
+    t(f"attn_norm-{il}", x)
+    a = attention_mixer(x, lw, cfg, positions, window)
+    t(f"attn_output-{il}", a)
+    h = h + a
+    t(f"attn_residual-{il}", h)
+    x = rms_norm(h, lw["post_attention_layernorm.weight"], eps)
+    t(f"attn_post_norm-{il}", x)
+    f = swiglu_ffn(x, lw)
+    t(f"ffn_out-{il}", f)
+    h = h + f
+    t(f"l_out-{il}", h)
     return h
 
 
@@ -197,17 +208,21 @@ def layer_weights(weights: dict, i: int) -> dict:
     return {k[len(prefix) :]: v for k, v in weights.items() if k.startswith(prefix)}
 
 
-def forward(cfg: dict, weights: dict, tokens) -> torch.Tensor:
+def forward(cfg: dict, weights: dict, tokens, trace=None) -> torch.Tensor:
     """Logits [T, V] at every position of one whole sequence that starts at
     position 0.  Final norm, then the head; the head is the embedding table
     when the folder has no lm_head.  crates/model/src/qwen35/cpu.rs:110-417,
     crates/model/src/qwen35/weights.rs:79"""
     positions = list(range(len(tokens)))
     h = embed(weights["model.embed_tokens.weight"], tokens)
+    if trace:
+        trace("model.input_embed", h)
     windows = layer_windows(cfg)
     for i in range(cfg["num_hidden_layers"]):
-        h = block(h, layer_weights(weights, i), cfg, positions, windows[i])
+        h = block(h, layer_weights(weights, i), cfg, positions, windows[i], trace, i)
     h = rms_norm(h, weights["model.norm.weight"], cfg["rms_norm_eps"])
+    if trace:
+        trace("result_norm", h)
     head = weights.get("lm_head.weight")
     if head is None:
         head = weights["model.embed_tokens.weight"]

@@ -131,3 +131,75 @@ def test_a_step_of_more_than_65535_tokens(folders):
         for i in (0, 37, 69):
             want = plain.forward(cfg, w, toks[i])[-1].numpy()
             assert ru.rel_err(logits[i][None], want[None]) <= ru.TOL[dtype], (dtype, i)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_named_intermediates_find_the_first_stage_that_differs(folders, tmp_path, dtype):
+    """A step can hand out its named intermediates (the reference's trace names).  Whole prompt against the
+    plain implementation's trace, stage by stage; then a fault is put into the engine's weights (the gain of the
+    second layer's pre-feed-forward norm), and walking the stages in order finds it at that stage."""
+    import plain_qwen3 as plain
+
+    name = "D"
+    folder = folders[(name, dtype)]
+    toks = prompts(ALL[name]["vocab_size"], [150], seed=5)[0]
+    cfg, w = plain.read_model(folder)
+    want = {}
+    plain.forward(cfg, w, toks, trace=lambda n, x: want.__setitem__(n, x.numpy().copy()))
+    order = list(want)
+    assert order[:3] == ["model.input_embed", "attn_norm-0", "attn_output-0"] and order[-1] == "result_norm"
+    tol = {"float32": 2e-5, "bfloat16": 3e-2}[dtype]
+
+    def stages(eng):
+        got = {}
+        slot = eng.acquire()
+        eng.step([(slot, toks)], [list(range(len(toks)))], probe=lambda n, t: got.__setitem__(n, t.float().cpu().numpy()))
+        eng.release(slot)
+        return got
+
+    def first_bad(got):
+        for n in order:
+            if ru.rel_err(got[n], want[n]) > tol:
+                return n
+        return None
+
+    eng = _engine(folder, dtype)
+    got = stages(eng)
+    assert set(order) <= set(got), sorted(set(order) - set(got))
+    assert first_bad(got) is None, first_bad(got)
+    eng.model.blocks[1].ff_norm.gain.mul_(1.5)
+    assert first_bad(stages(eng)) == "attn_post_norm-1"
+    # through the replay program's own class: one file per stage and step
+    from llmoxide_b200.engine.replay import Replayer
+    eng2 = _engine(folder, dtype)
+    rp = Replayer(eng2, tmp_path / "dump", dump=True)
+    rp.run_step(dict(step=0, entries=[dict(id="a", tokens=toks[:70], want=[69])], end=[]))
+    rp.run_step(dict(step=1, entries=[dict(id="a", tokens=toks[70:71], want=[0])], end=["a"]))
+    d = ALL[name]["hidden_size"]
+    first = np.fromfile(tmp_path / "dump" / "0.l_out-1.f32", dtype="<f4").reshape(70, d)
+    assert ru.rel_err(first, want["l_out-1"][:70]) <= tol
+    second = np.fromfile(tmp_path / "dump" / "1.attn_residual-0.f32", dtype="<f4").reshape(1, d)
+    assert ru.rel_err(second, want["attn_residual-0"][70:71]) <= tol
+
+
+def test_a_damaged_upload_is_noticed(folders, monkeypatch):
+    """The head and the tail of every tensor are read back after the copy to the device."""
+    from llmoxide_b200.config import read_config
+    from llmoxide_b200.errors import CheckpointFormatError
+    from llmoxide_b200.weights import loader
+
+    folder = folders[("A", "float32")]
+    spec = read_config(folder).to_spec()
+    good = loader.load_checkpoint(folder, spec, "float32", "cuda")
+    assert len(good) == len(spec.tensors())
+    real = torch.Tensor.to
+
+    def lossy(self, *a, **kw):
+        out = real(self, *a, **kw)
+        if kw.get("device") is not None and out.is_cuda and out.numel() == 64 * 128:     # one matrix of A's layers
+            out.view(-1)[-1] += 1.0
+        return out
+
+    monkeypatch.setattr(torch.Tensor, "to", lossy)
+    with pytest.raises(CheckpointFormatError, match="read back"):
+        loader.load_checkpoint(folder, spec, "float32", "cuda")
