@@ -1,6 +1,8 @@
 """Host-side bookkeeping of the cache: which slot belongs to which live
 sequence, which pages each slot holds in each group of layers, and each
-sequence's own length.  No tensors here, so it is tested without a GPU.
+sequence's own length.  No tensors here, so it is tested without a GPU.  The
+bookkeeping itself is C++ (``csrc/host_runtime.cpp``, built with the C++
+compiler alone); this class holds the handle and raises the typed errors.
 
 A *slot* is one live sequence's entry.  A *page* holds ``PAGE`` consecutive
 positions of one sequence for every layer of one *group* (layers with the same
@@ -16,53 +18,71 @@ attended to).  Lengths only grow: there is no rewind
 
 from __future__ import annotations
 
-from dataclasses import dataclass, field
+import ctypes
+from ctypes import c_char_p, c_int, c_longlong, c_void_p
 from typing import Optional
 
 from ..errors import CacheExhausted, CacheMisuse, ContextOverflow
 
 PAGE = 64
 
+# codes of csrc/host_runtime.cpp
+_MISUSE, _OVERFLOW_SEQ, _EXHAUSTED, _BAD_VALUE, _OVERFLOW_STEP, _TOO_SMALL = 1, 2, 3, 4, 5, 6
+_lib = None
+
 
 def pages_for(n_tokens: int) -> int:
     return (n_tokens + PAGE - 1) // PAGE
 
 
-class PagePool:
-    """Free list of physical pages of one group."""
+def host_library():
+    """The host runtime, built on first use."""
+    global _lib
+    if _lib is None:
+        from ..csrc.build import load_library
 
-    def __init__(self, n_pages: int):
-        self.n_pages = n_pages
-        self._free = list(range(n_pages - 1, -1, -1))  # pop() hands out low ids first
-        self._held = [False] * n_pages
+        lib = load_library("host_runtime")
+        P = ctypes.POINTER
+        lib.llmx_alloc_new.restype = c_void_p
+        lib.llmx_alloc_new.argtypes = [c_int, c_int, P(c_int), c_int, c_longlong]
+        lib.llmx_alloc_delete.argtypes = [c_void_p]
+        lib.llmx_alloc_delete.restype = None
+        for name in ("acquire", "check", "n_free_slots"):
+            getattr(lib, f"llmx_alloc_{name}").argtypes = [c_void_p]
+        for name in ("release", "unreserve", "n_free_pages"):
+            getattr(lib, f"llmx_alloc_{name}").argtypes = [c_void_p, c_int]
+        for name in ("reserve", "commit"):
+            getattr(lib, f"llmx_alloc_{name}").argtypes = [c_void_p, c_int, c_longlong]
+        lib.llmx_alloc_commit_many.argtypes = [c_void_p, c_int, c_void_p, c_void_p]
+        lib.llmx_alloc_length.argtypes = [c_void_p, c_int]
+        lib.llmx_alloc_length.restype = c_longlong
+        lib.llmx_alloc_generation.argtypes = [c_void_p, c_int]
+        lib.llmx_alloc_generation.restype = c_longlong
+        lib.llmx_alloc_page_row.argtypes = [c_void_p, c_int, c_int, c_void_p, c_int]
+        lib.llmx_host_error.argtypes = [c_char_p, c_int, P(c_longlong)]
+        lib.llmx_pack_step.argtypes = [c_int] + [c_void_p] * 6 + [c_int] + [c_void_p] * 4 + [c_longlong, c_void_p]
+        lib.llmx_plan_step.argtypes = [c_void_p, c_int] + [c_void_p] * 5 + [c_int, c_longlong, c_int, c_void_p,
+                                                                              c_longlong, c_void_p]
+        _lib = lib
+    return _lib
 
-    @property
-    def n_free(self) -> int:
-        return len(self._free)
 
-    def take(self, n: int) -> list:
-        if n > len(self._free):
-            raise CacheExhausted(f"{n} more cache pages are needed, {len(self._free)} of {self.n_pages} are free")
-        out = [self._free.pop() for _ in range(n)]
-        for p in out:
-            self._held[p] = True
-        return out
-
-    def give_back(self, pages) -> None:
-        for p in pages:
-            if not (0 <= p < self.n_pages) or not self._held[p]:
-                raise CacheMisuse(f"page {p} is given back but is not held")
-            self._held[p] = False
-            self._free.append(p)
-
-
-@dataclass
-class SlotState:
-    length: int = 0                    # positions written so far
-    reserved: int = 0                  # positions that have pages (>= length)
-    pages: list = field(default_factory=list)   # per group: logical page -> physical page or -1
-    live: bool = False
-    generation: int = 0                # counts owners of this slot
+def raise_host_error(code: int) -> None:
+    """The typed error for a non-zero code of the host runtime, with its message."""
+    lib = host_library()
+    buf = ctypes.create_string_buffer(600)
+    info = (c_longlong * 2)()
+    lib.llmx_host_error(buf, 600, info)
+    msg = buf.value.decode()
+    if code == _MISUSE:
+        raise CacheMisuse(msg)
+    if code == _OVERFLOW_SEQ:
+        raise ContextOverflow(int(info[0]), int(info[1]), "longest sequence the cache allows")
+    if code == _EXHAUSTED:
+        raise CacheExhausted(msg)
+    if code == _OVERFLOW_STEP:
+        raise ContextOverflow(int(info[0]), int(info[1]), "step limit (max_step_tokens)")
+    raise ValueError(msg)
 
 
 class CacheAllocator:
@@ -74,116 +94,83 @@ class CacheAllocator:
         self.n_slots, self.n_pages = n_slots, n_pages
         self.windows = list(windows)
         self.max_seq_len = max_seq_len if max_seq_len is not None else n_pages * PAGE
-        self.pools = [PagePool(n_pages) for _ in self.windows]
-        self.slots = [SlotState() for _ in range(n_slots)]
-        self._free_slots = list(range(n_slots - 1, -1, -1))
+        self._lib = host_library()
+        w = (c_int * len(self.windows))(*[int(x) if x else 0 for x in self.windows])
+        self._h = self._lib.llmx_alloc_new(n_slots, n_pages, w, len(self.windows), self.max_seq_len)
+        if not self._h:
+            raise ValueError("the cache needs at least one slot, one page and one group")
+        self._row = (c_int * max(1, n_pages))()
+
+    def __del__(self):
+        h, self._h = getattr(self, "_h", None), None
+        if h and self._lib is not None:
+            self._lib.llmx_alloc_delete(h)
+
+    @property
+    def handle(self):
+        return self._h
+
+    def _ok(self, code: int) -> None:
+        if code:
+            raise_host_error(code)
 
     # ---- slots -----------------------------------------------------------
 
     @property
     def n_free_slots(self) -> int:
-        return len(self._free_slots)
+        return self._lib.llmx_alloc_n_free_slots(self._h)
 
     def acquire(self) -> int:
-        if not self._free_slots:
-            raise CacheExhausted(f"all {self.n_slots} cache slots are held by live sequences")
-        s = self._free_slots.pop()
-        st = self.slots[s]
-        st.length = st.reserved = 0
-        st.pages = [[] for _ in self.windows]
-        st.live = True
-        st.generation += 1
+        s = self._lib.llmx_alloc_acquire(self._h)
+        if s < 0:
+            raise_host_error(-s)
         return s
 
     def release(self, slot: int) -> None:
-        st = self._live(slot)
-        for pool, pages in zip(self.pools, st.pages):
-            pool.give_back([p for p in pages if p >= 0])
-        st.pages = [[] for _ in self.windows]
-        st.length = st.reserved = 0
-        st.live = False
-        self._free_slots.append(slot)
-
-    def _live(self, slot: int) -> SlotState:
-        if not (0 <= slot < self.n_slots):
-            raise CacheMisuse(f"slot {slot} does not exist (there are {self.n_slots})")
-        st = self.slots[slot]
-        if not st.live:
-            raise CacheMisuse(f"slot {slot} is not held by a live sequence (freed twice, or used after being freed)")
-        return st
+        self._ok(self._lib.llmx_alloc_release(self._h, slot))
 
     def length(self, slot: int) -> int:
-        return self._live(slot).length
+        n = self._lib.llmx_alloc_length(self._h, slot)
+        if n < 0:
+            raise_host_error(_MISUSE)
+        return int(n)
+
+    def generation(self, slot: int) -> int:
+        """How many owners the slot has had."""
+        return int(self._lib.llmx_alloc_generation(self._h, slot))
 
     # ---- a step: reserve pages, then commit the new length ---------------
 
     def reserve(self, slot: int, n_new: int) -> None:
         """Makes sure positions length .. length+n_new-1 have pages in every
         group.  Raises before anything is changed if they do not fit."""
-        st = self._live(slot)
-        new_len = st.length + n_new
-        if new_len > self.max_seq_len:
-            raise ContextOverflow(new_len, self.max_seq_len, "longest sequence the cache allows")
-        want = pages_for(new_len)
-        for pool, pages in zip(self.pools, st.pages):
-            need = want - len(pages)
-            if need > pool.n_free:
-                raise CacheExhausted(
-                    f"slot {slot} needs {need} more cache pages for {new_len} positions, "
-                    f"{pool.n_free} of {pool.n_pages} are free")
-        for pool, pages in zip(self.pools, st.pages):
-            pages.extend(pool.take(want - len(pages)))
-        st.reserved = max(st.reserved, new_len)
+        self._ok(self._lib.llmx_alloc_reserve(self._h, slot, n_new))
 
     def unreserve(self, slot: int) -> None:
         """Takes back a reservation that no step will use: pages beyond those the slot's length needs return
-        to their pools (a step that was refused for another sequence of its batch calls this for the
+        to their pools (a step that was refused for another sequence of its batch does this for the
         sequences it had already reserved for)."""
-        st = self._live(slot)
-        keep = pages_for(st.length)
-        for pool, pages in zip(self.pools, st.pages):
-            pool.give_back([p for p in pages[keep:] if p >= 0])
-            del pages[keep:]
-        st.reserved = st.length
+        self._ok(self._lib.llmx_alloc_unreserve(self._h, slot))
 
     def commit(self, slot: int, n_new: int) -> None:
         """The step wrote n_new positions: the length grows, and groups with a
         window give back the pages no later query can see."""
-        st = self._live(slot)
-        if st.length + n_new > st.reserved:
-            raise CacheMisuse(f"slot {slot}: {n_new} positions are committed but only "
-                              f"{st.reserved - st.length} were reserved")
-        st.length += n_new
-        for pool, pages, window in zip(self.pools, st.pages, self.windows):
-            if window is None:
-                continue
-            # The next query sits at position `length` and sees keys from
-            # length - (window - 1) on; whole pages below that are dead.
-            first_visible = max(0, st.length - (window - 1))
-            dead = first_visible // PAGE
-            gone = [p for p in pages[:dead] if p >= 0]
-            if gone:
-                pool.give_back(gone)
-                for i in range(dead):
-                    pages[i] = -1
+        self._ok(self._lib.llmx_alloc_commit(self._h, slot, n_new))
+
+    def commit_many(self, slots, counts) -> None:
+        n = len(slots)
+        self._ok(self._lib.llmx_alloc_commit_many(self._h, n, (c_int * n)(*slots), (c_int * n)(*counts)))
 
     def page_row(self, slot: int, group: int) -> list:
         """Logical page -> physical page (-1 where a page was given back)."""
-        return self._live(slot).pages[group]
+        n = self._lib.llmx_alloc_page_row(self._h, slot, group, self._row, len(self._row))
+        if n < 0:
+            raise_host_error(_MISUSE)
+        return list(self._row[:n])
 
     def pages_held(self, group: int = 0) -> int:
-        return self.pools[group].n_pages - self.pools[group].n_free
+        return self.n_pages - self._lib.llmx_alloc_n_free_pages(self._h, group)
 
     def check_consistent(self) -> None:
         """No page held twice or lost; used by tests."""
-        for g, pool in enumerate(self.pools):
-            held = [p for st in self.slots if st.live for p in st.pages[g] if p >= 0]
-            if len(held) != len(set(held)):
-                raise CacheMisuse(f"group {g}: a page is held twice")
-            if len(held) + pool.n_free != pool.n_pages:
-                raise CacheMisuse(f"group {g}: {pool.n_pages - pool.n_free - len(held)} pages are lost")
-            if set(held) & set(pool._free):
-                raise CacheMisuse(f"group {g}: a held page is also on the free list")
-        live = [i for i, st in enumerate(self.slots) if st.live]
-        if len(live) + len(self._free_slots) != self.n_slots or set(live) & set(self._free_slots):
-            raise CacheMisuse("a slot is lost or both live and free")
+        self._ok(self._lib.llmx_alloc_check(self._h))

@@ -43,6 +43,8 @@ LIBRARIES = {
     "gemm_tc": (["gemm_tc.cu"], []),
     "sampling": (["sampling.cu"], []),
     "random_init": (["random_init.cu"], []),
+    # host code only (no CUDA): the cache's bookkeeping and the step plan
+    "host_runtime": (["host_runtime.cpp"], []),
 }
 HEADERS = ["common.cuh", "attention_decode_noalloc.h", "tc_ptx.cuh"]
 
@@ -65,6 +67,20 @@ def find_nvcc() -> str:
                            "llmoxide_b200 cannot be built, and there is no other path")
 
 
+def _host_only(name: str) -> bool:
+    return all(src.endswith(".cpp") for src in LIBRARIES[name][0])
+
+
+def find_cxx() -> str:
+    """The C++ compiler for the host-only library."""
+    for cand in (os.environ.get("CXX"), "g++", "c++", "clang++"):
+        found = shutil.which(cand) if cand else None
+        if found:
+            return found
+    raise ExtensionMissing("no C++ compiler was found (CXX, g++, c++): the host runtime of llmoxide_b200 "
+                           "cannot be built, and there is no other path")
+
+
 def _flags() -> list:
     # LLMX_NVCC_EXTRA: extra nvcc flags (for experiments with -D switches); part of the library's hash
     return list(NVCC_FLAGS) + os.environ.get("LLMX_NVCC_EXTRA", "").split()
@@ -73,7 +89,7 @@ def _flags() -> list:
 def _digest(name: str) -> str:
     sources, extra = LIBRARIES[name]
     h = hashlib.sha256()
-    for f in sorted(set(sources) | set(HEADERS)):
+    for f in sorted(set(sources) | (set() if _host_only(name) else set(HEADERS))):
         h.update(f.encode())
         h.update((SRC_DIR / f).read_bytes())
     h.update(" ".join(ARCH_FLAGS + _flags() + extra).encode())
@@ -122,7 +138,7 @@ def compile_library(name: str, verbose=True) -> Path:
     if have is not None:
         return have
     target = library_path(name, must_exist=False)
-    nvcc = find_nvcc()
+    nvcc = find_cxx() if _host_only(name) else find_nvcc()
     sources, extra = LIBRARIES[name]
     lock_path = target.with_suffix(".lock")
     with open(lock_path, "w") as lock_file:
@@ -131,10 +147,14 @@ def compile_library(name: str, verbose=True) -> Path:
             if target.is_file():  # another process built it meanwhile
                 return target
             tmp = target.with_name(f".{target.name}.{os.getpid()}.tmp")
-            cmd = [nvcc, *ARCH_FLAGS, *_flags(), *extra, "-I", str(SRC_DIR),
-                   *[str(SRC_DIR / s) for s in sources], "-o", str(tmp)]
+            if _host_only(name):
+                cmd = [nvcc, "-O2", "-std=c++17", "-shared", "-fPIC", "-fvisibility=hidden", *extra,
+                       *[str(SRC_DIR / s) for s in sources], "-o", str(tmp)]
+            else:
+                cmd = [nvcc, *ARCH_FLAGS, *_flags(), *extra, "-I", str(SRC_DIR),
+                       *[str(SRC_DIR / s) for s in sources], "-o", str(tmp)]
             if verbose:
-                _say(f"compiling {name} ({', '.join(sources)}) for sm_100a ...")
+                _say(f"compiling {name} ({', '.join(sources)})" + ("" if _host_only(name) else " for sm_100a") + " ...")
             t0 = time.time()
             proc = subprocess.Popen(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)
             done = threading.Event()

@@ -74,49 +74,78 @@ class StepContext:
     probe: object = None     # callable(name, tensor) for named intermediates of the step, or None
 
 
+N_FIXED = 7        # arrays before the block tables: tokens, token_seq, token_pos, seq_start, seq_past, seq_slot, want_rows
+_NAMES = ("tokens", "token_seq", "token_pos", "seq_start", "seq_past", "seq_slot", "want_rows")
+
+
+def layout_from_meta(meta) -> tuple:
+    """(layout, facts) from the numbers the C++ packer returns (csrc/host_runtime.cpp, write_meta)."""
+    n_tokens, n_seqs, n_want, total, max_new, max_len, is_decode, n_groups = (int(x) for x in meta[:8])
+    offs = [int(x) for x in meta[8 : 8 + N_FIXED + n_groups]]
+    widths = tuple(int(x) for x in meta[8 + N_FIXED + n_groups : 8 + N_FIXED + 2 * n_groups])
+    lay = StepLayout(n_tokens, n_seqs, n_want, widths)
+    sizes = (n_tokens, n_tokens, n_tokens, n_seqs + 1, n_seqs, n_seqs, n_want)
+    for name, at, n in zip(_NAMES, offs, sizes):
+        lay.offsets[name] = (at, n)
+    for g, w in enumerate(widths):
+        lay.offsets[f"block_table{g}"] = (offs[N_FIXED + g], n_seqs * w)
+    lay.total = total
+    return lay, dict(max_new=max_new, max_len=max_len, is_decode=bool(is_decode))
+
+
+def flatten_entries(entries, wants):
+    """The entries as the flat int32 arrays the C++ runtime takes; ``wants`` None: every entry's last token."""
+    n = len(entries)
+    slots = np.fromiter((s for s, _ in entries), dtype=np.int32, count=n)
+    counts = np.fromiter((len(t) for _, t in entries), dtype=np.int32, count=n)
+    toks = [t for _, t in entries]
+    tokens = (np.concatenate([np.asarray(t, dtype=np.int64) for t in toks]) if n and counts.sum() else
+              np.zeros(0, dtype=np.int64))
+    if tokens.size and (tokens.min() < -(1 << 31) or tokens.max() >= (1 << 31)):
+        raise ValueError("a token id does not fit 32 bits")
+    tokens = np.ascontiguousarray(tokens, dtype=np.int32)
+    if wants is None:
+        want_counts = np.full(n, -1, dtype=np.int32)
+        want_flat = np.zeros(1, dtype=np.int32)
+    else:
+        want_counts = np.fromiter((len(w) for w in wants), dtype=np.int32, count=n)
+        flat = [x for w in wants for x in w]
+        want_flat = np.asarray(flat if flat else [0], dtype=np.int32)
+    return slots, counts, tokens, want_counts, want_flat
+
+
 def build_host_arrays(entries, wants, lengths, page_rows, n_groups):
     """``entries``: [(slot, tokens)]; ``wants``: per entry the places among its
     tokens whose logits are wanted; ``lengths``: cached length per entry;
     ``page_rows[g][i]``: entry i's logical->physical page list in group g.
-    Returns (layout, int32 array, host facts)."""
-    n_seqs = len(entries)
-    counts = [len(t) for _, t in entries]
-    n_tokens = sum(counts)
-    seq_start = np.zeros(n_seqs + 1, dtype=np.int32)
-    seq_start[1:] = np.cumsum(counts)
-    tokens = np.concatenate([np.asarray(t, dtype=np.int64) for _, t in entries]).astype(np.int32)
-    token_seq = np.repeat(np.arange(n_seqs, dtype=np.int32), counts)
-    token_pos = np.concatenate(
-        [np.arange(p, p + c, dtype=np.int32) for p, c in zip(lengths, counts)])
-    want_rows = np.asarray(
-        [seq_start[i] + w for i, ws in enumerate(wants) for w in ws], dtype=np.int32)
-    final = [p + c for p, c in zip(lengths, counts)]
-    widths = []
-    tables = []
+    Returns (layout, int32 array, host facts).  The packing itself is the C++
+    runtime's (the engine's own steps go through its ``llmx_plan_step``, which
+    also checks and reserves)."""
+    from ..cache.allocator import host_library, raise_host_error
+
+    lib = host_library()
+    n = len(entries)
+    slots, counts, tokens, want_counts, want_flat = flatten_entries(entries, wants)
+    lens = np.asarray(lengths, dtype=np.int64)
+    rows, row_off, row_len = [], [], []
     for g in range(n_groups):
-        width = max(1, max((f + PAGE - 1) // PAGE for f in final))
-        # Round the width up so that a growing sequence changes the layout rarely.
-        width = _align(width, 4)
-        tab = np.full((n_seqs, width), -1, dtype=np.int32)
-        for i in range(n_seqs):
-            row = page_rows[g][i]
-            tab[i, : len(row)] = row
-        widths.append(width)
-        tables.append(tab)
-    lay = StepLayout.make(n_tokens, n_seqs, len(want_rows), widths)
-    buf = np.zeros(lay.total, dtype=np.int32)
-
-    def put(name, arr):
-        at, n = lay.offsets[name]
-        buf[at : at + n] = np.asarray(arr, dtype=np.int32).reshape(-1)
-
-    put("tokens", tokens), put("token_seq", token_seq), put("token_pos", token_pos)
-    put("seq_start", seq_start), put("seq_past", lengths), put("seq_slot", [s for s, _ in entries])
-    put("want_rows", want_rows)
-    for g, tab in enumerate(tables):
-        put(f"block_table{g}", tab)
-    facts = dict(max_new=max(counts), max_len=max(final), is_decode=all(c == 1 for c in counts))
-    return lay, buf, facts
+        for i in range(n):
+            row_off.append(len(rows))
+            row_len.append(len(page_rows[g][i]))
+            rows.extend(page_rows[g][i])
+    rows = np.asarray(rows if rows else [0], dtype=np.int32)
+    row_off = np.asarray(row_off, dtype=np.int64)
+    row_len = np.asarray(row_len, dtype=np.int32)
+    meta = np.zeros(8 + N_FIXED + 2 * n_groups, dtype=np.int64)
+    cap = 4 * int(counts.sum()) + 8 * n + len(want_flat) + n * n_groups * (int(lens.max() + counts.max()) // PAGE + 8) + 64
+    buf = np.zeros(cap, dtype=np.int32)
+    ptr = lambda a: a.ctypes.data
+    code = lib.llmx_pack_step(n, ptr(slots), ptr(counts), ptr(tokens), ptr(want_counts), ptr(want_flat), ptr(lens),
+                              n_groups, ptr(rows), ptr(row_off), ptr(row_len), ptr(buf), cap, ptr(meta))
+    if code:
+        raise_host_error(code)
+    lay, facts = layout_from_meta(meta)
+    return lay, buf[: lay.total], facts
 
 
 class StepBuffers:
@@ -138,15 +167,29 @@ class StepBuffers:
         self.dev = guarded((capacity,), torch.int32, self.device, "step buffer")
 
     def upload(self, lay: StepLayout, buf: np.ndarray, facts: dict) -> StepContext:
+        """A packed step (``build_host_arrays``) through the next pinned buffer to the device."""
         if lay.total > self.capacity:
-            torch.cuda.current_stream().synchronize()
-            self._alloc(max(lay.total, 2 * self.capacity))
+            self.grow(lay.total)
+        host = self.next_host()
+        host[: lay.total].copy_(torch.from_numpy(buf))
+        return self.send(lay, facts)
+
+    def grow(self, total: int) -> None:
+        torch.cuda.current_stream().synchronize()
+        self._alloc(max(total, 2 * self.capacity))
+
+    def next_host(self) -> torch.Tensor:
+        """The pinned buffer the next step is packed into (free again: the copy that last read it is done)."""
         i = self.turn
-        self.turn = (i + 1) % self.RING
         if self.events[i] is not None:
             self.events[i].synchronize()
+        return self.hosts[i]
+
+    def send(self, lay: StepLayout, facts: dict) -> StepContext:
+        """Copies the buffer ``next_host`` gave out to the device and hands out the step's views."""
+        i = self.turn
+        self.turn = (i + 1) % self.RING
         host = self.hosts[i]
-        host[: lay.total].copy_(torch.from_numpy(buf))
         self.dev[: lay.total].copy_(host[: lay.total], non_blocking=True)
         ev = torch.cuda.Event()
         ev.record()

@@ -16,6 +16,7 @@ from dataclasses import dataclass
 from pathlib import Path
 from typing import Optional
 
+import numpy as np
 import torch
 
 from .. import kernels
@@ -24,7 +25,8 @@ from ..config import read_config
 from ..errors import CacheExhausted, CacheMisuse, ContextOverflow
 from ..parts import Runtime
 from ..weights import load_checkpoint, random_tensors_on_device
-from .batch import StepBuffers, build_host_arrays
+from ..cache.allocator import _TOO_SMALL, host_library, raise_host_error
+from .batch import N_FIXED, StepBuffers, flatten_entries, layout_from_meta
 from .model import DecoderModel
 
 
@@ -154,52 +156,36 @@ class Engine:
                 logits = self.model.forward(ctx, self.cache)
             finally:
                 kernels.set_overlap(True)
-        for slot, toks in entries:
-            self.cache.alloc.commit(slot, len(toks))
+        self.cache.alloc.commit_many([slot for slot, _ in entries], [len(toks) for _, toks in entries])
         self.n_steps += 1
         return logits, replayed
 
     def _prepare(self, entries, want):
+        """The step's plan, made by the C++ runtime (csrc/host_runtime.cpp, llmx_plan_step): every check that
+        can refuse the step (slot validity, empty sequences, token ids, wanted places, the step limit), then
+        the reservation of pages for every sequence (taken back if one does not fit), then the step buffer,
+        packed straight into pinned memory."""
         if not entries:
             raise ValueError("a step needs at least one sequence")
-        vocab = self.spec.vocab_size
-        seen = set()
-        total = 0
-        for slot, toks in entries:
-            if slot in seen:
-                raise CacheMisuse(f"slot {slot} appears twice in one step")
-            seen.add(slot)
-            if len(toks) == 0:
-                raise ValueError(f"slot {slot} brings no token")
-            lo, hi = min(toks), max(toks)
-            if lo < 0 or hi >= vocab:
-                raise ValueError(f"token id {lo if lo < 0 else hi} is outside the vocabulary of {vocab}")
-            total += len(toks)
-        if total > self.options.max_step_tokens:
-            raise ContextOverflow(total, self.options.max_step_tokens, "step limit (max_step_tokens)")
-        if want is None:
-            want = [[len(t) - 1] for _, t in entries]
-        for (slot, toks), ws in zip(entries, want):
-            for w in ws:
-                if not (0 <= w < len(toks)):
-                    raise ValueError(f"slot {slot}: wanted place {w} is outside its {len(toks)} tokens")
+        lib = host_library()
         alloc = self.cache.alloc
-        lengths = [alloc.length(slot) for slot, _ in entries]
-        # Reserve for every sequence before anything runs.  When one of them does not fit, the ones before it
-        # give their new pages back, so that a refused step leaves the cache as it found it.
-        reserved = []
-        try:
-            for slot, toks in entries:
-                alloc.reserve(slot, len(toks))
-                reserved.append(slot)
-        except (CacheExhausted, ContextOverflow):
-            for slot in reserved:
-                alloc.unreserve(slot)
-            raise
         n_groups = max(1, self.cache.n_groups())
-        page_rows = [[alloc.page_row(slot, g) for slot, _ in entries] for g in range(n_groups)]
-        lay, buf, facts = build_host_arrays(entries, want, lengths, page_rows, n_groups)
-        return lay, self.buffers.upload(lay, buf, facts)
+        slots, counts, tokens, want_counts, want_flat = flatten_entries(entries, want)
+        meta = np.zeros(8 + N_FIXED + 2 * n_groups, dtype=np.int64)
+        ptr = lambda a: a.ctypes.data
+        for attempt in range(2):
+            host = self.buffers.next_host()
+            code = lib.llmx_plan_step(alloc.handle, len(entries), ptr(slots), ptr(counts), ptr(tokens), ptr(want_counts),
+                                      ptr(want_flat), self.spec.vocab_size, self.options.max_step_tokens, n_groups,
+                                      host.data_ptr(), self.buffers.capacity, ptr(meta))
+            if code == _TOO_SMALL and attempt == 0:
+                self.buffers.grow(int(meta[3]))          # (a captured decode graph reads the buffer at a fixed
+                continue                                 # address: its key holds the address, so it is captured anew)
+            if code:
+                raise_host_error(code)
+            break
+        lay, facts = layout_from_meta(meta)
+        return lay, self.buffers.send(lay, facts)
 
     def _graphed_forward(self, lay, ctx, slots):
         """Decode steps are launch-bound, so the whole forward of a decode
