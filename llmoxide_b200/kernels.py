@@ -359,13 +359,21 @@ def decode_chunks(n_seqs: int, n_kv_heads: int, group: int, n_pages: int, sms: i
     visible keys.  A CTA (two warps) takes one share of one (sequence, kv head,
     8 query heads); two CTAs fit an SM, and the whole grid should be resident
     at once, so the shares are as many as that allows on ``sms`` multiprocessors,
-    up to 8 (the CTAs of a sequence and kv head then merge as one thread-block
-    cluster), and never more than would leave a warp without a 32-key tile of a
-    full block table.  It depends on the batch's shape only (not on its
-    lengths), so a captured graph stays valid while the shape does; each
-    sequence's own length is divided on the device."""
+    and never more than would leave a warp without a 32-key tile of a full block
+    table.  Up to 8 shares the CTAs of a sequence and kv head merge as one
+    thread-block cluster.  Beyond 8 (up to 32) the partials go through a
+    workspace, which costs a little more per share; that is taken only where a
+    small batch with a long context would otherwise leave most of the GPU idle:
+    when 8 shares fill less than half of it and every share still has at least
+    8 pages of keys.  It depends on the batch's shape only (not on its lengths),
+    so a captured graph stays valid while the shape does; each sequence's own
+    length is divided on the device."""
     base = n_seqs * n_kv_heads * ((group + 7) // 8)
-    return max(1, min(2 * sms // base, n_pages, 8))
+    room = 2 * sms // base
+    n = max(1, min(room, n_pages, 8))
+    if n == 8 and base * 8 <= sms:
+        n = max(8, min(3 * sms // (2 * base), n_pages // 8, 32))     # about one and a half CTAs per SM measured best
+    return n
 
 
 _decode_counters: dict = {}

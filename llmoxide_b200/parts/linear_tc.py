@@ -47,6 +47,19 @@ def choose_splits(n_rows: int, k: int, n_tokens: int, n_sm: int = 148, max_split
     return best
 
 
+def choose_prompt_splits(n_rows: int, k: int, n_tokens: int, n_sm: int = 148, max_splits: int = 8) -> int:
+    """The same question for a prompt-sized step (more than 64 tokens).  Whole tiles of 256 rows x 256 tokens
+    on CTA pairs are best when there are enough of them to occupy most pairs.  A short prompt (or a chunk of
+    one) against a narrow matrix leaves most of the GPU idle (512 tokens x 4096 rows: 32 tiles for 74 pairs);
+    then single CTAs take tiles of 128 rows and the reduction is split until about one unit per SM streams, each
+    split at least 8 blocks of K long.  The float32 partials are summed by the kernel that consumes them."""
+    pair_units = -(-n_rows // 256) * -(-n_tokens // 256)
+    if pair_units * 5 >= (n_sm // 2) * 4:
+        return 1
+    units = -(-n_rows // TILE_ROWS) * -(-n_tokens // 256)
+    return max(1, min(max_splits, n_sm // units, ((k + 63) // 64) // 8))
+
+
 class TensorCoreLinear:
     def __init__(self, weight: torch.Tensor, n_sm: int = 148):
         self.weight, self.n_sm = weight, n_sm
@@ -60,7 +73,10 @@ class TensorCoreLinear:
             out = torch.empty((T, self.N), dtype=out_dtype, device=x.device)
             kernels.gemm_fma(x, self.weight, out)
             return out
-        s = choose_splits(self.N, self.K, T, self.n_sm) if splits_ok else 1
+        s = 1
+        if splits_ok:
+            s = (choose_splits(self.N, self.K, T, self.n_sm) if T <= 64 else
+                 choose_prompt_splits(self.N, self.K, T, self.n_sm))
         if s > 1:
             out = scratch((s, T, self.N), torch.float32, x.device, "split partials of a matrix product")
             kernels.gemm_tc(x, self.weight, out, n_split=s, scale=scale)

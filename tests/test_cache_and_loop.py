@@ -370,7 +370,8 @@ def test_a_refused_step_leaves_the_cache_as_it_was():
 
 def test_decode_attention_share_count_depends_on_the_shape_only():
     """Every sequence's keys are cut into as many shares as keep the whole grid resident at once (two CTAs per
-    SM), at most 8 (one thread-block cluster) and never more than a full block table has 32-key tiles for."""
+    SM), never more than a full block table has 32-key tiles for; at most 8 (one thread-block cluster), or up to
+    32 through the workspace where a small batch with a long context would leave most of the GPU idle."""
     from llmoxide_b200.kernels import decode_chunks
 
     for n_sm in (148, 132, 20):
@@ -379,6 +380,9 @@ def test_decode_attention_share_count_depends_on_the_shape_only():
                 for n_pages in (1, 3, 64, 640):
                     n = decode_chunks(n_seqs, n_kv, group, n_pages, n_sm)
                     base = n_seqs * n_kv * ((group + 7) // 8)
-                    assert 1 <= n <= min(8, n_pages)
+                    assert 1 <= n <= min(32, n_pages)
                     assert n == 1 or base * n <= 2 * n_sm
+                    if n > 8:       # through the workspace only for a small batch with a long context
+                        assert base * 8 <= n_sm and n_pages >= 8 * n
     assert decode_chunks(8, 8, 4, 64) == 4 and decode_chunks(64, 8, 4, 64) == 1 and decode_chunks(1, 8, 4, 64) == 8
+    assert decode_chunks(1, 8, 4, 516) == 27 and decode_chunks(1, 8, 4, 132) == 16 and decode_chunks(2, 8, 4, 516) == 13
