@@ -25,11 +25,15 @@ from .allocator import PAGE, CacheAllocator
 @dataclass(frozen=True)
 class KVNeed:
     """Keys and values for every position (window None) or for the last
-    ``window`` positions."""
+    ``window`` positions.  Values may be narrower or wider than keys
+    (``v_head_dim``, default ``head_dim``), and an entry may keep its keys and
+    values in a dtype of its own (default: the runtime's cache dtype)."""
 
     n_kv_heads: int
     head_dim: int
     window: Optional[int] = None
+    v_head_dim: Optional[int] = None
+    dtype: Optional[torch.dtype] = None
 
 
 @dataclass(frozen=True)
@@ -46,7 +50,7 @@ class CacheEntryView:
 
     group: Optional[int]            # index of the block table to use; None without keys/values
     k: Optional[torch.Tensor]       # [n_pages, G, PAGE, D]
-    v: Optional[torch.Tensor]
+    v: Optional[torch.Tensor]       # [n_pages, G, PAGE, D of the values]
     state: Optional[torch.Tensor]   # [n_slots, *shape]
     need: Optional[KVNeed]
 
@@ -75,11 +79,12 @@ class Cache:
             members[kv].append(len(self._entry_group) - 1)
         self.k_store, self.v_store = [], []
         for kv in self.groups:
-            shape = (len(members[kv]), n_pages, kv.n_kv_heads, PAGE, kv.head_dim)
+            k_shape = (len(members[kv]), n_pages, kv.n_kv_heads, PAGE, kv.head_dim)
+            v_shape = k_shape[:-1] + (kv.v_head_dim or kv.head_dim,)
             # (every long-lived buffer carries guard words behind it: guard.py)
             g = len(self.k_store)
-            self.k_store.append(guarded(shape, dtype, device, f"cache group {g} keys", zero=True))
-            self.v_store.append(guarded(shape, dtype, device, f"cache group {g} values", zero=True))
+            self.k_store.append(guarded(k_shape, kv.dtype or dtype, device, f"cache group {g} keys", zero=True))
+            self.v_store.append(guarded(v_shape, kv.dtype or dtype, device, f"cache group {g} values", zero=True))
         self.state_store = [
             None if st is None else guarded((n_slots, *st.shape), st.dtype, device, f"cache entry {e} state", zero=True)
             for e, (_, st) in enumerate(needs)

@@ -215,7 +215,7 @@ def test_layer_named_twice_and_shared_cache(tmp_path):
 # ---- parts of the test's own ------------------------------------------------------------
 
 def _register_toys():
-    from llmoxide_b200.cache import StateNeed
+    from llmoxide_b200.cache import KVNeed, StateNeed
     from llmoxide_b200.parts import (register_embedding, register_feed_forward, register_mixer,
                                      register_position)
 
@@ -258,6 +258,29 @@ def _register_toys():
                 last = start[1:] - 1                                 # every sequence's last token
                 view.state.index_copy_(0, ctx.seq_slot.long(), torch.cat([sums[last], counts[last, None]], dim=1))
             return (sums / counts[:, None]) @ self.w.t()
+
+    @register_mixer("toy_previous_value")
+    class PreviousValue:
+        """y_t = W v_{t-1} with v_t = the first 8 dims of x_t (zero at a sequence's first position): a mixer that
+        keeps values narrower than its keys, in float64 whatever the model's dtype, in the paged cache, and
+        finds them through the step's block table.  All on the device."""
+
+        def __init__(self, spec, position, weights, rt):
+            self.w = weights.pop(spec.tensors["w"].name).float()          # [d, 8]
+
+        def cache_need(self):
+            return KVNeed(n_kv_heads=1, head_dim=16, v_head_dim=8, dtype=torch.float64), None
+
+        def forward(self, x, ctx, view, writes_cache=True):
+            assert view.v.shape[-1] == 8 and view.k.shape[-1] == 16 and view.v.dtype == torch.float64
+            table = ctx.block_tables[view.group].long()
+            seq, pos = ctx.token_seq.long(), ctx.token_pos.long()
+            page = table[seq, pos // 64]
+            if writes_cache:
+                view.v[page, 0, pos % 64] = x[:, :8].double()
+            prev = (pos - 1).clamp(min=0)
+            v_prev = view.v[table[seq, prev // 64], 0, prev % 64].float() * (pos > 0).float()[:, None]
+            return v_prev @ self.w.t()
 
     @register_feed_forward("toy_routed")
     class Routed:
@@ -329,9 +352,16 @@ def test_toy_parts_register_build_and_step(tmp_path):
                           dict(mixer=norm("l1.n1"), feed_forward=norm("l1.n2")),
                           PartSpec("toy_half_speed", dict(n_rot=D, base=100.0))),
             )
+            blocks = blocks + (
+                BlockSpec("pre_norm", PartSpec("toy_previous_value", {}, dict(w=TensorSpec("l2.w", (d, 8)))),
+                          PartSpec("gated_mlp", dict(hidden_size=d, intermediate_size=64, activation="silu"),
+                                   dict(gate=TensorSpec("l2.g", (64, d)), up=TensorSpec("l2.u", (64, d)),
+                                        down=TensorSpec("l2.d", (d, 64)))),
+                          dict(mixer=norm("l2.n1"), feed_forward=norm("l2.n2"))),
+            )
             return ModelSpec("ToyLM", d, V,
                              PartSpec("toy_scaled_table", dict(scale=3.0), dict(table=TensorSpec("emb", (V, d)))),
-                             blocks, default_schedule(2), norm("final"),
+                             blocks, default_schedule(3), norm("final"),
                              PartSpec("linear", dict(tied=True, softcap=5.0), {}),
                              max_positions=512, storage_dtype="float32")
 
@@ -339,6 +369,8 @@ def test_toy_parts_register_build_and_step(tmp_path):
     folder = write_model_folder(tmp_path / "toy", ToyConfig(dict(architectures=["ToyLM"])), 9)
     eng = Engine.load(folder, LoadOptions(dtype="float32", max_tokens=512, max_batch=2))
     assert eng.cache.state_store[0].shape == (2, d + 1) and eng.cache.state_store[1] is None
+    assert eng.cache.n_groups() == 2          # the attention layer's keys and values, and the toy's narrower values
+    assert eng.cache.v_store[1].shape[-1] == 8 and eng.cache.k_store[1].shape[-1] == 16
     assert eng.model.graph_safe and eng.options.cuda_graphs      # decode steps of this model replay CUDA graphs
 
     rng = np.random.default_rng(0)
