@@ -280,10 +280,12 @@ def main() -> int:
     print(f"[bench] prefill {T} tokens: {prefill['ms']:.2f} ms", file=sys.stderr)
 
     # ---- decode: B sequences at depth, K steps ----------------------------------
-    def decode_rate(batch, steps, warmup, sampler=None):
+    def decode_rate(batch, steps, warmup, sampler=None, depth=None):
+        depth = depth or args.depth
         slots = [eng.acquire() for _ in range(batch)]
         for s in slots:
-            eng.step([(s, rng.integers(0, V, args.depth).tolist())], [[]])
+            for lo in range(0, depth, 8192):          # deep contexts are fed in chunks
+                eng.step([(s, rng.integers(0, V, min(8192, depth - lo)).tolist())], [[]])
         toks = rng.integers(0, V, (warmup + steps, batch)).tolist()
         for i in range(warmup):
             eng.step([(s, [t]) for s, t in zip(slots, toks[i])])
@@ -304,7 +306,7 @@ def main() -> int:
         launches = kernels.launch_count - launches
         for s in slots:
             eng.release(s)
-        mean_depth = args.depth + warmup + steps / 2
+        mean_depth = depth + warmup + steps / 2
         step_bytes = weight_bytes + batch * mean_depth * kv_per_token
         gbs = step_bytes / (ms / steps * 1e-3) / 1e9
         return dict(value=batch * steps / ms * 1e3, ms_per_step=ms / steps, gb_per_s=gbs, frac=gbs / pk["hbm_gbs"],
@@ -347,6 +349,11 @@ def main() -> int:
                                                e2e=rate, e2e_frac_of_device=rate / pt["value"], host_us_per_step=h_us)
         details[f"decode_b{B}"] = dict(ms_per_step=ms_per_step, gb_per_s=achieved, frac=main_pt["frac"], e2e=e2e_value,
                                        e2e_frac_of_device=e2e_value / value, host_us_per_step=host_us)
+        for batch, depth in ((8, 8192), (1, 32768)):       # deeper contexts: the cache outweighs the weights
+            pt = decode_rate(batch, 16, 3, depth=depth)
+            points[f"decode_b{batch}_depth{depth}"] = pt["value"]
+            details[f"decode_b{batch}_depth{depth}"] = dict(ms_per_step=pt["ms_per_step"], gb_per_s=pt["gb_per_s"],
+                                                            frac=pt["frac"])
         lens16 = rng.integers(64, 2049, 16).tolist()       # an unequal batch: 16 prompts of 64..2048 tokens
         for name, lengths in (("prefill_512", [512]), ("prefill_8192", [8192]), ("prefill_16_unequal", lens16)):
             pp = prefill_point(lengths)
