@@ -23,8 +23,8 @@ PAIR_MIN_TOKENS = 128         # above this, CTA pairs (tcgen05 cta_group::2) sha
 
 def choose_splits(n_rows: int, k: int, n_tokens: int, n_sm: int = 148, max_splits: int = 16) -> int:
     """How many ways to split the reduction over K at ``n_tokens`` tokens, from
-    a small time model of the streaming kernel (microseconds): CTAs run in
-    rounds of n_sm * CTAS_PER_SM; a CTA streams its share of the weights at
+    a small time model of the streaming kernel (microseconds): n_sm * CTAS_PER_SM
+    CTAs run at once; a CTA streams its share of the weights at
     the HBM rate divided by the CTAs running, but never faster than one CTA
     can pull; every round costs a fixed start and drain; float32 partials are
     written once and read once by the kernel that consumes them."""
@@ -37,9 +37,11 @@ def choose_splits(n_rows: int, k: int, n_tokens: int, n_sm: int = 148, max_split
     best, best_t = 1, None
     for s in range(1, min(max_splits, max(1, k_blocks // MIN_KBLOCKS_PER_SPLIT)) + 1):
         ctas = tiles * s
-        rounds = -(-ctas // slots)
         rate = min(hbm / min(ctas, slots), one_cta)
-        t = rounds * (TILE_ROWS * (k / s) * 2 / rate + fixed)
+        unit = TILE_ROWS * (k / s) * 2 / rate + fixed
+        # persistent CTAs walk their units without waiting for one another: more units than slots cost their
+        # share of rounds, plus on average half a unit at the end where the slots run dry unevenly
+        t = unit if ctas <= slots else (ctas / slots + 0.5) * unit
         if s > 1:
             t += 2.0 * s * n_tokens * n_rows * 4 / 5.0e6
         if best_t is None or t < best_t - 1e-9:
