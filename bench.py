@@ -381,7 +381,7 @@ def main() -> int:
 
 def cpu_baseline() -> int:
     """Tokens per second of the plain implementation (tests/plain_qwen3.py: float32, whole sequences, no cache)
-    on this machine's CPU, on the tiny configurations A and B: a prompt step over BASELINE.json's prompts and
+    on this machine's CPU, on the tiny configurations A and B: a prompt step over prompts of 5, 9, 13 (A) and 1, 7, 16, 31 (B) tokens and
     greedy decoding that recomputes the whole sequence for every token.  It is the oracle of the tests, timed
     for orientation; the reference's own CPU path cannot be built here."""
     import tempfile
