@@ -233,3 +233,29 @@ def test_sampler_properties():
     rng = plain.Rng(0)
     xs = [rng.next_f32() for _ in range(4000)]
     assert all(0 <= x < 1 for x in xs) and abs(np.mean(xs) - 0.5) < 0.02
+
+
+def test_a_checkpoint_split_over_files_with_an_index(tmp_path):
+    """model.safetensors.index.json names the file of every tensor; the loaded tensors are the same, and a file the
+    index names but the folder lacks is an error of the checkpoint's format."""
+    import json
+
+    from llmoxide_b200.errors import CheckpointFormatError
+
+    folder = make_folder(tmp_path, "B", "float32")
+    spec = read_config(folder).to_spec()
+    whole = load_checkpoint(folder, spec, "float32", "cpu")
+    entries = open_checkpoint(folder)
+    names = sorted(entries)
+    shards = {"model-00001-of-00002.safetensors": names[: len(names) // 2],
+              "model-00002-of-00002.safetensors": names[len(names) // 2:]}
+    for fname, part in shards.items():
+        save_file({n: entries[n].file.tensor(n).clone() for n in part}, folder / fname)
+    (folder / "model.safetensors.index.json").write_text(json.dumps(
+        {"metadata": {}, "weight_map": {n: fname for fname, part in shards.items() for n in part}}))
+    (folder / "model.safetensors").unlink()
+    split = load_checkpoint(folder, spec, "float32", "cpu")
+    assert set(split) == set(whole) and all(torch.equal(split[k], whole[k]) for k in whole)
+    (folder / "model-00002-of-00002.safetensors").unlink()
+    with pytest.raises(CheckpointFormatError, match="does not exist"):
+        load_checkpoint(folder, spec, "float32", "cpu")
