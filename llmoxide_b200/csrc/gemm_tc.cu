@@ -197,7 +197,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
   if (warp == 0) {
     // ---------------- producer ----------------
     if (lane == 0) {
-      int it = 0;                 // k-blocks issued so far by this CTA (ring position)
+      RingPos pos{0, 0};          // where the next k-block goes
       bool waited = false, ok = true;
       for (int u = blockIdx.x; u < n_units && ok; u += gridDim.x) {
         int n0, t0, kb_begin, n_kb, split;
@@ -220,12 +220,12 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
             tma_load_2d(base + (uint32_t)j * STAGE_BYTES + N_ACC * A_BYTES, &map_x, (kb_begin + j) * TC_BK, t0,
                         full0 + 8u * j);
           i = pre;
-          it = pre;
+          if (pre == n_stages) pos = RingPos{0, 1};
+          else pos = RingPos{pre, 0};
         }
-        for (; i < n_kb; ++i, ++it) {
-          const int s = it % n_stages;
-          const uint32_t parity = ((it / n_stages) & 1) ^ 1;
-          if (!mbar_wait(empty0 + 8u * s, parity)) { tc_report(1); ok = false; break; }
+        for (; i < n_kb; ++i, pos.next(n_stages)) {
+          const int s = pos.s;
+          if (!mbar_wait(empty0 + 8u * s, pos.phase ^ 1u)) { tc_report(1); ok = false; break; }
           const uint32_t stage = base + (uint32_t)s * STAGE_BYTES;
           const uint32_t bar = full0 + 8u * s;
           mbar_expect_tx(bar, STAGE_BYTES);
@@ -240,7 +240,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
     // ---------------- MMA issuer ----------------
     if (lane == 0) {
       constexpr uint32_t idesc = umma_idesc(BN);
-      int it = 0, j = 0;          // ring position; units done by this CTA
+      int j = 0;                  // units done by this CTA
+      RingPos pos{0, 0};
+      const uint32_t desc0 = umma_desc_lo(base);       // stage 0's W tile; every other tile is an offset from it
       bool ok = true;
       for (int u = blockIdx.x; u < n_units && ok; u += gridDim.x, ++j) {
         int n0, t0, kb_begin, n_kb, split;
@@ -250,18 +252,18 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
         // the epilogue must have drained this accumulator set (ACC_BUFS units ago)
         if (!mbar_wait(acc_empty0 + 8u * buf, (use & 1) ^ 1)) { tc_report(4); ok = false; break; }
         tc_fence_after();
-        for (int i = 0; i < n_kb; ++i, ++it) {
-          const int s = it % n_stages;
-          const uint32_t parity = (it / n_stages) & 1;
-          if (!mbar_wait(full0 + 8u * s, parity)) { tc_report(2); ok = false; break; }
+        for (int i = 0; i < n_kb; ++i, pos.next(n_stages)) {
+          const int s = pos.s;
+          if (!mbar_wait(full0 + 8u * s, pos.phase)) { tc_report(2); ok = false; break; }
           tc_fence_after();
-          const uint32_t stage = base + (uint32_t)s * STAGE_BYTES;
+          const uint32_t da = desc0 + (uint32_t)s * (STAGE_BYTES >> 4);
 #pragma unroll
           for (int kk = 0; kk < TC_BK / TC_UMMA_K; ++kk) {
-            const uint64_t db = umma_desc(stage + N_ACC * A_BYTES + kk * (TC_UMMA_K * 2));
+            const uint32_t db = da + ((N_ACC * A_BYTES) >> 4) + kk * ((TC_UMMA_K * 2) >> 4);
             const uint32_t acc = (i > 0 || kk > 0) ? 1u : 0u;
-            umma_bf16(acc_addr, umma_desc(stage + kk * (TC_UMMA_K * 2)), db, idesc, acc);
-            if (MODE == 1) umma_bf16(acc_addr + BN, umma_desc(stage + A_BYTES + kk * (TC_UMMA_K * 2)), db, idesc, acc);
+            umma_bf16_lo(acc_addr, da + kk * ((TC_UMMA_K * 2) >> 4), db, idesc, acc);
+            if (MODE == 1)
+              umma_bf16_lo(acc_addr + BN, da + (A_BYTES >> 4) + kk * ((TC_UMMA_K * 2) >> 4), db, idesc, acc);
           }
           umma_commit(empty0 + 8u * s);   // the stage is free once these MMAs have read it
         }
@@ -394,6 +396,15 @@ __device__ __forceinline__ void umma_bf16_pair(uint32_t tmem_d, uint64_t a, uint
       ::"r"(tmem_d), "l"(a), "l"(b), "r"(idesc), "r"(accumulate)
       : "memory");
 }
+__device__ __forceinline__ void umma_bf16_pair_lo(uint32_t tmem_d, uint32_t a_lo, uint32_t b_lo, uint32_t idesc,
+                                                  uint32_t accumulate) {
+  asm volatile(
+      "{\n.reg .pred p;\n.reg .b64 da, db;\n"
+      "mov.b64 da, {%1, %5};\nmov.b64 db, {%2, %5};\nsetp.ne.b32 p, %4, 0;\n"
+      "tcgen05.mma.cta_group::2.kind::f16 [%0], da, db, %3, p;\n}"
+      ::"r"(tmem_d), "r"(a_lo), "r"(b_lo), "r"(idesc), "r"(accumulate), "r"(UMMA_DESC_HI)
+      : "memory");
+}
 __device__ __forceinline__ void umma_commit_pair(uint32_t bar) {   // arrives on `bar` in both CTAs
   asm volatile(
       "tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
@@ -475,7 +486,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
   if (warp == 0) {
     // ---------------- producer (one per CTA) ----------------
     if (lane == 0) {
-      int it = 0;
+      RingPos pos{0, 0};
       bool waited = false, ok = true;
       for (int u = pair; u < n_units && ok; u += n_pairs) {
         int n0, t0;
@@ -495,12 +506,12 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
             tma_load_2d_pair(base + (uint32_t)j * STAGE_BYTES + N_ACC * A_BYTES, &map_x, j * TC_BK, tx,
                              leader_full0 + 8u * j);
           i = pre;
-          it = pre;
+          if (pre == n_stages) pos = RingPos{0, 1};
+          else pos = RingPos{pre, 0};
         }
-        for (; i < total_kb; ++i, ++it) {
-          const int s = it % n_stages;
-          const uint32_t parity = ((it / n_stages) & 1) ^ 1;
-          if (!mbar_wait_cluster(empty0 + 8u * s, parity)) { tc_report(11); ok = false; break; }
+        for (; i < total_kb; ++i, pos.next(n_stages)) {
+          const int s = pos.s;
+          if (!mbar_wait_cluster(empty0 + 8u * s, pos.phase ^ 1u)) { tc_report(11); ok = false; break; }
           const uint32_t stage = base + (uint32_t)s * STAGE_BYTES, bar = leader_full0 + 8u * s;
           mbar_remote_expect_tx(bar, STAGE_BYTES);
           tma_load_2d_pair(stage, &map_w, i * TC_BK, n0, bar);
@@ -513,25 +524,27 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
     // ---------------- MMA issuer (leader CTA only) ----------------
     if (leader && lane == 0) {
       constexpr uint32_t idesc = umma_idesc_pair(BN);
-      int it = 0, j = 0;
+      int j = 0;
+      RingPos pos{0, 0};
+      const uint32_t desc0 = umma_desc_lo(base);       // stage 0's W tile; every other tile is an offset from it
       bool ok = true;
       for (int u = pair; u < n_units && ok; u += n_pairs, ++j) {
         const int buf = j % ACC_BUFS, use = j / ACC_BUFS;
         const uint32_t acc_addr = tmem_base + (uint32_t)buf * ACC_COLS;
         if (!mbar_wait_cluster(acc_empty0 + 8u * buf, (use & 1) ^ 1)) { tc_report(14); ok = false; break; }
         tc_fence_after();
-        for (int i = 0; i < total_kb; ++i, ++it) {
-          const int s = it % n_stages;
-          if (!mbar_wait_cluster(full0 + 8u * s, (it / n_stages) & 1)) { tc_report(12); ok = false; break; }
+        for (int i = 0; i < total_kb; ++i, pos.next(n_stages)) {
+          const int s = pos.s;
+          if (!mbar_wait_cluster(full0 + 8u * s, pos.phase)) { tc_report(12); ok = false; break; }
           tc_fence_after();
-          const uint32_t stage = base + (uint32_t)s * STAGE_BYTES;
+          const uint32_t da = desc0 + (uint32_t)s * (STAGE_BYTES >> 4);
 #pragma unroll
           for (int kk = 0; kk < TC_BK / TC_UMMA_K; ++kk) {
-            const uint64_t db = umma_desc(stage + N_ACC * A_BYTES + kk * (TC_UMMA_K * 2));
+            const uint32_t db = da + ((N_ACC * A_BYTES) >> 4) + kk * ((TC_UMMA_K * 2) >> 4);
             const uint32_t acc = (i > 0 || kk > 0) ? 1u : 0u;
-            umma_bf16_pair(acc_addr, umma_desc(stage + kk * (TC_UMMA_K * 2)), db, idesc, acc);
+            umma_bf16_pair_lo(acc_addr, da + kk * ((TC_UMMA_K * 2) >> 4), db, idesc, acc);
             if (MODE == 1)
-              umma_bf16_pair(acc_addr + BN, umma_desc(stage + A_BYTES + kk * (TC_UMMA_K * 2)), db, idesc, acc);
+              umma_bf16_pair_lo(acc_addr + BN, da + (A_BYTES >> 4) + kk * ((TC_UMMA_K * 2) >> 4), db, idesc, acc);
           }
           umma_commit_pair(empty0 + 8u * s);
         }

@@ -73,6 +73,34 @@ __device__ __forceinline__ uint64_t umma_desc(uint32_t smem_addr) {
   d |= (uint64_t)2 << 61;                               // SWIZZLE_128B
   return d;
 }
+// The same descriptor in halves.  The upper word is one constant for every tile of this layout, and the lower
+// word is (address / 16) plus a constant, so the thread that issues the MMAs steps from tile to tile with one
+// 32-bit add.  That thread's instruction count is what bounds a prompt-sized product: every stage of the
+// ring costs it a wait, four MMAs and a commit, one after the other.
+#define UMMA_DESC_HI 0x40004040u          // stride 1024 bytes | version of sm_100 | SWIZZLE_128B
+__device__ __forceinline__ uint32_t umma_desc_lo(uint32_t smem_addr) {
+  return ((smem_addr & 0x3FFFFu) >> 4) | (1u << 16);
+}
+__device__ __forceinline__ void umma_bf16_lo(uint32_t tmem_d, uint32_t a_lo, uint32_t b_lo, uint32_t idesc,
+                                             uint32_t accumulate) {
+  asm volatile(
+      "{\n.reg .pred p;\n.reg .b64 da, db;\n"
+      "mov.b64 da, {%1, %5};\nmov.b64 db, {%2, %5};\nsetp.ne.b32 p, %4, 0;\n"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %3, p;\n}"
+      ::"r"(tmem_d), "r"(a_lo), "r"(b_lo), "r"(idesc), "r"(accumulate), "r"(UMMA_DESC_HI)
+      : "memory");
+}
+// Position in a ring of n stages: the stage, and the parity of how often the ring has been walked.
+struct RingPos {
+  int s;
+  uint32_t phase;
+  __device__ __forceinline__ void next(int n) {
+    if (++s == n) {
+      s = 0;
+      phase ^= 1u;
+    }
+  }
+};
 __device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t a, uint64_t b, uint32_t idesc, uint32_t accumulate) {
   asm volatile(
       "{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\n"
