@@ -58,21 +58,21 @@ __host__ __device__ constexpr uint32_t umma_idesc(int n) {
 // Epilogue of one accumulator tile: this warp's quarter (32 lanes = 32 rows of
 // W) of BN token columns, 16 columns at a time.
 // MODE 0: out[t, n] = acc.          MODE 1: two accumulators (gate, up): out[t, n] = silu(gate) * up.
-// MODE 2: W's rows come in blocks of 128 = 64 gate rows then the 64 up rows of the same features, so
-//         lanes 0..63 of the tile hold gate and lanes 64..127 hold up.  The two upper warps pass their
-//         values through shared memory (double-buffered, one named barrier per 16 columns) and the two
-//         lower warps write out[t, n0/2 + row] = silu(gate) * up.  All four warps run the same loop
-//         whatever happened before, so the barrier cannot be left waiting.
+// MODE 2: W's rows come in blocks of 32 = 16 gate rows then the 16 up rows of the same features, so a warp's
+//         lanes 0..15 hold gate and lanes 16..31 hold up of the same 16 features: one shuffle per pair of
+//         columns brings the two together (the lower lanes finish the even columns, the upper lanes the odd
+//         ones), and no warp waits for another.  A tile of 128 rows gives 64 features:
+//         out[t, n0/2 + 16 * quad + lane % 16] = silu(gate) * up.
 // ---------------------------------------------------------------------------
-#define TC_XBUF_FLOATS (2 * 64 * 17)
 #define TC_FUSE_BYTES (64 * 4)                    // row scales
 
 template <int BN, int MODE, typename TY>
 __device__ __forceinline__ void epilogue_tile(uint32_t acc_addr, bool have_acc, bool store, TY* __restrict__ out,
                                               int n0, int t0, int T, int n_limit, long long ldy, int quad, int lane,
-                                              float* xbuf, const float* row_scale = nullptr) {
+                                              const float* row_scale = nullptr) {
   const int row = quad * 32 + lane;
-  const int n = MODE == 2 ? (n0 >> 1) + (row & 63) : n0 + row;
+  const int n = MODE == 2 ? (n0 >> 1) + quad * 16 + (lane & 15) : n0 + row;
+  const bool upper = lane >= 16;
 #pragma unroll 1
   for (int c = 0; c < BN; c += 16) {
     if (t0 + c >= T) break;
@@ -93,18 +93,16 @@ __device__ __forceinline__ void epilogue_tile(uint32_t acc_addr, bool have_acc, 
       }
     }
     if (MODE == 2) {
-      float* xb = xbuf + ((c >> 4) & 1) * (64 * 17);
-      if (quad >= 2) {
 #pragma unroll
-        for (int e = 0; e < 16; ++e) xb[(row - 64) * 17 + e] = v[e];
+      for (int e = 0; e < 16; e += 2) {
+        const float got = __shfl_xor_sync(0xffffffffu, upper ? v[e] : v[e + 1], 16);
+        const float gate = upper ? got : v[e];
+        const float up = upper ? v[e + 1] : got;
+        const int t = t0 + c + e + (upper ? 1 : 0);
+        if (store && n < n_limit && t < T)
+          out[(size_t)t * ldy + n] = from_f32<TY>(__fdividef(gate, 1.0f + __expf(-gate)) * up);
       }
-      asm volatile("bar.sync 1, 128;" ::: "memory");
-      if (quad < 2) {
-#pragma unroll
-        for (int e = 0; e < 16; ++e) g[e] = xb[row * 17 + e];
-      }
-    }
-    if (store && n < n_limit && (MODE != 2 || quad < 2)) {
+    } else if (store && n < n_limit) {
 #pragma unroll
       for (int e = 0; e < 16; ++e) {
         const int t = t0 + c + e;
@@ -153,8 +151,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
   const uint32_t full0 = smem_u32(bars), empty0 = full0 + 8u * n_stages;
   const uint32_t acc_full0 = empty0 + 8u * n_stages, acc_empty0 = acc_full0 + 16u;
   uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(bars + 2 * n_stages + 4);
-  float* xbuf = reinterpret_cast<float*>(bars + 2 * n_stages + 6);   // MODE 2 only
-  float* row_scales = xbuf + (MODE == 2 ? TC_XBUF_FLOATS : 0);       // [64] r[t]
+  float* row_scales = reinterpret_cast<float*>(bars + 2 * n_stages + 6);   // [64] r[t]
 
   pdl_launch_dependents();
   if (threadIdx.x == 0) {
@@ -301,7 +298,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
         if (!ok && lane == 0) tc_report(3);
         failed = __shfl_sync(0xffffffffu, ok ? 0 : 1, 0) != 0;
       }
-      if (failed && MODE != 2) break;   // MODE 2 keeps walking (without loads or stores): its warps meet at a barrier
+      if (failed) break;
       tc_fence_after();
       if (n_kb == 0 && !waited) {       // no load ordered this unit after the kernel before: do it here
         pdl_wait();
@@ -309,8 +306,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
       }
       TY* out = Y + (MODE == 0 ? (size_t)split * split_stride : 0);
       const uint32_t acc_addr = tmem_base + (uint32_t)buf * ACC_COLS + ((uint32_t)(quad * 32) << 16);
-      epilogue_tile<BN, MODE, TY>(acc_addr, n_kb > 0 && !failed, !failed, out, n0, t0, T, n_limit, ldy, quad, lane, xbuf,
-                                  row_scale);
+      epilogue_tile<BN, MODE, TY>(acc_addr, n_kb > 0, true, out, n0, t0, T, n_limit, ldy, quad, lane, row_scale);
       // hand the accumulator set back to the MMA warp
       tc_fence_before();
       __syncwarp();
@@ -443,7 +439,6 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
   const uint32_t full0 = smem_u32(bars), empty0 = full0 + 8u * n_stages;
   const uint32_t acc_full0 = empty0 + 8u * n_stages, acc_empty0 = acc_full0 + 16u;
   uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(bars + 2 * n_stages + 4);
-  float* xbuf = reinterpret_cast<float*>(bars + 2 * n_stages + 6);   // MODE 2 only
   // the leader's copies of the barriers that both CTAs signal
   const uint32_t leader_full0 = map_to_cta(full0, 0), leader_acc_empty0 = map_to_cta(acc_empty0, 0);
 
@@ -567,10 +562,10 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
         if (!ok && lane == 0) tc_report(13);
         failed = __shfl_sync(0xffffffffu, ok ? 0 : 1, 0) != 0;
       }
-      if (failed && MODE != 2) break;
+      if (failed) break;
       tc_fence_after();
       const uint32_t acc_addr = tmem_base + (uint32_t)buf * ACC_COLS + ((uint32_t)(quad * 32) << 16);
-      epilogue_tile<BN, MODE, TY>(acc_addr, !failed, !failed, Y, n0, t0, T, n_limit, ldy, quad, lane, xbuf);
+      epilogue_tile<BN, MODE, TY>(acc_addr, true, true, Y, n0, t0, T, n_limit, ldy, quad, lane);
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_remote_arrive(leader_acc_empty0 + 8u * buf);
@@ -607,11 +602,11 @@ static int launch(const CUtensorMap& mw, const CUtensorMap& mx, void* Y, int T, 
   // Decode tiles (few tokens) stream weights: two CTAs per SM, so that more loads are in flight per SM.
   // Prompt tiles take the whole SM.
   const int ctas_per_sm = BN <= 64 ? 2 : 1;
-  const size_t budget = BN <= 64 ? 100 * 1024 : (MODE == 2 ? 192 * 1024 : 200 * 1024);
+  const size_t budget = BN <= 64 ? 100 * 1024 : 200 * 1024;
   int stages = (int)(budget / STAGE);
   if (stages > 12) stages = 12;
   if (stages < 2) stages = 2;
-  const size_t smem = 1024 + (size_t)stages * STAGE + (2 * stages + 6) * 8 + (MODE == 2 ? TC_XBUF_FLOATS * 4 : 0) +
+  const size_t smem = 1024 + (size_t)stages * STAGE + (2 * stages + 6) * 8 +
                       TC_FUSE_BYTES;
   auto kernel = gemm_tc_kernel<BN, MODE, TY>;
   static bool attr_set = false;
@@ -634,7 +629,7 @@ static int launch(const CUtensorMap& mw, const CUtensorMap& mx, void* Y, int T, 
 // X [T,K] bf16 (row stride ldx), W [N,K] bf16 (row stride ldw).
 // mode 0: Y [T,N] of y_dtype, or with n_split > 1 float32 partials [n_split][T,N] (split_stride elements apart).
 // mode 1: W = [gate rows; up rows] with N = 2F; Y = act [T,F] of y_dtype.
-// mode 2: W = blocks of 128 rows, each 64 gate rows then the 64 up rows of the same features (N = 2F, F % 64 == 0);
+// mode 2: W = blocks of 32 rows, each 16 gate rows then the 16 up rows of the same features (N = 2F, F % 16 == 0);
 //         Y = act [T,F] bf16.
 // The same with row scales applied in the epilogue (see TcScale): in_sumsq [in_parts][in_stride >= T], T <= 64.
 LLMX_API int llmx_gemm_tc_scaled(const void* X, const void* W, void* Y, int y_dtype, int T, int N, int K, long long ldx,
@@ -661,7 +656,7 @@ LLMX_API int llmx_gemm_tc_scaled(const void* X, const void* W, void* Y, int y_dt
   }
   if (K <= 0 || (K % 8) || (ldx % 8) || (ldw % 8) || ((uintptr_t)X & 15) || ((uintptr_t)W & 15)) return LLMX_REFUSED(1);
   if (n_split < 1 || (n_split > 1 && (mode != 0 || y_dtype != LLMX_F32))) return LLMX_REFUSED(1);
-  if (mode < 0 || mode > 2 || (mode == 1 && (N % 2)) || (mode == 2 && (N % 128))) return LLMX_REFUSED(1);
+  if (mode < 0 || mode > 2 || (mode == 1 && (N % 2)) || (mode == 2 && (N % 32))) return LLMX_REFUSED(1);
   const int F = mode != 0 ? N / 2 : 0;
   int bn = 16;
   while (bn < T && bn < (mode == 1 ? 128 : 256)) bn <<= 1;
@@ -699,9 +694,9 @@ static int launch_pair(const CUtensorMap& mw, const CUtensorMap& mx, void* Y, in
                        int F, cudaStream_t stream) {
   constexpr int N_ACC = MODE == 1 ? 2 : 1;
   constexpr size_t STAGE = (size_t)N_ACC * TC_BM * TC_BK * 2 + (size_t)(BN / 2) * TC_BK * 2;
-  int stages = (int)(((MODE == 2 ? 192 : 200) * 1024) / STAGE);
+  int stages = (int)((200 * 1024) / STAGE);
   if (stages > 12) stages = 12;
-  const size_t smem = 1024 + (size_t)stages * STAGE + (2 * stages + 6) * 8 + (MODE == 2 ? TC_XBUF_FLOATS * 4 : 0);
+  const size_t smem = 1024 + (size_t)stages * STAGE + (2 * stages + 6) * 8;
   auto kernel = gemm_tc_pair_kernel<BN, MODE, TY>;
   static bool attr_set = false;
   if (!attr_set) {
@@ -749,7 +744,7 @@ LLMX_API int llmx_gemm_tc_pair(const void* X, const void* W, void* Y, int y_dtyp
                                long long ldx, long long ldw, long long ldy, int mode, cudaStream_t stream) {
   if (T <= 0 || N <= 0) return 0;
   if (K <= 0 || (K % 8) || (ldx % 8) || (ldw % 8) || ((uintptr_t)X & 15) || ((uintptr_t)W & 15)) return LLMX_REFUSED(1);
-  if (T <= 128 || mode < 0 || mode > 2 || (mode == 1 && (N % 2)) || (mode == 2 && (N % 128))) return LLMX_REFUSED(1);
+  if (T <= 128 || mode < 0 || mode > 2 || (mode == 1 && (N % 2)) || (mode == 2 && (N % 32))) return LLMX_REFUSED(1);
   const int F = mode != 0 ? N / 2 : 0;
   const int bn = mode == 1 ? 128 : 256;
   CUtensorMap mw, mx;

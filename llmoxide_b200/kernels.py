@@ -498,8 +498,8 @@ def gemm_tc(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, n_split: int = 
     """bfloat16 x [T,K] times w [N,K]^T on tcgen05.  ``out`` is [T,N] (bfloat16
     or float32), or float32 partials [n_split,T,N] of a split reduction, or,
     with ``gated``, [T,N/2] = silu(gate) * up: ``gated=True`` (or 1) for
-    w = [gate rows; up rows], ``gated=2`` for w in blocks of 64 gate rows each
-    followed by the 64 up rows of the same features (N/2 a multiple of 64).
+    w = [gate rows; up rows], ``gated=2`` for w in blocks of 16 gate rows each
+    followed by the 16 up rows of the same features (N/2 a multiple of 16).
     ``pair`` runs the CTA-pair kernel (prompt-sized T > 128, no split).
     ``scale = (sumsq, parts, eps, d)``, for T <= 64: output row t is multiplied
     by 1/sqrt(sum(sumsq[:parts, t]) / d + eps) before any activation (the

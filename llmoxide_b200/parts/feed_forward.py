@@ -31,13 +31,14 @@ class GatedMLP:
         wg, wu = weights.pop(t["gate"].name), weights.pop(t["up"].name)
         if wg.dtype != wu.dtype:
             wg, wu = wg.float(), wu.float()
-        # One matrix for gate and up.  Where the width allows, rows go in blocks of 64 gate rows each
-        # followed by the 64 up rows of the same features: a 128-row tile of the matrix product then holds
-        # both halves of 64 features, and the activation can be its epilogue.  Otherwise gate rows, then up rows.
-        self.block = 64 if self.F % 64 == 0 else 0
+        # One matrix for gate and up.  Where the width allows, rows go in blocks of 16 gate rows each
+        # followed by the 16 up rows of the same features: a warp of the matrix product's epilogue (32 rows of
+        # a tile) then holds both halves of 16 features, and the activation is one shuffle away.  Otherwise
+        # gate rows, then up rows.
+        self.block = 16 if self.F % 16 == 0 else 0
         if self.block:
             k = wg.shape[1]
-            fused = torch.stack([wg.view(-1, 64, k), wu.view(-1, 64, k)], dim=1).reshape(2 * self.F, k)
+            fused = torch.stack([wg.view(-1, 16, k), wu.view(-1, 16, k)], dim=1).reshape(2 * self.F, k)
         else:
             fused = torch.cat([wg, wu], dim=0)
         del wg, wu

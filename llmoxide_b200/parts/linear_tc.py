@@ -95,11 +95,11 @@ class TensorCoreLinear:
         return x, None
 
     def gated(self, x, out_dtype, block: int = 0):
-        """silu(gate x) * (up x), [T, N/2]; ``block`` = 0 for weight = [gate rows; up rows], 64 for
-        blocks of 64 gate rows each followed by the 64 up rows of the same features."""
+        """silu(gate x) * (up x), [T, N/2]; ``block`` = 0 for weight = [gate rows; up rows], 16 for
+        blocks of 16 gate rows each followed by the 16 up rows of the same features."""
         x, scale = self._unpack(x)
         out = scratch((x.shape[0], self.N // 2), out_dtype, x.device, "output of the gated matrix product")
-        kernels.gemm_tc(x, self.weight, out, gated=2 if block == 64 else 1, pair=x.shape[0] > PAIR_MIN_TOKENS,
+        kernels.gemm_tc(x, self.weight, out, gated=2 if block == 16 else 1, pair=x.shape[0] > PAIR_MIN_TOKENS,
                         scale=scale)
         return out
 

@@ -345,9 +345,9 @@ def test_gemm_tc(T, N, K):
         kernels.gemm_tc(xd, wd, act, gated=True)
         gate, up = want[:, :F].float(), want[:, F:].float()
         assert rel(act, plain.silu(gate) * up) < 8e-3
-    if N % 128 == 0:      # rows in blocks of 64 gate rows + the 64 up rows of the same features
+    if N % 32 == 0:       # rows in blocks of 16 gate rows + the 16 up rows of the same features
         F = N // 2
-        blocks = want.float().view(T, N // 128, 2, 64)
+        blocks = want.float().view(T, N // 32, 2, 16)
         act = torch.full((T, F), float("nan"), dtype=torch.bfloat16, device=DEV)
         kernels.gemm_tc(xd, wd, act, gated=2)
         assert rel(act, (plain.silu(blocks[:, :, 0]) * blocks[:, :, 1]).reshape(T, F)) < 8e-3
@@ -384,9 +384,9 @@ def test_gemm_tc_pair(T, N, K):
         kernels.gemm_tc(xd, wd, act, gated=True, pair=True)
         gate, up = want[:, :F].float(), want[:, F:].float()
         assert rel(act, plain.silu(gate) * up) < 8e-3
-    if N % 128 == 0:
+    if N % 32 == 0:
         F = N // 2
-        blocks = want.float().view(T, N // 128, 2, 64)
+        blocks = want.float().view(T, N // 32, 2, 16)
         act = torch.full((T, F), float("nan"), dtype=torch.bfloat16, device=DEV)
         kernels.gemm_tc(xd, wd, act, gated=2, pair=True)
         assert rel(act, (plain.silu(blocks[:, :, 0]) * blocks[:, :, 1]).reshape(T, F)) < 8e-3
@@ -632,7 +632,7 @@ def test_norm_in_two_halves(T, d, N2):
             act = torch.empty((T, F), dtype=torch.bfloat16, device=DEV)
             kernels.gemm_tc(x, w2d, act, gated=True, scale=(sumsq, parts, eps, d))
             assert rel(act, plain.silu(want_y[:, :F]) * want_y[:, F:]) < 1e-2
-            blocks = want_y.view(T, N2 // 128, 2, 64)
+            blocks = want_y.view(T, N2 // 32, 2, 16)
             kernels.gemm_tc(x, w2d, act, gated=2, scale=(sumsq, parts, eps, d))
             assert rel(act, (plain.silu(blocks[:, :, 0]) * blocks[:, :, 1]).reshape(T, F)) < 1e-2
     assert kernels.gemm_tc_status() == 0
