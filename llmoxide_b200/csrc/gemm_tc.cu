@@ -411,12 +411,16 @@ __host__ __device__ constexpr uint32_t umma_idesc_pair(int n) {   // M = 256 ove
   return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(256 >> 4) << 24);
 }
 
-// Units: (pair of row tiles = 256 rows of W, tile of BN tokens); unit u -> token tile fastest.
+// Units: (pair of row tiles = 256 rows of W, tile of BN tokens).  Token tiles come in groups of `group_tiles`;
+// a group's units run token tile fastest, then row pair, and group follows group.  The pairs that run side by
+// side then share a few W tiles through L2, and a group's activations (chosen by the host to fit well inside
+// L2) are fetched from memory once and serve every row pair, however many tokens the step has; W is streamed
+// once per group.  With one group this is "token tile fastest" over the whole product.
 template <int BN, int MODE, typename TY>
 __global__ void __launch_bounds__(TC_THREADS)
 gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
                     TY* __restrict__ Y, int T, int N, int K, long long ldy, int F, int n_stages, int row_pairs,
-                    int token_tiles, int n_units) {
+                    int token_tiles, int n_units, int group_tiles) {
   extern __shared__ uint8_t smem_raw[];
   constexpr int N_ACC = MODE == 1 ? 2 : 1;
   constexpr int HALF = BN / 2;                                              // tokens this CTA loads
@@ -473,8 +477,11 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
   const uint32_t tmem_base = *tmem_holder;
 
   auto unit_coords = [&](int u, int& n0, int& t0) {
-    const int tt = u % token_tiles;
-    n0 = (u / token_tiles) * 2 * TC_BM + (int)rank * TC_BM;   // this CTA's 128 rows
+    const int per_group = group_tiles * row_pairs;
+    const int g = u / per_group, r = u - g * per_group;
+    const int here = min(group_tiles, token_tiles - g * group_tiles);     // the last group may be narrower
+    const int rp = r / here, tt = g * group_tiles + (r - rp * here);
+    n0 = rp * 2 * TC_BM + (int)rank * TC_BM;                  // this CTA's 128 rows
     t0 = tt * BN;
   };
 
@@ -708,6 +715,18 @@ static int launch_pair(const CUtensorMap& mw, const CUtensorMap& mx, void* Y, in
   const int row_pairs = (rows + 2 * TC_BM - 1) / (2 * TC_BM), token_tiles = (T + BN - 1) / BN;
   const long long n_units = (long long)row_pairs * token_tiles;
   if (n_units > 0x7fffffff) return LLMX_REFUSED(3);
+  // token tiles per group: a group's activations (BN tokens x K each) take at most half of L2, and the groups
+  // are of about equal size
+  static int l2_bytes = 0;
+  if (!l2_bytes) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (cudaDeviceGetAttribute(&l2_bytes, cudaDevAttrL2CacheSize, dev) != cudaSuccess || l2_bytes <= 0) l2_bytes = 64 << 20;
+  }
+  long long most = (l2_bytes / 2) / ((long long)BN * K * 2);
+  if (most < 2) most = 2;
+  const long long n_groups = (token_tiles + most - 1) / most;
+  const long long group_tiles = (token_tiles + n_groups - 1) / n_groups;
   cudaLaunchConfig_t cfg = {};
   cfg.blockDim = dim3(TC_THREADS);
   cfg.dynamicSmemBytes = smem;
@@ -734,7 +753,7 @@ static int launch_pair(const CUtensorMap& mw, const CUtensorMap& mx, void* Y, in
   cfg.gridDim = dim3(2 * pairs);
   cfg.numAttrs = 2;
   cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, mw, mx, (TY*)Y, T, N, K, ldy, F, stages, row_pairs, token_tiles,
-                                     (int)n_units);
+                                     (int)n_units, (int)group_tiles);
   if (e != cudaSuccess) return (int)e;
   return LLMX_LAUNCH_STATUS();
 }

@@ -354,6 +354,26 @@ def test_gemm_tc(T, N, K):
     assert kernels.gemm_tc_status() == 0
 
 
+def test_gemm_tc_pair_token_tile_groups():
+    """So many tokens that their activations no longer share L2: the CTA-pair kernel walks the token tiles
+    in groups (here two groups of sixteen tiles, the last tile partly empty).  Neighbouring token tiles differ
+    in loudness, so a tile computed for the wrong place shows."""
+    from llmoxide_b200 import kernels
+    T, N, K = 8000, 768, 4096
+    g = torch.Generator().manual_seed(5)
+    x = torch.randn(T, K, generator=g).bfloat16()
+    x *= (1 + (torch.arange(T) // 256) % 7).to(torch.bfloat16)[:, None]
+    w = (torch.randn(N, K, generator=g) / math.sqrt(K)).bfloat16()
+    xd, wd = x.to(DEV), w.to(DEV)
+    want = (xd.double() @ wd.double().t()).cpu()
+    out = torch.full((T, N), float("nan"), dtype=torch.float32, device=DEV)
+    kernels.gemm_tc(xd, wd, out, pair=True)
+    assert kernels.gemm_tc_status() == 0
+    assert rel(out, want) < 1e-5
+    for tile in range(0, T, 256):
+        assert rel(out[tile:tile + 256], want[tile:tile + 256]) < 1e-5, tile
+
+
 @pytest.mark.parametrize("T, N, K", [(129, 256, 64), (300, 520, 320), (2048, 1024, 512), (600, 20480, 192),
                                      (1000, 200, 1000), (257, 4096 + 128, 4096),
                                      # more units than CTA pairs, and not a multiple of them: a last round partly empty
