@@ -116,6 +116,54 @@ __device__ __forceinline__ void epilogue_tile(uint32_t acc_addr, bool have_acc, 
   }
 }
 
+// The same tile by way of shared memory, for prompt-sized steps (MODE 0 or 2): the four epilogue warps write
+// EP_ROWS tokens x EP_COLS features to one of two staging buffers, token after token as in Y, and one thread
+// sends the buffer off as a bulk tensor store.  A warp's direct stores reach only 64 bytes of a token's row each
+// (lane = feature), sixteen to a chunk; at 256 tokens a tile they cost four times what the rest of the
+// epilogue does, and a kernel's last tile has no MMAs of a next one to hide behind.
+template <typename TY>
+struct TcStage {
+  static constexpr int ROWS = 64 / sizeof(TY);      // tokens per chunk: 32 (bfloat16) or 16 (float32)
+};
+#define TC_STAGE_BYTES (2 * 32 * 128 * 2)            // two buffers of [ROWS][128 features]
+
+template <int BN, int MODE, typename TY>
+__device__ __forceinline__ void epilogue_tile_staged(uint32_t acc_addr, const CUtensorMap* map_y, TY* stage,
+                                                     int& chunk_no, int n0, int t0, int T, int quad, int lane,
+                                                     bool first_thread) {
+  static_assert(MODE != 1, "one accumulator");
+  constexpr int ROWS = TcStage<TY>::ROWS;
+  constexpr int COLS = MODE == 2 ? 64 : 128;
+  const bool upper = lane >= 16;
+  const int col = MODE == 2 ? quad * 16 + (lane & 15) : quad * 32 + lane;
+#pragma unroll 1
+  for (int c = 0; c < BN; c += ROWS) {
+    if (t0 + c >= T) break;
+    float v[ROWS];
+    if (ROWS == 32) tmem_ld32(acc_addr + (uint32_t)c, v);
+    else tmem_ld16(acc_addr + (uint32_t)c, v);
+    TY* buf = stage + (size_t)(chunk_no & 1) * ROWS * COLS;
+    if (first_thread) bulk_wait_read<1>();              // the store that last read this buffer is done with it
+    asm volatile("bar.sync 1, 128;" ::: "memory");
+    if (MODE == 2) {
+#pragma unroll
+      for (int e = 0; e < ROWS; e += 2) {
+        const float got = __shfl_xor_sync(0xffffffffu, upper ? v[e] : v[e + 1], 16);
+        const float gate = upper ? got : v[e];
+        const float up = upper ? v[e + 1] : got;
+        buf[(e + (upper ? 1 : 0)) * COLS + col] = from_f32<TY>(__fdividef(gate, 1.0f + __expf(-gate)) * up);
+      }
+    } else {
+#pragma unroll
+      for (int e = 0; e < ROWS; ++e) buf[e * COLS + col] = from_f32<TY>(v[e]);
+    }
+    fence_proxy_async();
+    asm volatile("bar.sync 1, 128;" ::: "memory");
+    if (first_thread) tma_store_2d(map_y, MODE == 2 ? (n0 >> 1) : n0, t0 + c, smem_u32(buf));
+    ++chunk_no;
+  }
+}
+
 // ---------------------------------------------------------------------------
 // The kernel: persistent CTAs over work units.  A unit is (tile of 128 rows
 // of W, tile of BN tokens, one split of K); unit u = ((split * row_tiles +
@@ -419,8 +467,8 @@ __host__ __device__ constexpr uint32_t umma_idesc_pair(int n) {   // M = 256 ove
 template <int BN, int MODE, typename TY>
 __global__ void __launch_bounds__(TC_THREADS)
 gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
-                    TY* __restrict__ Y, int T, int N, int K, long long ldy, int F, int n_stages, int row_pairs,
-                    int token_tiles, int n_units, int group_tiles) {
+                    const __grid_constant__ CUtensorMap map_y, TY* __restrict__ Y, int T, int N, int K, long long ldy,
+                    int F, int n_stages, int row_pairs, int token_tiles, int n_units, int group_tiles, int staged) {
   extern __shared__ uint8_t smem_raw[];
   constexpr int N_ACC = MODE == 1 ? 2 : 1;
   constexpr int HALF = BN / 2;                                              // tokens this CTA loads
@@ -443,6 +491,8 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
   const uint32_t full0 = smem_u32(bars), empty0 = full0 + 8u * n_stages;
   const uint32_t acc_full0 = empty0 + 8u * n_stages, acc_empty0 = acc_full0 + 16u;
   uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(bars + 2 * n_stages + 4);
+  volatile uint32_t* epi_failed = reinterpret_cast<volatile uint32_t*>(bars + 2 * n_stages + 5);
+  TY* stage_buf = reinterpret_cast<TY*>(base_ptr + (size_t)n_stages * STAGE_BYTES + 256);   // after the barriers
   // the leader's copies of the barriers that both CTAs signal
   const uint32_t leader_full0 = map_to_cta(full0, 0), leader_acc_empty0 = map_to_cta(acc_empty0, 0);
 
@@ -461,9 +511,11 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
       mbar_init(acc_full0 + 8u * i, 1);    // the multicast commit
       mbar_init(acc_empty0 + 8u * i, 8);   // four epilogue warps of each CTA (used in the leader only)
     }
+    *epi_failed = 0u;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("prefetch.tensormap [%0];" ::"l"(&map_w) : "memory");
     asm volatile("prefetch.tensormap [%0];" ::"l"(&map_x) : "memory");
+    if (staged) asm volatile("prefetch.tensormap [%0];" ::"l"(&map_y) : "memory");
   }
   if (warp == 1) {
     asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_holder)),
@@ -559,7 +611,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
     const int quad = warp & 3;
     const int n_limit = MODE == 0 ? N : F;
     bool failed = false;
-    int j = 0;
+    int j = 0, chunk_no = 0;
     for (int u = pair; u < n_units; u += n_pairs, ++j) {
       int n0, t0;
       unit_coords(u, n0, t0);
@@ -569,14 +621,25 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
         if (!ok && lane == 0) tc_report(13);
         failed = __shfl_sync(0xffffffffu, ok ? 0 : 1, 0) != 0;
       }
+      if (MODE != 1 && staged) {
+        // the four warps meet at barriers inside the staged epilogue, so they leave together or not at all
+        if (failed && lane == 0) *epi_failed = 1u;
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        failed = *epi_failed != 0u;
+      }
       if (failed) break;
       tc_fence_after();
       const uint32_t acc_addr = tmem_base + (uint32_t)buf * ACC_COLS + ((uint32_t)(quad * 32) << 16);
-      epilogue_tile<BN, MODE, TY>(acc_addr, true, true, Y, n0, t0, T, n_limit, ldy, quad, lane);
+      if (MODE != 1 && staged)
+        epilogue_tile_staged<BN, MODE == 1 ? 0 : MODE, TY>(acc_addr, &map_y, stage_buf, chunk_no, n0, t0, T, quad, lane,
+                                                             threadIdx.x == 64);
+      else
+        epilogue_tile<BN, MODE, TY>(acc_addr, true, true, Y, n0, t0, T, n_limit, ldy, quad, lane);
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_remote_arrive(leader_acc_empty0 + 8u * buf);
     }
+    if (threadIdx.x == 64) bulk_wait_all();    // this CTA's stores are in global memory before it ends
   }
   tc_fence_before();
   cluster_sync_all();                      // the peer may still read this CTA's shared and tensor memory until here
@@ -703,7 +766,13 @@ static int launch_pair(const CUtensorMap& mw, const CUtensorMap& mx, void* Y, in
   constexpr size_t STAGE = (size_t)N_ACC * TC_BM * TC_BK * 2 + (size_t)(BN / 2) * TC_BK * 2;
   int stages = (int)((200 * 1024) / STAGE);
   if (stages > 12) stages = 12;
-  const size_t smem = 1024 + (size_t)stages * STAGE + (2 * stages + 6) * 8;
+  // the output tiles leave through a staging buffer and bulk tensor stores where Y allows it
+  CUtensorMap my = mw;
+  int staged = 0;
+  if (MODE != 1 && !((uintptr_t)Y & 15) && !((ldy * (long long)sizeof(TY)) & 15))
+    staged = make_store_map(&my, Y, (int)sizeof(TY), (uint64_t)T, (uint64_t)(MODE == 2 ? F : N), (uint64_t)ldy,
+                            TcStage<TY>::ROWS, MODE == 2 ? 64 : 128) == 0;
+  const size_t smem = 1024 + (size_t)stages * STAGE + 256 + (MODE != 1 ? TC_STAGE_BYTES : 0);
   auto kernel = gemm_tc_pair_kernel<BN, MODE, TY>;
   static bool attr_set = false;
   if (!attr_set) {
@@ -752,8 +821,8 @@ static int launch_pair(const CUtensorMap& mw, const CUtensorMap& mx, void* Y, in
   const int pairs = n_units < max_pairs ? (int)n_units : max_pairs;
   cfg.gridDim = dim3(2 * pairs);
   cfg.numAttrs = 2;
-  cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, mw, mx, (TY*)Y, T, N, K, ldy, F, stages, row_pairs, token_tiles,
-                                     (int)n_units, (int)group_tiles);
+  cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, mw, mx, my, (TY*)Y, T, N, K, ldy, F, stages, row_pairs, token_tiles,
+                                     (int)n_units, (int)group_tiles, staged);
   if (e != cudaSuccess) return (int)e;
   return LLMX_LAUNCH_STATUS();
 }

@@ -189,6 +189,21 @@ __device__ __forceinline__ uint64_t umma_desc_mn(uint32_t smem_addr, uint32_t lb
 
 // Makes shared-memory writes of ordinary threads visible to the tensor core and TMA (the async proxy).
 __device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+// A tile written to shared memory goes out to global memory as one bulk tensor copy (rows and columns past the
+// tensor's extent are clipped).  The copies of a thread form groups; wait_read<N> returns once all but the N
+// newest groups have been read out of shared memory (their buffers may be written again), wait_all once every
+// group's bytes are in global memory.
+__device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, int x, int y, uint32_t src) {
+  asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%1, %2}], [%3];"
+               ::"l"(map), "r"(x), "r"(y), "r"(src)
+               : "memory");
+  asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+}
+template <int N>
+__device__ __forceinline__ void bulk_wait_read() {
+  asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(N) : "memory");
+}
+__device__ __forceinline__ void bulk_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
 __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
 }
@@ -210,6 +225,22 @@ static EncodeTiledFn encode_fn() {
       fn = (EncodeTiledFn)p;
   }
   return fn;
+}
+
+// A matrix [rows, cols] of 2- or 4-byte elements with row stride `ld` elements, as the target of bulk stores of
+// [box_rows x box_cols] tiles that lie row after row in shared memory (no swizzle).
+static int make_store_map(CUtensorMap* map, void* ptr, int elem_bytes, uint64_t rows, uint64_t cols, uint64_t ld,
+                          uint32_t box_rows, uint32_t box_cols) {
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) return 1;
+  cuuint64_t dims[2] = {cols, rows};
+  cuuint64_t strides[1] = {ld * (uint64_t)elem_bytes};
+  cuuint32_t box[2] = {box_cols, box_rows};
+  cuuint32_t elem[2] = {1, 1};
+  CUresult r = fn(map, elem_bytes == 2 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, ptr, dims,
+                  strides, box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE,
+                  CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? 0 : 2;
 }
 
 // A bf16 matrix [rows, cols] with row stride `ld` elements, boxes of [box_rows x 64 columns], 128-byte swizzle.
