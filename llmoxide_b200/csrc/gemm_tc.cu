@@ -130,7 +130,7 @@ struct TcStage {
 template <int BN, int MODE, typename TY>
 __device__ __forceinline__ void epilogue_tile_staged(uint32_t acc_addr, const CUtensorMap* map_y, TY* stage,
                                                      int& chunk_no, int n0, int t0, int T, int quad, int lane,
-                                                     bool first_thread) {
+                                                     bool first_thread, bool accumulate) {
   static_assert(MODE != 1, "one accumulator");
   constexpr int ROWS = TcStage<TY>::ROWS;
   constexpr int COLS = MODE == 2 ? 64 : 128;
@@ -159,7 +159,10 @@ __device__ __forceinline__ void epilogue_tile_staged(uint32_t acc_addr, const CU
     }
     fence_proxy_async();
     asm volatile("bar.sync 1, 128;" ::: "memory");
-    if (first_thread) tma_store_2d(map_y, MODE == 2 ? (n0 >> 1) : n0, t0 + c, smem_u32(buf));
+    if (first_thread) {
+      if (accumulate) tma_reduce_add_2d(map_y, n0, t0 + c, smem_u32(buf));       // Y += tile (MODE 0, float32)
+      else tma_store_2d(map_y, MODE == 2 ? (n0 >> 1) : n0, t0 + c, smem_u32(buf));
+    }
     ++chunk_no;
   }
 }
@@ -468,7 +471,8 @@ template <int BN, int MODE, typename TY>
 __global__ void __launch_bounds__(TC_THREADS)
 gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
                     const __grid_constant__ CUtensorMap map_y, TY* __restrict__ Y, int T, int N, int K, long long ldy,
-                    int F, int n_stages, int row_pairs, int token_tiles, int n_units, int group_tiles, int staged) {
+                    int F, int n_stages, int row_pairs, int token_tiles, int n_units, int group_tiles, int staged,
+                    int accumulate) {
   extern __shared__ uint8_t smem_raw[];
   constexpr int N_ACC = MODE == 1 ? 2 : 1;
   constexpr int HALF = BN / 2;                                              // tokens this CTA loads
@@ -632,7 +636,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
       const uint32_t acc_addr = tmem_base + (uint32_t)buf * ACC_COLS + ((uint32_t)(quad * 32) << 16);
       if (MODE != 1 && staged)
         epilogue_tile_staged<BN, MODE == 1 ? 0 : MODE, TY>(acc_addr, &map_y, stage_buf, chunk_no, n0, t0, T, quad, lane,
-                                                             threadIdx.x == 64);
+                                                             threadIdx.x == 64, accumulate != 0);
       else
         epilogue_tile<BN, MODE, TY>(acc_addr, true, true, Y, n0, t0, T, n_limit, ldy, quad, lane);
       tc_fence_before();
@@ -761,7 +765,7 @@ LLMX_API int llmx_gemm_tc_scaled(const void* X, const void* W, void* Y, int y_dt
 
 template <int BN, int MODE, typename TY>
 static int launch_pair(const CUtensorMap& mw, const CUtensorMap& mx, void* Y, int T, int N, int K, long long ldy,
-                       int F, cudaStream_t stream) {
+                       int F, int accumulate, cudaStream_t stream) {
   constexpr int N_ACC = MODE == 1 ? 2 : 1;
   constexpr size_t STAGE = (size_t)N_ACC * TC_BM * TC_BK * 2 + (size_t)(BN / 2) * TC_BK * 2;
   int stages = (int)((200 * 1024) / STAGE);
@@ -772,6 +776,7 @@ static int launch_pair(const CUtensorMap& mw, const CUtensorMap& mx, void* Y, in
   if (MODE != 1 && !((uintptr_t)Y & 15) && !((ldy * (long long)sizeof(TY)) & 15))
     staged = make_store_map(&my, Y, (int)sizeof(TY), (uint64_t)T, (uint64_t)(MODE == 2 ? F : N), (uint64_t)ldy,
                             TcStage<TY>::ROWS, MODE == 2 ? 64 : 128) == 0;
+  if (accumulate && !staged) return LLMX_REFUSED(4);      // Y += ... exists only as a bulk tensor reduction
   const size_t smem = 1024 + (size_t)stages * STAGE + 256 + (MODE != 1 ? TC_STAGE_BYTES : 0);
   auto kernel = gemm_tc_pair_kernel<BN, MODE, TY>;
   static bool attr_set = false;
@@ -822,14 +827,17 @@ static int launch_pair(const CUtensorMap& mw, const CUtensorMap& mx, void* Y, in
   cfg.gridDim = dim3(2 * pairs);
   cfg.numAttrs = 2;
   cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, mw, mx, my, (TY*)Y, T, N, K, ldy, F, stages, row_pairs, token_tiles,
-                                     (int)n_units, (int)group_tiles, staged);
+                                     (int)n_units, (int)group_tiles, staged, accumulate);
   if (e != cudaSuccess) return (int)e;
   return LLMX_LAUNCH_STATUS();
 }
 
-// The CTA-pair kernel: prompt-sized token counts only (T > 128), no split.  Same arguments as llmx_gemm_tc.
+// The CTA-pair kernel: prompt-sized token counts only (T > 128), no split.  Same arguments as llmx_gemm_tc, and
+// `accumulate`: Y += X W^T instead of Y = X W^T (mode 0 and float32 Y only: every element receives one
+// float32 addition, so the result does not depend on the order in which the tiles arrive).
 LLMX_API int llmx_gemm_tc_pair(const void* X, const void* W, void* Y, int y_dtype, int T, int N, int K,
-                               long long ldx, long long ldw, long long ldy, int mode, cudaStream_t stream) {
+                               long long ldx, long long ldw, long long ldy, int mode, int accumulate,
+                               cudaStream_t stream) {
   if (T <= 0 || N <= 0) return 0;
   if (K <= 0 || (K % 8) || (ldx % 8) || (ldw % 8) || ((uintptr_t)X & 15) || ((uintptr_t)W & 15)) return LLMX_REFUSED(1);
   if (T <= 128 || mode < 0 || mode > 2 || (mode == 1 && (N % 2)) || (mode == 2 && (N % 32))) return LLMX_REFUSED(1);
@@ -838,10 +846,11 @@ LLMX_API int llmx_gemm_tc_pair(const void* X, const void* W, void* Y, int y_dtyp
   CUtensorMap mw, mx;
   if (make_map(&mw, W, (uint64_t)N, (uint64_t)K, (uint64_t)ldw, TC_BM, true)) return LLMX_REFUSED(4);
   if (make_map(&mx, X, (uint64_t)T, (uint64_t)K, (uint64_t)ldx, (uint32_t)(bn / 2), false)) return LLMX_REFUSED(4);
-  if (mode == 0 && y_dtype == LLMX_BF16) return launch_pair<256, 0, bf16>(mw, mx, Y, T, N, K, ldy, F, stream);
-  if (mode == 0 && y_dtype == LLMX_F32) return launch_pair<256, 0, float>(mw, mx, Y, T, N, K, ldy, F, stream);
-  if (mode == 1 && y_dtype == LLMX_BF16) return launch_pair<128, 1, bf16>(mw, mx, Y, T, N, K, ldy, F, stream);
-  if (mode == 2 && y_dtype == LLMX_BF16) return launch_pair<256, 2, bf16>(mw, mx, Y, T, N, K, ldy, F, stream);
+  if (accumulate && (mode != 0 || y_dtype != LLMX_F32)) return LLMX_REFUSED(1);
+  if (mode == 0 && y_dtype == LLMX_BF16) return launch_pair<256, 0, bf16>(mw, mx, Y, T, N, K, ldy, F, 0, stream);
+  if (mode == 0 && y_dtype == LLMX_F32) return launch_pair<256, 0, float>(mw, mx, Y, T, N, K, ldy, F, accumulate, stream);
+  if (mode == 1 && y_dtype == LLMX_BF16) return launch_pair<128, 1, bf16>(mw, mx, Y, T, N, K, ldy, F, 0, stream);
+  if (mode == 2 && y_dtype == LLMX_BF16) return launch_pair<256, 2, bf16>(mw, mx, Y, T, N, K, ldy, F, 0, stream);
   return LLMX_REFUSED(2);
 }
 

@@ -199,6 +199,13 @@ __device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, int x, int 
                : "memory");
   asm volatile("cp.async.bulk.commit_group;" ::: "memory");
 }
+// The same copy as an addition: global[tile] += shared[tile], element by element in the tensor's type.
+__device__ __forceinline__ void tma_reduce_add_2d(const CUtensorMap* map, int x, int y, uint32_t src) {
+  asm volatile("cp.reduce.async.bulk.tensor.2d.global.shared::cta.add.tile.bulk_group [%0, {%1, %2}], [%3];"
+               ::"l"(map), "r"(x), "r"(y), "r"(src)
+               : "memory");
+  asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+}
 template <int N>
 __device__ __forceinline__ void bulk_wait_read() {
   asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(N) : "memory");

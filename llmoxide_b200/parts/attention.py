@@ -66,7 +66,9 @@ class GQAttention:
             libs.add("attention")
         return libs
 
-    def forward(self, x, ctx, view, writes_cache=True):
+    adds_to_residual = True      # forward() takes ``residual`` and may return None: "already added"
+
+    def forward(self, x, ctx, view, writes_cache=True, residual=None):
         H, G, D = self.H, self.G, self.D
         T = x.shape[0]
         dev = x.device
@@ -85,6 +87,8 @@ class GQAttention:
                                    self.q_gain, self.k_gain, self.eps, cos, sin, n_rot, H, G, D, writes_cache)
         out = torch.empty_like(q)
         self.attend(q, out, view, block_table, ctx)
+        if residual is not None and self.o.add_into(out, residual):
+            return None
         return self.o(out, splits_ok=True)
 
     def attend(self, q, out, view, block_table, ctx):

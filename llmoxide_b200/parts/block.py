@@ -5,7 +5,9 @@ h += mixer(norm(h)); h += feed_forward(norm(h)).
 
 The residual stream stays float32.  Each residual add is fused into the norm
 that follows it, so a block hands its last delta on as ``pending`` instead of
-adding it itself."""
+adding it itself.  A mixer or feed-forward with ``adds_to_residual`` is given the
+stream (``residual=h``) and may add its result there itself, in the kernel of its
+last product; it then returns None, and the norm that follows has nothing to add."""
 
 from __future__ import annotations
 
@@ -44,13 +46,19 @@ class PreNormBlock:
         x = _norm(self.mixer_norm, h, pending, self.mixer, plain=probe is not None)
         if probe:
             probe("resid_in", h), probe("attn_norm", x)      # names after crates/model/src/qwen35/cpu.rs:136-401
-        a = self.mixer.forward(x, ctx, view, writes_cache)
+        if probe is None and getattr(self.mixer, "adds_to_residual", False):
+            a = self.mixer.forward(x, ctx, view, writes_cache, residual=h)
+        else:
+            a = self.mixer.forward(x, ctx, view, writes_cache)
         if probe:
             probe("attn_output", _summed(a))
         x = _norm(self.ff_norm, h, a, self.feed_forward, plain=probe is not None)
         if probe:
             probe("attn_residual", h), probe("attn_post_norm", x)
-        out = self.feed_forward.forward(x, ctx)
+        if probe is None and getattr(self.feed_forward, "adds_to_residual", False):
+            out = self.feed_forward.forward(x, ctx, residual=h)
+        else:
+            out = self.feed_forward.forward(x, ctx)
         if probe:
             probe("ffn_out", _summed(out))
         return out

@@ -54,7 +54,9 @@ class GatedMLP:
         """The gate|up product can apply a norm's row scales in its epilogue, ahead of the activation."""
         return self.gate_up._tc is not None
 
-    def forward(self, x, ctx):
+    adds_to_residual = True      # forward() takes ``residual`` and may return None: "already added"
+
+    def forward(self, x, ctx, residual=None):
         tc = self.gate_up._tc
         scaled = isinstance(x, RowScaled)
         n_tokens = x.shape[0]
@@ -67,4 +69,6 @@ class GatedMLP:
             gu = self.gate_up(x, splits_ok=True)
             act = torch.empty((n_tokens, self.F), dtype=self.rt.act_dtype, device=x.device)
             kernels.silu_gate(gu, act, self.block)
+        if residual is not None and self.down.add_into(act, residual):
+            return None
         return self.down(act, splits_ok=True)

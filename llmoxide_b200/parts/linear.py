@@ -37,6 +37,14 @@ class Linear:
         kernels.gemm_fma(x, self.weight, out)
         return out
 
+    def add_into(self, x, residual) -> bool:
+        """residual += x W^T inside the product's kernel, if it can for these rows (then True); else nothing
+        happens and the caller takes the product as a tensor and leaves the addition to the norm that follows."""
+        if self._tc is None or isinstance(x, RowScaled) or x.dtype != torch.bfloat16 or not self._tc.adds_to(x, residual):
+            return False
+        self._tc.add_into(x, residual)
+        return True
+
     @property
     def takes_row_scales(self) -> bool:
         return self._tc is not None

@@ -67,6 +67,18 @@ class TensorCoreLinear:
         self.weight, self.n_sm = weight, n_sm
         self.N, self.K = weight.shape
 
+    def adds_to(self, x, residual) -> bool:
+        """Whether this product, for these rows, can add its result to ``residual`` itself (prompt-sized steps
+        on the CTA-pair kernel: every element of ``residual`` then receives exactly one float32 addition)."""
+        return (not isinstance(x, RowScaled) and residual is not None and residual.dtype == torch.float32
+                and residual.is_contiguous() and residual.shape == (x.shape[0], self.N) and self.N % 4 == 0
+                and x.shape[0] > PAIR_MIN_TOKENS and kernels.gemm_tc_supports(x, self.weight)
+                and choose_prompt_splits(self.N, self.K, x.shape[0], self.n_sm) == 1)
+
+    def add_into(self, x, residual) -> None:
+        """residual += x W^T."""
+        kernels.gemm_tc(x, self.weight, residual, pair=True, accumulate=True)
+
     def __call__(self, x, out_dtype, splits_ok):
         x, scale = self._unpack(x)
         T = x.shape[0]

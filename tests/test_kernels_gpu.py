@@ -398,6 +398,11 @@ def test_gemm_tc_pair(T, N, K):
     out16 = torch.empty(T, N, dtype=torch.bfloat16, device=DEV)
     kernels.gemm_tc(xd, wd, out16, pair=True)
     assert rel(out16, want) < 6e-3
+    if N % 4 == 0:        # Y += X W^T: one float32 addition per element, the same bits as adding the product
+        base = torch.randn(T, N, generator=g).to(DEV)
+        acc = base.clone()
+        kernels.gemm_tc(xd, wd, acc, pair=True, accumulate=True)
+        assert torch.equal(acc, base + out32)
     if N % 2 == 0:
         F = N // 2
         act = torch.full((T, F), float("nan"), dtype=torch.bfloat16, device=DEV)

@@ -12,7 +12,7 @@ import pytest
 import torch
 
 import plain_qwen3 as plain
-from tiny_configs import TINY_B, TINY_C
+from tiny_configs import TINY_B, TINY_C, TINY_D
 
 pytestmark = pytest.mark.gpu
 DEV = "cuda"
@@ -138,6 +138,30 @@ def test_feed_forward_part():
     out = ff.forward(x.to(DEV), None)
     out = out.sum(0) if out.dim() == 3 else out
     assert rel(out, plain.swiglu_ffn(x, plain.layer_weights(w, 2))) < 2e-5
+
+
+def test_feed_forward_adds_to_residual():
+    """A prompt-sized bfloat16 step: the feed-forward adds its result to the stream it is given, inside its last
+    product, and says so by returning None.  The stream then holds what adding the returned tensor would give,
+    up to that tensor's rounding to bfloat16 (the fused sum skips it)."""
+    from llmoxide_b200.parts.registry import FEED_FORWARDS
+
+    cfg, spec, w = _weights_of(TINY_D)
+    bs = spec.blocks[1]
+    ff = FEED_FORWARDS[bs.feed_forward.kind](bs.feed_forward, {k: v.to(DEV).bfloat16() for k, v in w.items()},
+                                             _rt("bfloat16"))
+    assert ff.adds_to_residual
+    g = torch.Generator().manual_seed(1)
+    x = torch.randn(300, TINY_D["hidden_size"], generator=g).bfloat16().to(DEV)
+    out = ff.forward(x, None)
+    assert out is not None and out.dim() == 2
+    h0 = torch.randn(300, TINY_D["hidden_size"], generator=g).to(DEV)
+    h = h0.clone()
+    assert ff.forward(x, None, residual=h) is None
+    assert rel(h - h0, out) < 4e-3 and not torch.equal(h, h0)
+    few = x[:40]                     # a step of few tokens keeps the addition for the norm that follows
+    h = h0[:40].clone()
+    assert ff.forward(few, None, residual=h) is not None and torch.equal(h, h0[:40])
 
 
 def test_block_part():
