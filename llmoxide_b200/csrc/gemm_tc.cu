@@ -330,11 +330,15 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
       // r[t] for the step's tokens (T <= 64): the partial sums of squares come from the kernel before
       pdl_wait();
       waited = true;
-      for (int t = quad; t < T && t < 64; t += 4) {
+      // one thread per token: its partial sums are loaded together (one trip to L2 for the whole tile; a loop
+      // over tokens would make one trip per token and, at 64 tokens, outlast the MMAs) and added in the order
+      // of the parts
+      const int t = (int)threadIdx.x - 64;
+      if (t < T && t < 64) {
         float a = 0.f;
-        for (int p = lane; p < sc.parts; p += 32) a += __ldcg(sc.sumsq + (size_t)p * sc.stride + t);
-        a = warp_sum(a);
-        if (lane == 0) row_scales[t] = 1.0f / sqrtf(a / sc.d + sc.eps);
+#pragma unroll 8
+        for (int p = 0; p < sc.parts; ++p) a += __ldcg(sc.sumsq + (size_t)p * sc.stride + t);
+        row_scales[t] = 1.0f / sqrtf(a / sc.d + sc.eps);
       }
       asm volatile("bar.sync 2, 128;" ::: "memory");
       row_scale = row_scales;
