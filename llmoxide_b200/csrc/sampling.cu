@@ -310,44 +310,102 @@ LLMX_API int llmx_sample(float* logits, long long ld, int n_rows, int V, const f
   return LLMX_LAUNCH_STATUS();
 }
 
-// Argmax alone, for greedy decoding: the last index among equal maxima.
-__global__ void __launch_bounds__(SMP_THREADS)
-argmax_kernel(const float* __restrict__ logits, long long ld, int V, int* __restrict__ out_tokens) {
-  __shared__ float red_v[32];
-  __shared__ int red_i[32];
+// Argmax alone, for greedy decoding: the last index among equal maxima.  A row is cut into slices, one CTA
+// each, so that a few rows of a large vocabulary still occupy the GPU (one CTA per row reads its 600 KB one
+// scalar load at a time: 30 us at eight rows).  A CTA's result is one 64-bit word, (order key of the value,
+// index): the larger word is the larger value and, among equal values, the later index; 0 stands for "no
+// number here".  The CTA that arrives last for a row (a counter that it sets back to 0) takes the largest of
+// the slices' words.  Nothing waits for anything.
+#define ARG_THREADS 256
+#define ARG_MAX_ROWS 4096
+#define ARG_MAX_SLICES 64
+static __device__ unsigned long long g_arg_part[ARG_MAX_ROWS * ARG_MAX_SLICES];
+static __device__ unsigned int g_arg_count[ARG_MAX_ROWS];
+
+__device__ __forceinline__ unsigned long long arg_word(float v, int i) {
+  return v != v ? 0ull : ((unsigned long long)order_key(v + 0.0f) << 32) | (unsigned int)i;   // (-0 counts as +0)
+}
+
+__global__ void __launch_bounds__(ARG_THREADS)
+argmax_kernel(const float* __restrict__ logits, long long ld, int V, int n_slices, int slice_len,
+              int* __restrict__ out_tokens) {
+  __shared__ unsigned long long red[ARG_THREADS / 32];
+  __shared__ bool is_last;
   pdl_launch_dependents();
   pdl_wait();
-  const int b = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int b = blockIdx.y, sl = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const float* row = logits + (size_t)b * ld;
-  float best = -INFINITY;
-  int best_i = -1;
-  for (int i = tid; i < V; i += SMP_THREADS) {
-    const float v = row[i];
-    if (v != v) continue;
-    if (best_i < 0 || v > best || (v == best && i > best_i)) { best = v; best_i = i; }
-  }
-  for (int o = 16; o > 0; o >>= 1) {
-    const float ov = __shfl_xor_sync(0xffffffffu, best, o);
-    const int oi = __shfl_xor_sync(0xffffffffu, best_i, o);
-    if (oi >= 0 && (best_i < 0 || ov > best || (ov == best && oi > best_i))) { best = ov; best_i = oi; }
-  }
-  if (lane == 0) { red_v[warp] = best; red_i[warp] = best_i; }
-  __syncthreads();
-  if (warp == 0) {
-    best = red_v[lane]; best_i = red_i[lane];
-    for (int o = 16; o > 0; o >>= 1) {
-      const float ov = __shfl_xor_sync(0xffffffffu, best, o);
-      const int oi = __shfl_xor_sync(0xffffffffu, best_i, o);
-      if (oi >= 0 && (best_i < 0 || ov > best || (ov == best && oi > best_i))) { best = ov; best_i = oi; }
+  const int lo = sl * slice_len, hi = min(V, lo + slice_len);
+  unsigned long long best = 0ull;
+  if ((((uintptr_t)row | (uintptr_t)(ld * 4)) & 15) == 0 && (slice_len & 3) == 0) {
+    // whole groups of four, four loads in flight per thread
+    const int n4 = (hi - lo) >> 2;
+    const float4* r4 = reinterpret_cast<const float4*>(row + lo);
+    for (int i0 = tid; i0 < n4; i0 += 4 * ARG_THREADS) {
+      float4 v[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u)
+        if (i0 + u * ARG_THREADS < n4) v[u] = __ldcs(r4 + i0 + u * ARG_THREADS);
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const int i = i0 + u * ARG_THREADS;
+        if (i < n4) {
+          const int at = lo + 4 * i;
+          best = max(best, arg_word(v[u].x, at));
+          best = max(best, arg_word(v[u].y, at + 1));
+          best = max(best, arg_word(v[u].z, at + 2));
+          best = max(best, arg_word(v[u].w, at + 3));
+        }
+      }
     }
-    if (lane == 0) out_tokens[b] = best_i < 0 ? 0 : best_i;
+    for (int i = lo + 4 * n4 + tid; i < hi; i += ARG_THREADS) best = max(best, arg_word(row[i], i));
+  } else {
+    for (int i = lo + tid; i < hi; i += ARG_THREADS) best = max(best, arg_word(row[i], i));
+  }
+  for (int o = 16; o > 0; o >>= 1) best = max(best, __shfl_xor_sync(0xffffffffu, best, o));
+  if (lane == 0) red[warp] = best;
+  __syncthreads();
+  if (tid == 0) {
+    for (int w = 1; w < ARG_THREADS / 32; ++w) best = max(best, red[w]);
+    if (n_slices == 1) {
+      out_tokens[b] = (int)(unsigned int)best;          // (no number at all: 0)
+      is_last = false;
+    } else {
+      g_arg_part[(size_t)b * ARG_MAX_SLICES + sl] = best;
+      __threadfence();
+      is_last = atomicAdd(&g_arg_count[b], 1u) == (unsigned int)(n_slices - 1);
+    }
+  }
+  __syncthreads();
+  if (!is_last) return;
+  __threadfence();
+  if (warp == 0) {
+    unsigned long long all = 0ull;
+    for (int i = lane; i < n_slices; i += 32) all = max(all, __ldcg(&g_arg_part[(size_t)b * ARG_MAX_SLICES + i]));
+    for (int o = 16; o > 0; o >>= 1) all = max(all, __shfl_xor_sync(0xffffffffu, all, o));
+    if (lane == 0) {
+      out_tokens[b] = (int)(unsigned int)all;
+      g_arg_count[b] = 0u;                              // for the next launch
+    }
   }
 }
 
 LLMX_API int llmx_argmax(const float* logits, long long ld, int n_rows, int V, int* out_tokens,
                          cudaStream_t stream) {
   if (n_rows <= 0) return 0;
-  if (V <= 0 || ld < V) return LLMX_REFUSED(1);
-  launch_pdl(argmax_kernel, dim3(n_rows), dim3(SMP_THREADS), 0, stream, logits, ld, V, out_tokens);
+  if (V <= 0 || ld < V || n_rows > 65535) return LLMX_REFUSED(1);
+  // slices: about two CTAs per SM in all, each of a whole number of 4-float groups, at least 1024 floats
+  int n_slices = 1;
+  if (n_rows <= ARG_MAX_ROWS) {
+    n_slices = (2 * 148 + n_rows - 1) / n_rows;
+    if (n_slices > ARG_MAX_SLICES) n_slices = ARG_MAX_SLICES;
+    if (n_slices > V / 1024) n_slices = V / 1024;
+    if (n_slices < 1) n_slices = 1;
+  }
+  int slice_len = (V + n_slices - 1) / n_slices;
+  slice_len = (slice_len + 3) & ~3;
+  n_slices = (V + slice_len - 1) / slice_len;
+  launch_pdl(argmax_kernel, dim3(n_slices, n_rows), dim3(ARG_THREADS), 0, stream, logits, ld, V, n_slices, slice_len,
+             out_tokens);
   return LLMX_LAUNCH_STATUS();
 }

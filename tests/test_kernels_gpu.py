@@ -247,6 +247,30 @@ def test_argmax_takes_the_last_of_equal_maxima():
     assert out.tolist() == [plain.argmax(r.numpy()) for r in logits]
 
 
+@pytest.mark.parametrize("n_rows, V", [(8, 151936), (1, 151936), (64, 32000), (300, 1000), (3, 4099)])
+def test_argmax_in_slices(n_rows, V):
+    """Rows cut into slices over many CTAs: equal maxima in different slices, a maximum at a slice's edge, rows
+    without a finite number, NaNs, and both zeros; twice, since the kernel leaves its counters for the next call."""
+    from llmoxide_b200 import kernels
+    g = torch.Generator().manual_seed(n_rows + V)
+    logits = torch.randn(n_rows, V, generator=g)
+    logits[0, [5, V // 2, V - 3]] = 7.5                       # equal maxima far apart: the last one
+    if n_rows > 1:
+        logits[1] = float("-inf")                             # no finite number: the last index
+        logits[-1, ::7] = float("nan")
+    if n_rows > 2:
+        logits[2] = -1.0
+        logits[2, [3, V - 2]] = torch.tensor([-0.0, 0.0])     # the two zeros are one value: the later index
+        logits[2, V - 2], logits[2, 3] = -0.0, 0.0
+    want = [plain.argmax(np.where(np.isnan(r.numpy()), -np.inf, r.numpy())) if not np.isnan(r.numpy()).all() else 0
+            for r in logits]
+    dev = logits.to(DEV)
+    for _ in range(2):
+        out = torch.full((n_rows,), -1, dtype=torch.int32, device=DEV)
+        kernels.argmax(dev, out)
+        assert out.tolist() == want
+
+
 @pytest.mark.parametrize("V, top_k, top_p, temp, pen", [
     (307, 20, 0.8, 0.7, 1.0), (5003, 64, 0.95, 1.0, 1.3), (5003, 1, 1.0, 1.0, 1.0),
     (5003, 1024, 1.0, 2.0, 1.0), (307, 0, 0.9, 1.5, 1.0), (151936, 20, 0.8, 0.7, 1.1),
