@@ -9,6 +9,12 @@
 // depend on what else is in the batch.  Equal logits are ordered by lower
 // token id first.
 //
+// A row of a large vocabulary is read by one SM at about 25 bytes a cycle, so what the kernel costs is how often
+// it reads the row: once for the maximum, the count of finite logits and a histogram of the keys' top byte, and
+// once more to collect every logit whose top byte is at least that of the k-th largest; those are usually a few
+// hundred, and sorting them gives the top k with its ties in id order.  Only when they are more than 1024 (a
+// row whose top logits crowd one binade) does the radix select go on byte by byte, a reading of the row each.
+//
 // top_k in [1, 1024] runs the sorted algorithm.  top_k = 0 (no limit) with
 // top_p >= 1 walks the whole vocabulary in id order instead of sorted order:
 // the same distribution, another mapping from u to a token.
@@ -32,13 +38,40 @@ __device__ __forceinline__ bool cand_before(const Cand& a, const Cand& b) {
   return a.v > b.v || (a.v == b.v && a.idx < b.idx);
 }
 
-__global__ void __launch_bounds__(SMP_THREADS)
+// Every element of a row to fn(value, index), four 16-byte loads in flight per thread where the row is
+// 16-byte aligned.  The order in which a thread sees its elements is not the index order.
+template <typename F>
+__device__ __forceinline__ void scan_row(const float* __restrict__ row, int V, int tid, F&& fn) {
+  if (((uintptr_t)row & 15) == 0) {
+    const int n4 = V >> 2;
+    const float4* r4 = reinterpret_cast<const float4*>(row);
+    int i = tid;
+    for (; i + 3 * SMP_THREADS < n4; i += 4 * SMP_THREADS) {
+      const float4 a = r4[i], b = r4[i + SMP_THREADS], c = r4[i + 2 * SMP_THREADS], d = r4[i + 3 * SMP_THREADS];
+      const int ib = i + SMP_THREADS, ic = i + 2 * SMP_THREADS, id = i + 3 * SMP_THREADS;
+      fn(a.x, 4 * i), fn(a.y, 4 * i + 1), fn(a.z, 4 * i + 2), fn(a.w, 4 * i + 3);
+      fn(b.x, 4 * ib), fn(b.y, 4 * ib + 1), fn(b.z, 4 * ib + 2), fn(b.w, 4 * ib + 3);
+      fn(c.x, 4 * ic), fn(c.y, 4 * ic + 1), fn(c.z, 4 * ic + 2), fn(c.w, 4 * ic + 3);
+      fn(d.x, 4 * id), fn(d.y, 4 * id + 1), fn(d.z, 4 * id + 2), fn(d.w, 4 * id + 3);
+    }
+    for (; i < n4; i += SMP_THREADS) {
+      const float4 a = r4[i];
+      fn(a.x, 4 * i), fn(a.y, 4 * i + 1), fn(a.z, 4 * i + 2), fn(a.w, 4 * i + 3);
+    }
+    for (int j = 4 * n4 + tid; j < V; j += SMP_THREADS) fn(row[j], j);
+  } else {
+    for (int j = tid; j < V; j += SMP_THREADS) fn(row[j], j);
+  }
+}
+
+__global__ void __launch_bounds__(SMP_THREADS, 1)
 sample_kernel(float* __restrict__ logits, long long ld, int V, const float* __restrict__ temperature,
               const int* __restrict__ top_k, const float* __restrict__ top_p,
               const float* __restrict__ repeat_penalty, const int* __restrict__ recent, int recent_width,
               const float* __restrict__ uniform, int* __restrict__ out_tokens, int* __restrict__ status) {
   __shared__ Cand cand[SMP_MAX_K];
   __shared__ unsigned hist[256];
+  __shared__ unsigned hist0[256];      // the keys' top byte, over the whole row
   __shared__ float red_v[32];
   __shared__ int red_i[32];
   __shared__ unsigned sh_prefix, sh_need, sh_count, sh_taken_eq;
@@ -58,21 +91,25 @@ sample_kernel(float* __restrict__ logits, long long ld, int V, const float* __re
       if (t >= 0 && t < V) row[t] = row[t] > 0.f ? row[t] / pen : row[t] * pen;
     }
   }
+  if (tid < 256) hist0[tid] = 0u;
   __syncthreads();
 
   const float temp = temperature[b];
   int k = top_k[b];
   const float tp = top_p[b];
 
-  // -- argmax (also the fallback when no logit is finite) ------------------
+  // -- argmax (also the fallback when no logit is finite), and the top byte's histogram -----
   float best = -INFINITY;
   int best_i = -1, n_finite_local = 0;
-  for (int i = tid; i < V; i += SMP_THREADS) {
-    const float v = row[i];
-    if (v != v) continue;
-    if (finite_f32(v)) ++n_finite_local;
+  const bool want_hist = temp > 0.f;
+  scan_row(row, V, tid, [&](float v, int i) {
+    if (v != v) return;
+    if (finite_f32(v)) {
+      ++n_finite_local;
+      if (want_hist) atomicAdd(&hist0[order_key(v) >> 24], 1u);
+    }
     if (best_i < 0 || v > best || (v == best && i > best_i)) { best = v; best_i = i; }
-  }
+  });
   // reduce (value, index): larger value, then larger index
   for (int o = 16; o > 0; o >>= 1) {
     const float ov = __shfl_xor_sync(0xffffffffu, best, o);
@@ -171,20 +208,33 @@ sample_kernel(float* __restrict__ logits, long long ld, int V, const float* __re
   }
   if (k > n_finite) k = n_finite;
 
-  // ---- radix select of the k-th largest key ------------------------------
-  if (tid == 0) { sh_prefix = 0u; sh_need = (unsigned)k; }
+  // ---- radix select of the k-th largest key: its top byte is in the histogram already ----------
+  if (tid == 0) {
+    unsigned need = (unsigned)k;
+    int digit = 255;
+    for (; digit > 0; --digit) {
+      if (hist0[digit] >= need) break;
+      need -= hist0[digit];
+    }
+    sh_need = need;  // how many of this digit's keys are still wanted
+    sh_prefix = (unsigned)digit << 24;
+    sh_count = hist0[digit];
+  }
   __syncthreads();
-  unsigned mask = 0u;
-  for (int shift = 24; shift >= 0; shift -= 8) {
+  // every logit with at least that top byte: the ones above it (all in the top k) and the ones that share it
+  const unsigned n_ge = ((unsigned)k - sh_need) + sh_count;
+  const bool few = n_ge <= (unsigned)SMP_MAX_K;
+  const unsigned top_byte = sh_prefix >> 24;
+  unsigned mask = 0xff000000u;
+  for (int shift = 16; shift >= 0 && !few; shift -= 8) {
     if (tid < 256) hist[tid] = 0u;
     __syncthreads();
     const unsigned prefix = sh_prefix;
-    for (int i = tid; i < V; i += SMP_THREADS) {
-      const float v = row[i];
-      if (!finite_f32(v)) continue;
+    scan_row(row, V, tid, [&](float v, int) {
+      if (!finite_f32(v)) return;
       const unsigned key = order_key(v);
       if ((key & mask) == prefix) atomicAdd(&hist[(key >> shift) & 255u], 1u);
-    }
+    });
     __syncthreads();
     if (tid == 0) {
       unsigned need = sh_need;
@@ -193,7 +243,7 @@ sample_kernel(float* __restrict__ logits, long long ld, int V, const float* __re
         if (hist[digit] >= need) break;
         need -= hist[digit];
       }
-      sh_need = need;  // how many of this digit's keys are still wanted
+      sh_need = need;
       sh_prefix = prefix | ((unsigned)digit << shift);
       sh_count = hist[digit];
     }
@@ -208,14 +258,21 @@ sample_kernel(float* __restrict__ logits, long long ld, int V, const float* __re
   __syncthreads();  // every thread has read the select's results before they are reset
   if (tid == 0) { sh_count = 0u; sh_taken_eq = 0u; }
   __syncthreads();
-  if (n_eq == need_eq) {
-    for (int i = tid; i < V; i += SMP_THREADS) {
-      const float v = row[i];
+  if (few) {
+    // at most 1024 of them: all are sorted below, and the first k of the sorted order are the top k
+    scan_row(row, V, tid, [&](float v, int i) {
+      if (finite_f32(v) && (order_key(v) >> 24) >= top_byte) {
+        const unsigned at = atomicAdd(&sh_count, 1u);
+        if (at < SMP_MAX_K) { cand[at].v = v; cand[at].idx = i; }
+      }
+    });
+  } else if (n_eq == need_eq) {
+    scan_row(row, V, tid, [&](float v, int i) {
       if (finite_f32(v) && order_key(v) >= kth_key) {
         const unsigned at = atomicAdd(&sh_count, 1u);
         if (at < SMP_MAX_K) { cand[at].v = v; cand[at].idx = i; }
       }
-    }
+    });
   } else {
     // ties at the threshold: those with the lowest ids are kept, so the equal
     // keys are taken in id order, one chunk of the row at a time
@@ -250,15 +307,18 @@ sample_kernel(float* __restrict__ logits, long long ld, int V, const float* __re
     }
   }
   __syncthreads();
-  const int n_cand = min((int)sh_count, SMP_MAX_K);
-  for (int i = n_cand + tid; i < SMP_MAX_K; i += SMP_THREADS) { cand[i].v = -INFINITY; cand[i].idx = 0x7fffffff; }
+  const int n_gathered = min((int)sh_count, SMP_MAX_K);
+  const int n_cand = min(n_gathered, k);                 // what the walk below sees: the top k
+  int sort_n = 2;
+  while (sort_n < n_gathered) sort_n <<= 1;
+  for (int i = n_gathered + tid; i < sort_n; i += SMP_THREADS) { cand[i].v = -INFINITY; cand[i].idx = 0x7fffffff; }
   __syncthreads();
 
   // ---- bitonic sort: larger value first, then lower id ---------------------
-  for (int size = 2; size <= SMP_MAX_K; size <<= 1) {
+  for (int size = 2; size <= sort_n; size <<= 1) {
     for (int stride = size >> 1; stride > 0; stride >>= 1) {
       const int i = tid, j = i ^ stride;
-      if (j > i) {
+      if (j > i && j < sort_n) {
         const bool up = (i & size) == 0;
         const Cand a = cand[i], c = cand[j];
         const bool swap = up ? cand_before(c, a) : cand_before(a, c);

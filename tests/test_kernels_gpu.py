@@ -309,6 +309,34 @@ def test_sample_matches_the_plain_sampler(V, top_k, top_p, temp, pen):
     assert len(mismatches) <= 1, mismatches
 
 
+@pytest.mark.parametrize("top_k", [64, 1024])
+def test_sample_with_many_equal_logits_at_the_threshold(top_k):
+    """Logits that take a dozen values only, so that the k-th largest is shared by a hundred others of which
+    a few belong to the top k: those with the lowest ids.  With k = 64 the logits at or above the threshold's
+    binade are few and the kernel sorts them all; with k = 1024 they are more than 1024 and it selects byte by
+    byte and takes the equal ones in id order."""
+    from llmoxide_b200 import kernels
+    V, B = 5003, 16
+    g = torch.Generator().manual_seed(top_k)
+    logits = torch.round(2 * torch.randn(B, V, generator=g)).float()
+    u = torch.rand(B, generator=g)
+    u[0], u[1] = 0.0, 0.9999999                    # the first and the last of the kept tokens
+    dev = lambda t: t.to(DEV)
+    out = torch.empty(B, dtype=torch.int32, device=DEV)
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    kernels.sample(dev(logits.clone()), dev(torch.ones(B)), dev(torch.full((B,), top_k, dtype=torch.int32)),
+                   dev(torch.ones(B)), None, None, dev(u), out, status)
+    assert status.item() == 0
+    want = [plain.sample(logits[b].numpy(), [], temperature=1.0, top_k=top_k, top_p=1.0, repeat_penalty=1.0,
+                         repeat_window=64, u=float(u[b])) for b in range(B)]
+    wrong = [(b, g_, w) for b, (g_, w) in enumerate(zip(out.tolist(), want)) if g_ != w]
+    assert len(wrong) <= 1, wrong                  # (a draw on the edge between two tokens may fall either way)
+    # every chosen token is one of the top k in the order (value down, id up)
+    for b, tok in enumerate(out.tolist()):
+        order = sorted(range(V), key=lambda i: (-float(logits[b, i]), i))[:top_k]
+        assert tok in order, (b, tok)
+
+
 def test_sample_whole_vocabulary_follows_the_distribution():
     from llmoxide_b200 import kernels
     V, B = 3000, 4096
