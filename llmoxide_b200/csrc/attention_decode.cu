@@ -347,30 +347,37 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
     }
   }
   __syncthreads();
-  for (int idx = threadIdx.x; idx < n_heads * D; idx += DEC_WARPS * 32) {
-    const int h = idx / D, d = idx % D;
+  for (int idx = threadIdx.x; idx < n_heads * (D / 4); idx += DEC_WARPS * 32) {     // four dims at a time
+    const int h = idx / (D / 4), d = (idx % (D / 4)) * 4;
     float mx = -INFINITY;
 #pragma unroll
     for (int w = 0; w < DEC_WARPS; ++w) mx = fmaxf(mx, mml[(w * DEC_ROWS + h) * 2]);
-    float a = 0.f, ls = 0.f;
+    float4 a = make_float4(0.f, 0.f, 0.f, 0.f);
+    float ls = 0.f;
 #pragma unroll
     for (int w = 0; w < DEC_WARPS; ++w) {
       const float mw = mml[(w * DEC_ROWS + h) * 2];
       const float f = (mw == -INFINITY) ? 0.f : exp2f(mw - mx);
-      a += f * macc[((size_t)w * DEC_ROWS + h) * D + d];
+      const float4 v = *reinterpret_cast<const float4*>(macc + ((size_t)w * DEC_ROWS + h) * D + d);
+      a.x += f * v.x;
+      a.y += f * v.y;
+      a.z += f * v.z;
+      a.w += f * v.w;
       ls += f * mml[(w * DEC_ROWS + h) * 2 + 1];
     }
-    if (n_chunks == 1) {
-      out[((size_t)b * H + h0 + h) * D + d] = __float2bfloat16_rn(a / ls);   // nothing to merge with
+    if (n_chunks == 1) {                                                              // nothing to merge with
+      __nv_bfloat162 lo = __floats2bfloat162_rn(a.x / ls, a.y / ls), hi = __floats2bfloat162_rn(a.z / ls, a.w / ls);
+      *reinterpret_cast<uint2*>(out + ((size_t)b * H + h0 + h) * D + d) =
+          make_uint2(*reinterpret_cast<uint32_t*>(&lo), *reinterpret_cast<uint32_t*>(&hi));
     } else if (cluster_merge) {
-      cacc[idx] = a;
+      *reinterpret_cast<float4*>(cacc + (size_t)h * D + d) = a;
       if (d == 0) {
         cml[2 * h] = mx;
         cml[2 * h + 1] = ls;
       }
     } else {
       float* dst = ws + (((size_t)b * H + h0 + h) * n_chunks + chunk) * DEC_WS_ROW(D);
-      __stcg(dst + d, a);
+      __stcg(reinterpret_cast<float4*>(dst + d), a);
       if (d == 0) {
         __stcg(dst + D, mx);
         __stcg(dst + D + 1, ls);
