@@ -396,34 +396,37 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
     const int hi = min(groups, (chunk + 1) * per);
     for (int idx = chunk * per + threadIdx.x; idx < hi; idx += DEC_WARPS * 32) {
       const int h = idx / (D / 4), d = (idx % (D / 4)) * 4;
+      // every rank's statistics and its four accumulators of this slice are asked for together: one trip
+      // through the cluster's shared memory, not two
       float mc[8], lc[8], mx = -INFINITY;
+      float4 vc[8];
 #pragma unroll
       for (int c = 0; c < 8; ++c) {
         mc[c] = -INFINITY;
         lc[c] = 0.f;
+        vc[c] = make_float4(0.f, 0.f, 0.f, 0.f);
         if (c < n_chunks) {
-          uint32_t ra;
+          uint32_t ra, rb;
           asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(ra) : "r"(my_ml + 8u * h), "r"(c));
+          asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(rb) : "r"(my_acc + 4u * (h * D + d)), "r"(c));
           asm volatile("ld.shared::cluster.v2.f32 {%0, %1}, [%2];" : "=f"(mc[c]), "=f"(lc[c]) : "r"(ra));
-          mx = fmaxf(mx, mc[c]);
+          asm volatile("ld.shared::cluster.v4.f32 {%0, %1, %2, %3}, [%4];"
+                       : "=f"(vc[c].x), "=f"(vc[c].y), "=f"(vc[c].z), "=f"(vc[c].w)
+                       : "r"(rb));
         }
       }
+#pragma unroll
+      for (int c = 0; c < 8; ++c) mx = fmaxf(mx, mc[c]);
       float4 a = make_float4(0.f, 0.f, 0.f, 0.f);
       float l = 0.f;
 #pragma unroll
       for (int c = 0; c < 8; ++c) {
         if (c < n_chunks && mc[c] != -INFINITY) {            // -inf: a chunk that got none of the keys
           const float w = exp2f(mc[c] - mx);
-          uint32_t ra;
-          float4 v;
-          asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(ra) : "r"(my_acc + 4u * (h * D + d)), "r"(c));
-          asm volatile("ld.shared::cluster.v4.f32 {%0, %1, %2, %3}, [%4];"
-                       : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w)
-                       : "r"(ra));
-          a.x += w * v.x;
-          a.y += w * v.y;
-          a.z += w * v.z;
-          a.w += w * v.w;
+          a.x += w * vc[c].x;
+          a.y += w * vc[c].y;
+          a.z += w * vc[c].z;
+          a.w += w * vc[c].w;
           l += w * lc[c];
         }
       }
