@@ -386,3 +386,19 @@ def test_decode_attention_share_count_depends_on_the_shape_only():
                         assert base * 8 <= n_sm and n_pages >= 8 * n
     assert decode_chunks(8, 8, 4, 64) == 4 and decode_chunks(64, 8, 4, 64) == 1 and decode_chunks(1, 8, 4, 64) == 8
     assert decode_chunks(1, 8, 4, 516) == 27 and decode_chunks(1, 8, 4, 132) == 16 and decode_chunks(2, 8, 4, 516) == 13
+
+
+def test_bench_refuses_more_than_one_gpu_and_names_the_missing_reference():
+    """The measurement's contract at its edges: more than one GPU is one line and exit code 2; the reference arm
+    says in one JSON line why it cannot run, and exits 0."""
+    import json
+    import subprocess
+    import sys
+    from pathlib import Path
+
+    bench = str(Path(__file__).resolve().parent.parent / "bench.py")
+    many = subprocess.run([sys.executable, bench, "--gpus", "2"], capture_output=True, text=True, timeout=300)
+    assert many.returncode == 2 and len(many.stdout.strip().splitlines()) == 1
+    ref = subprocess.run([sys.executable, bench, "--impl", "reference"], capture_output=True, text=True, timeout=300)
+    line = json.loads(ref.stdout.strip().splitlines()[-1])
+    assert ref.returncode == 0 and line["impl"] == "reference" and line["unavailable"]
