@@ -129,8 +129,8 @@ struct TcStage {
 
 template <int BN, int MODE, typename TY>
 __device__ __forceinline__ void epilogue_tile_staged(uint32_t acc_addr, const CUtensorMap* map_y, TY* stage,
-                                                     int& chunk_no, int n0, int t0, int T, int quad, int lane,
-                                                     bool first_thread, bool accumulate) {
+                                                     int& chunk_no, int n0, int t0, int split, int T, int quad,
+                                                     int lane, bool first_thread, bool accumulate) {
   static_assert(MODE != 1, "one accumulator");
   constexpr int ROWS = TcStage<TY>::ROWS;
   constexpr int COLS = MODE == 2 ? 64 : 128;
@@ -160,8 +160,8 @@ __device__ __forceinline__ void epilogue_tile_staged(uint32_t acc_addr, const CU
     fence_proxy_async();
     asm volatile("bar.sync 1, 128;" ::: "memory");
     if (first_thread) {
-      if (accumulate) tma_reduce_add_2d(map_y, n0, t0 + c, smem_u32(buf));       // Y += tile (MODE 0, float32)
-      else tma_store_2d(map_y, MODE == 2 ? (n0 >> 1) : n0, t0 + c, smem_u32(buf));
+      if (accumulate) tma_reduce_add_3d(map_y, n0, t0 + c, 0, smem_u32(buf));    // Y += tile (MODE 0, float32)
+      else tma_store_3d(map_y, MODE == 2 ? (n0 >> 1) : n0, t0 + c, split, smem_u32(buf));
     }
     ++chunk_no;
   }
@@ -470,13 +470,15 @@ __host__ __device__ constexpr uint32_t umma_idesc_pair(int n) {   // M = 256 ove
 // a group's units run token tile fastest, then row pair, and group follows group.  The pairs that run side by
 // side then share a few W tiles through L2, and a group's activations (chosen by the host to fit well inside
 // L2) are fetched from memory once and serve every row pair, however many tokens the step has; W is streamed
-// once per group.  With one group this is "token tile fastest" over the whole product.
+// once per group.  With one group this is "token tile fastest" over the whole product.  A short prompt against a
+// narrow matrix has fewer units than the GPU has pairs; its reduction is then split (the units of split 0, then
+// those of split 1, ...), each split writing float32 partials of its own for the kernel that consumes them.
 template <int BN, int MODE, typename TY>
 __global__ void __launch_bounds__(TC_THREADS)
 gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
                     const __grid_constant__ CUtensorMap map_y, TY* __restrict__ Y, int T, int N, int K, long long ldy,
                     int F, int n_stages, int row_pairs, int token_tiles, int n_units, int group_tiles, int staged,
-                    int accumulate) {
+                    int accumulate, int kb_per_split, long long split_stride) {
   extern __shared__ uint8_t smem_raw[];
   constexpr int N_ACC = MODE == 1 ? 2 : 1;
   constexpr int HALF = BN / 2;                                              // tokens this CTA loads
@@ -536,7 +538,12 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
   tc_fence_after();
   const uint32_t tmem_base = *tmem_holder;
 
-  auto unit_coords = [&](int u, int& n0, int& t0) {
+  auto unit_coords = [&](int u, int& n0, int& t0, int& split, int& kb_begin, int& n_kb) {
+    const int per_split = row_pairs * token_tiles;
+    split = u / per_split;
+    u -= split * per_split;
+    kb_begin = split * kb_per_split;
+    n_kb = min(total_kb, kb_begin + kb_per_split) - kb_begin;          // (the host leaves no split empty)
     const int per_group = group_tiles * row_pairs;
     const int g = u / per_group, r = u - g * per_group;
     const int here = min(group_tiles, token_tiles - g * group_tiles);     // the last group may be narrower
@@ -551,34 +558,35 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
       RingPos pos{0, 0};
       bool waited = false, ok = true;
       for (int u = pair; u < n_units && ok; u += n_pairs) {
-        int n0, t0;
-        unit_coords(u, n0, t0);
+        int n0, t0, split, kb_begin, n_kb;
+        unit_coords(u, n0, t0, split, kb_begin, n_kb);
         const int tx = t0 + (int)rank * HALF;                 // this CTA's half of the token tile
         int i = 0;
         if (!waited) {
-          const int pre = total_kb < n_stages ? total_kb : n_stages;
+          const int pre = n_kb < n_stages ? n_kb : n_stages;
           for (int j = 0; j < pre; ++j) {
             const uint32_t stage = base + (uint32_t)j * STAGE_BYTES, bar = leader_full0 + 8u * j;
             mbar_remote_expect_tx(bar, STAGE_BYTES);
-            tma_load_2d_pair(stage, &map_w, j * TC_BK, n0, bar);
-            if (MODE == 1) tma_load_2d_pair(stage + A_BYTES, &map_w, j * TC_BK, n0 + F, bar);
+            tma_load_2d_pair(stage, &map_w, (kb_begin + j) * TC_BK, n0, bar);
+            if (MODE == 1) tma_load_2d_pair(stage + A_BYTES, &map_w, (kb_begin + j) * TC_BK, n0 + F, bar);
           }
           waited = true;                    // (the CTA waited for the kernel before it at its start)
           for (int j = 0; j < pre; ++j)
-            tma_load_2d_pair(base + (uint32_t)j * STAGE_BYTES + N_ACC * A_BYTES, &map_x, j * TC_BK, tx,
+            tma_load_2d_pair(base + (uint32_t)j * STAGE_BYTES + N_ACC * A_BYTES, &map_x, (kb_begin + j) * TC_BK, tx,
                              leader_full0 + 8u * j);
           i = pre;
           if (pre == n_stages) pos = RingPos{0, 1};
           else pos = RingPos{pre, 0};
         }
-        for (; i < total_kb; ++i, pos.next(n_stages)) {
+        for (; i < n_kb; ++i, pos.next(n_stages)) {
           const int s = pos.s;
           if (!mbar_wait_cluster(empty0 + 8u * s, pos.phase ^ 1u)) { tc_report(11); ok = false; break; }
           const uint32_t stage = base + (uint32_t)s * STAGE_BYTES, bar = leader_full0 + 8u * s;
           mbar_remote_expect_tx(bar, STAGE_BYTES);
-          tma_load_2d_pair(stage, &map_w, i * TC_BK, n0, bar);
-          if (MODE == 1) tma_load_2d_pair(stage + A_BYTES, &map_w, i * TC_BK, n0 + F, bar);
-          tma_load_2d_pair(stage + N_ACC * A_BYTES, &map_x, i * TC_BK, tx, bar);
+          const int k = (kb_begin + i) * TC_BK;
+          tma_load_2d_pair(stage, &map_w, k, n0, bar);
+          if (MODE == 1) tma_load_2d_pair(stage + A_BYTES, &map_w, k, n0 + F, bar);
+          tma_load_2d_pair(stage + N_ACC * A_BYTES, &map_x, k, tx, bar);
         }
       }
     }
@@ -591,11 +599,13 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
       const uint32_t desc0 = umma_desc_lo(base);       // stage 0's W tile; every other tile is an offset from it
       bool ok = true;
       for (int u = pair; u < n_units && ok; u += n_pairs, ++j) {
+        int n0, t0, split, kb_begin, n_kb;
+        unit_coords(u, n0, t0, split, kb_begin, n_kb);
         const int buf = j % ACC_BUFS, use = j / ACC_BUFS;
         const uint32_t acc_addr = tmem_base + (uint32_t)buf * ACC_COLS;
         if (!mbar_wait_cluster(acc_empty0 + 8u * buf, (use & 1) ^ 1)) { tc_report(14); ok = false; break; }
         tc_fence_after();
-        for (int i = 0; i < total_kb; ++i, pos.next(n_stages)) {
+        for (int i = 0; i < n_kb; ++i, pos.next(n_stages)) {
           const int s = pos.s;
           if (!mbar_wait_cluster(full0 + 8u * s, pos.phase)) { tc_report(12); ok = false; break; }
           tc_fence_after();
@@ -621,8 +631,8 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
     bool failed = false;
     int j = 0, chunk_no = 0;
     for (int u = pair; u < n_units; u += n_pairs, ++j) {
-      int n0, t0;
-      unit_coords(u, n0, t0);
+      int n0, t0, split, kb_begin, n_kb;
+      unit_coords(u, n0, t0, split, kb_begin, n_kb);
       const int buf = j % ACC_BUFS, use = j / ACC_BUFS;
       if (!failed) {
         bool ok = mbar_wait_cluster(acc_full0 + 8u * buf, use & 1);
@@ -639,10 +649,11 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
       tc_fence_after();
       const uint32_t acc_addr = tmem_base + (uint32_t)buf * ACC_COLS + ((uint32_t)(quad * 32) << 16);
       if (MODE != 1 && staged)
-        epilogue_tile_staged<BN, MODE == 1 ? 0 : MODE, TY>(acc_addr, &map_y, stage_buf, chunk_no, n0, t0, T, quad, lane,
-                                                             threadIdx.x == 64, accumulate != 0);
+        epilogue_tile_staged<BN, MODE == 1 ? 0 : MODE, TY>(acc_addr, &map_y, stage_buf, chunk_no, n0, t0, split, T, quad,
+                                                             lane, threadIdx.x == 64, accumulate != 0);
       else
-        epilogue_tile<BN, MODE, TY>(acc_addr, true, true, Y, n0, t0, T, n_limit, ldy, quad, lane);
+        epilogue_tile<BN, MODE, TY>(acc_addr, true, true, Y + (size_t)split * split_stride, n0, t0, T, n_limit, ldy, quad,
+                                    lane);
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_remote_arrive(leader_acc_empty0 + 8u * buf);
@@ -769,7 +780,7 @@ LLMX_API int llmx_gemm_tc_scaled(const void* X, const void* W, void* Y, int y_dt
 
 template <int BN, int MODE, typename TY>
 static int launch_pair(const CUtensorMap& mw, const CUtensorMap& mx, void* Y, int T, int N, int K, long long ldy,
-                       int F, int accumulate, cudaStream_t stream) {
+                       int F, int accumulate, int n_split, long long split_stride, cudaStream_t stream) {
   constexpr int N_ACC = MODE == 1 ? 2 : 1;
   constexpr size_t STAGE = (size_t)N_ACC * TC_BM * TC_BK * 2 + (size_t)(BN / 2) * TC_BK * 2;
   int stages = (int)((200 * 1024) / STAGE);
@@ -778,8 +789,9 @@ static int launch_pair(const CUtensorMap& mw, const CUtensorMap& mx, void* Y, in
   CUtensorMap my = mw;
   int staged = 0;
   if (MODE != 1 && !((uintptr_t)Y & 15) && !((ldy * (long long)sizeof(TY)) & 15))
-    staged = make_store_map(&my, Y, (int)sizeof(TY), (uint64_t)T, (uint64_t)(MODE == 2 ? F : N), (uint64_t)ldy,
-                            TcStage<TY>::ROWS, MODE == 2 ? 64 : 128) == 0;
+    staged = (n_split == 1 || !((split_stride * (long long)sizeof(TY)) & 15)) &&
+             make_store_map(&my, Y, (int)sizeof(TY), (uint64_t)n_split, (uint64_t)T, (uint64_t)(MODE == 2 ? F : N),
+                            (uint64_t)ldy, (uint64_t)split_stride, TcStage<TY>::ROWS, MODE == 2 ? 64 : 128) == 0;
   if (accumulate && !staged) return LLMX_REFUSED(4);      // Y += ... exists only as a bulk tensor reduction
   const size_t smem = 1024 + (size_t)stages * STAGE + 256 + (MODE != 1 ? TC_STAGE_BYTES : 0);
   auto kernel = gemm_tc_pair_kernel<BN, MODE, TY>;
@@ -791,7 +803,10 @@ static int launch_pair(const CUtensorMap& mw, const CUtensorMap& mx, void* Y, in
   }
   const int rows = MODE == 1 ? F : N;
   const int row_pairs = (rows + 2 * TC_BM - 1) / (2 * TC_BM), token_tiles = (T + BN - 1) / BN;
-  const long long n_units = (long long)row_pairs * token_tiles;
+  const int total_kb = (K + TC_BK - 1) / TC_BK;
+  const int kb_per_split = (total_kb + n_split - 1) / n_split;
+  if ((long long)kb_per_split * (n_split - 1) >= total_kb) return LLMX_REFUSED(1);      // a split without any K
+  const long long n_units = (long long)row_pairs * token_tiles * n_split;
   if (n_units > 0x7fffffff) return LLMX_REFUSED(3);
   // token tiles per group: a group's activations (BN tokens x K each) take at most half of L2, and the groups
   // are of about equal size
@@ -831,17 +846,18 @@ static int launch_pair(const CUtensorMap& mw, const CUtensorMap& mx, void* Y, in
   cfg.gridDim = dim3(2 * pairs);
   cfg.numAttrs = 2;
   cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, mw, mx, my, (TY*)Y, T, N, K, ldy, F, stages, row_pairs, token_tiles,
-                                     (int)n_units, (int)group_tiles, staged, accumulate);
+                                     (int)n_units, (int)group_tiles, staged, accumulate, kb_per_split, split_stride);
   if (e != cudaSuccess) return (int)e;
   return LLMX_LAUNCH_STATUS();
 }
 
-// The CTA-pair kernel: prompt-sized token counts only (T > 128), no split.  Same arguments as llmx_gemm_tc, and
+// The CTA-pair kernel: prompt-sized token counts only (T > 128).  Same arguments as llmx_gemm_tc (n_split > 1:
+// float32 partials [n_split][T,N], split_stride elements apart, mode 0), and
 // `accumulate`: Y += X W^T instead of Y = X W^T (mode 0 and float32 Y only: every element receives one
 // float32 addition, so the result does not depend on the order in which the tiles arrive).
 LLMX_API int llmx_gemm_tc_pair(const void* X, const void* W, void* Y, int y_dtype, int T, int N, int K,
-                               long long ldx, long long ldw, long long ldy, int mode, int accumulate,
-                               cudaStream_t stream) {
+                               long long ldx, long long ldw, long long ldy, int mode, int accumulate, int n_split,
+                               long long split_stride, cudaStream_t stream) {
   if (T <= 0 || N <= 0) return 0;
   if (K <= 0 || (K % 8) || (ldx % 8) || (ldw % 8) || ((uintptr_t)X & 15) || ((uintptr_t)W & 15)) return LLMX_REFUSED(1);
   if (T <= 128 || mode < 0 || mode > 2 || (mode == 1 && (N % 2)) || (mode == 2 && (N % 32))) return LLMX_REFUSED(1);
@@ -850,11 +866,13 @@ LLMX_API int llmx_gemm_tc_pair(const void* X, const void* W, void* Y, int y_dtyp
   CUtensorMap mw, mx;
   if (make_map(&mw, W, (uint64_t)N, (uint64_t)K, (uint64_t)ldw, TC_BM, true)) return LLMX_REFUSED(4);
   if (make_map(&mx, X, (uint64_t)T, (uint64_t)K, (uint64_t)ldx, (uint32_t)(bn / 2), false)) return LLMX_REFUSED(4);
-  if (accumulate && (mode != 0 || y_dtype != LLMX_F32)) return LLMX_REFUSED(1);
-  if (mode == 0 && y_dtype == LLMX_BF16) return launch_pair<256, 0, bf16>(mw, mx, Y, T, N, K, ldy, F, 0, stream);
-  if (mode == 0 && y_dtype == LLMX_F32) return launch_pair<256, 0, float>(mw, mx, Y, T, N, K, ldy, F, accumulate, stream);
-  if (mode == 1 && y_dtype == LLMX_BF16) return launch_pair<128, 1, bf16>(mw, mx, Y, T, N, K, ldy, F, 0, stream);
-  if (mode == 2 && y_dtype == LLMX_BF16) return launch_pair<256, 2, bf16>(mw, mx, Y, T, N, K, ldy, F, 0, stream);
+  if (accumulate && (mode != 0 || y_dtype != LLMX_F32 || n_split != 1)) return LLMX_REFUSED(1);
+  if (n_split < 1 || (n_split > 1 && (mode != 0 || y_dtype != LLMX_F32))) return LLMX_REFUSED(1);
+  if (mode == 0 && y_dtype == LLMX_BF16) return launch_pair<256, 0, bf16>(mw, mx, Y, T, N, K, ldy, F, 0, 1, 0, stream);
+  if (mode == 0 && y_dtype == LLMX_F32)
+    return launch_pair<256, 0, float>(mw, mx, Y, T, N, K, ldy, F, accumulate, n_split, split_stride, stream);
+  if (mode == 1 && y_dtype == LLMX_BF16) return launch_pair<128, 1, bf16>(mw, mx, Y, T, N, K, ldy, F, 0, 1, 0, stream);
+  if (mode == 2 && y_dtype == LLMX_BF16) return launch_pair<256, 2, bf16>(mw, mx, Y, T, N, K, ldy, F, 0, 1, 0, stream);
   return LLMX_REFUSED(2);
 }
 

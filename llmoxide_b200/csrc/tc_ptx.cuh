@@ -193,16 +193,16 @@ __device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.
 // tensor's extent are clipped).  The copies of a thread form groups; wait_read<N> returns once all but the N
 // newest groups have been read out of shared memory (their buffers may be written again), wait_all once every
 // group's bytes are in global memory.
-__device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, int x, int y, uint32_t src) {
-  asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%1, %2}], [%3];"
-               ::"l"(map), "r"(x), "r"(y), "r"(src)
+__device__ __forceinline__ void tma_store_3d(const CUtensorMap* map, int x, int y, int z, uint32_t src) {
+  asm volatile("cp.async.bulk.tensor.3d.global.shared::cta.bulk_group [%0, {%1, %2, %3}], [%4];"
+               ::"l"(map), "r"(x), "r"(y), "r"(z), "r"(src)
                : "memory");
   asm volatile("cp.async.bulk.commit_group;" ::: "memory");
 }
 // The same copy as an addition: global[tile] += shared[tile], element by element in the tensor's type.
-__device__ __forceinline__ void tma_reduce_add_2d(const CUtensorMap* map, int x, int y, uint32_t src) {
-  asm volatile("cp.reduce.async.bulk.tensor.2d.global.shared::cta.add.tile.bulk_group [%0, {%1, %2}], [%3];"
-               ::"l"(map), "r"(x), "r"(y), "r"(src)
+__device__ __forceinline__ void tma_reduce_add_3d(const CUtensorMap* map, int x, int y, int z, uint32_t src) {
+  asm volatile("cp.reduce.async.bulk.tensor.3d.global.shared::cta.add.tile.bulk_group [%0, {%1, %2, %3}], [%4];"
+               ::"l"(map), "r"(x), "r"(y), "r"(z), "r"(src)
                : "memory");
   asm volatile("cp.async.bulk.commit_group;" ::: "memory");
 }
@@ -234,17 +234,20 @@ static EncodeTiledFn encode_fn() {
   return fn;
 }
 
-// A matrix [rows, cols] of 2- or 4-byte elements with row stride `ld` elements, as the target of bulk stores of
-// [box_rows x box_cols] tiles that lie row after row in shared memory (no swizzle).
-static int make_store_map(CUtensorMap* map, void* ptr, int elem_bytes, uint64_t rows, uint64_t cols, uint64_t ld,
-                          uint32_t box_rows, uint32_t box_cols) {
+// `planes` matrices [rows, cols] of 2- or 4-byte elements, `ld` elements from row to row and `plane_stride`
+// from matrix to matrix, as the target of bulk stores of [box_rows x box_cols] tiles of one matrix that lie
+// row after row in shared memory (no swizzle).  A tile that reaches past a matrix's rows or columns is clipped
+// there: it never touches the next matrix.
+static int make_store_map(CUtensorMap* map, void* ptr, int elem_bytes, uint64_t planes, uint64_t rows, uint64_t cols,
+                          uint64_t ld, uint64_t plane_stride, uint32_t box_rows, uint32_t box_cols) {
   EncodeTiledFn fn = encode_fn();
   if (!fn) return 1;
-  cuuint64_t dims[2] = {cols, rows};
-  cuuint64_t strides[1] = {ld * (uint64_t)elem_bytes};
-  cuuint32_t box[2] = {box_cols, box_rows};
-  cuuint32_t elem[2] = {1, 1};
-  CUresult r = fn(map, elem_bytes == 2 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, ptr, dims,
+  if (planes == 1) plane_stride = rows * ld;            // (unused, but it has to be a multiple of 16 bytes)
+  cuuint64_t dims[3] = {cols, rows, planes};
+  cuuint64_t strides[2] = {ld * (uint64_t)elem_bytes, plane_stride * (uint64_t)elem_bytes};
+  cuuint32_t box[3] = {box_cols, box_rows, 1};
+  cuuint32_t elem[3] = {1, 1, 1};
+  CUresult r = fn(map, elem_bytes == 2 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, ptr, dims,
                   strides, box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE,
                   CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   return r == CUDA_SUCCESS ? 0 : 2;

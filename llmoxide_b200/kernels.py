@@ -500,7 +500,7 @@ def gemm_tc(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, n_split: int = 
     with ``gated``, [T,N/2] = silu(gate) * up: ``gated=True`` (or 1) for
     w = [gate rows; up rows], ``gated=2`` for w in blocks of 16 gate rows each
     followed by the 16 up rows of the same features (N/2 a multiple of 16).
-    ``pair`` runs the CTA-pair kernel (prompt-sized T > 128, no split); with
+    ``pair`` runs the CTA-pair kernel (prompt-sized T > 128; it splits too); with
     ``accumulate`` it adds to a float32 ``out`` instead of overwriting it
     (one float32 addition per element, whatever order the tiles finish in).
     ``scale = (sumsq, parts, eps, d)``, for T <= 64: output row t is multiplied
@@ -522,12 +522,12 @@ def gemm_tc(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, n_split: int = 
         ldy, stride = N, 0
     assert pair or not accumulate
     if pair:
-        assert n_split == 1 and T > 128 and scale is None
+        assert T > 128 and scale is None and not (accumulate and n_split > 1)
         f = _fn("gemm_tc", "llmx_gemm_tc_pair",
                 [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_longlong, c_longlong, c_longlong, c_int,
-                 c_int, c_void_p])
+                 c_int, c_int, c_longlong, c_void_p])
         _check(f(_ptr(x), _ptr(w), _ptr(out), _tag(out), T, N, K, x.stride(0), w.stride(0), ldy,
-                 gated, int(accumulate), _stream()), "gemm_tc_pair")
+                 gated, int(accumulate), n_split, stride, _stream()), "gemm_tc_pair")
         return
     if scale is None:
         f = _fn("gemm_tc", "llmx_gemm_tc",

@@ -4,8 +4,8 @@ takes at a given number of tokens.
 Decode is bound by reading the weights once, so a matrix with few 128-row
 tiles splits its reduction over K until about one CTA per SM streams; the
 float32 partials are summed by the kernel that consumes them (the residual
-add + norm, or the gated activation).  Prefill has tiles enough and does not
-split."""
+add + norm, or the gated activation).  A long prompt has tiles enough and does
+not split; a short one against a narrow matrix does (``choose_prompt_splits``)."""
 
 from __future__ import annotations
 
@@ -50,16 +50,16 @@ def choose_splits(n_rows: int, k: int, n_tokens: int, n_sm: int = 148, max_split
 
 
 def choose_prompt_splits(n_rows: int, k: int, n_tokens: int, n_sm: int = 148, max_splits: int = 8) -> int:
-    """The same question for a prompt-sized step (more than 64 tokens).  Whole tiles of 256 rows x 256 tokens
-    on CTA pairs are best when there are enough of them to occupy most pairs.  A short prompt (or a chunk of
-    one) against a narrow matrix leaves most of the GPU idle (512 tokens x 4096 rows: 32 tiles for 74 pairs);
-    then single CTAs take tiles of 128 rows and the reduction is split until about one unit per SM streams, each
-    split at least 8 blocks of K long.  The float32 partials are summed by the kernel that consumes them."""
-    pair_units = -(-n_rows // 256) * -(-n_tokens // 256)
-    if pair_units * 5 >= (n_sm // 2) * 4:
+    """The same question for a prompt-sized step (more than 128 tokens), which runs on CTA pairs in units of
+    256 rows x 256 tokens.  Whole units are best when there are enough of them to occupy most pairs.  A short
+    prompt (or a chunk of one) against a narrow matrix leaves most of the GPU idle (512 tokens x 4096 rows:
+    32 units for 74 pairs); then the reduction is split until about one unit per pair runs, each split at
+    least 8 blocks of K long.  The float32 partials are summed by the kernel that consumes them."""
+    pairs = max(1, n_sm // 2)
+    units = -(-n_rows // 256) * -(-n_tokens // 256)
+    if units * 5 >= pairs * 4:
         return 1
-    units = -(-n_rows // TILE_ROWS) * -(-n_tokens // 256)
-    return max(1, min(max_splits, n_sm // units, ((k + 63) // 64) // 8))
+    return max(1, min(max_splits, pairs // units, ((k + 63) // 64) // 8))
 
 
 class TensorCoreLinear:
@@ -93,7 +93,7 @@ class TensorCoreLinear:
                  choose_prompt_splits(self.N, self.K, T, self.n_sm))
         if s > 1:
             out = scratch((s, T, self.N), torch.float32, x.device, "split partials of a matrix product")
-            kernels.gemm_tc(x, self.weight, out, n_split=s, scale=scale)
+            kernels.gemm_tc(x, self.weight, out, n_split=s, scale=scale, pair=T > PAIR_MIN_TOKENS)
             return out
         out = scratch((T, self.N), out_dtype, x.device, "output of a matrix product")
         kernels.gemm_tc(x, self.weight, out, pair=T > PAIR_MIN_TOKENS, scale=scale)

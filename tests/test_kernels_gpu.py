@@ -450,6 +450,12 @@ def test_gemm_tc_pair(T, N, K):
     out16 = torch.empty(T, N, dtype=torch.bfloat16, device=DEV)
     kernels.gemm_tc(xd, wd, out16, pair=True)
     assert rel(out16, want) < 6e-3
+    for n_split in (2, 3):        # the reduction cut into splits: float32 partials, one plane each
+        if K >= 128 * n_split:
+            parts = torch.full((n_split, T, N), float("nan"), dtype=torch.float32, device=DEV)
+            kernels.gemm_tc(xd, wd, parts, n_split=n_split, pair=True)
+            assert kernels.gemm_tc_status() == 0
+            assert rel(parts.sum(0), want) < 1e-5, n_split
     if N % 4 == 0:        # Y += X W^T: one float32 addition per element, the same bits as adding the product
         base = torch.randn(T, N, generator=g).to(DEV)
         acc = base.clone()
