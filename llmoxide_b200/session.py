@@ -11,6 +11,7 @@ from typing import Callable, Optional, Sequence
 
 import torch
 
+from . import kernels
 from .engine.engine import Engine, LoadOptions
 from .engine.generate import GenerationLoop, Limits, Outcome, Request
 from .sampling.params import Sampling
@@ -25,6 +26,10 @@ class Session:
         self.default_sampling = Sampling(**engine.spec.default_sampling)
         self.loop = GenerationLoop(engine, self.limits, self.default_sampling, engine.spec.stop_ids)
         self._resident: Optional[int] = None   # slot of the sequence that forward() extends
+        # A session generates, so it samples: the sampling kernels are built and loaded now, not in the middle of
+        # the first request (trace replay, which samples nothing, drives the engine without a session).
+        if engine.device.type == "cuda":
+            kernels.preload(["sampling"])
 
     # ---- loading ---------------------------------------------------------------
 
