@@ -691,7 +691,8 @@ static int launch(const CUtensorMap& mw, const CUtensorMap& mx, void* Y, int T, 
   // Decode tiles (few tokens) stream weights: two CTAs per SM, so that more loads are in flight per SM.
   // Prompt tiles take the whole SM.
   const int ctas_per_sm = BN <= 64 ? 2 : 1;
-  const size_t budget = BN <= 64 ? 100 * 1024 : 200 * 1024;
+  // (108 KB: six stages of a 16-token tile; two such CTAs and the driver's 1 KB each still fit the SM's 228 KB)
+  const size_t budget = BN <= 64 ? 108 * 1024 : 200 * 1024;
   int stages = (int)(budget / STAGE);
   if (stages > 12) stages = 12;
   if (stages < 2) stages = 2;
