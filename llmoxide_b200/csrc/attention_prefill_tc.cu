@@ -11,17 +11,21 @@
 //   warp 0     TMA: the query tile once, then per key tile K and V, each as
 //              [2 panels of 64 dims][64 keys][128 bytes], 128-byte swizzle
 //   warp 1     one lane issues  S = Q K^T  (both operands K-major) into one of
-//              two S buffers in tensor memory, and  O += P V  (P K-major from
-//              shared memory, V MN-major straight from its cache layout)
+//              two S buffers in tensor memory, and  O += P V  (P from tensor
+//              memory, V MN-major straight from its cache layout)
 //   warps 2-5  softmax, one thread per query row: tcgen05.ld the row of S,
-//              mask, running maximum, exp2, row sum, P as bfloat16 into shared
-//              memory in the MMA's swizzled layout.  O stays in tensor memory;
+//              mask, running maximum, exp2, row sum, P as bfloat16 back into
+//              tensor memory over the scores it came from (tcgen05.st; two keys
+//              to a column), where the MMA takes it as its A operand: P never
+//              passes through shared memory, whose bandwidth is what a key tile
+//              costs most of (Q 32 KB, K and V 16 KB each, read by the MMAs and
+//              written by the copies).  O stays in tensor memory;
 //              it is rescaled (load, multiply, store) only when a row's maximum
 //              has grown by more than 2^8 since the maximum its exponentials
 //              were taken against, which is rare after the first tiles.
 // S of tile j+1 is issued before P V of tile j, so the tensor core works on the
 // next scores while the softmax warps work on these.  A CTA takes half of an
-// SM (112 KB of shared memory, 256 columns of tensor memory, 168 registers),
+// SM (96 KB of shared memory, 256 columns of tensor memory, 168 registers),
 // so two CTAs share it: while one's softmax warps wait for a tensor-memory load
 // or the special-function unit, the other's run.  Every mbarrier wait is
 // bounded; a wait that runs out sets the status word and the CTA winds down.
@@ -31,11 +35,11 @@
 #define AT_KEYS 64         // keys per tile = MMA N of S = one cache page
 #define AT_D 128
 #define AT_THREADS 192        // warp 0 TMA, warp 1 MMA, warps 2..5 softmax
-#define AT_PANEL (128 * 128)   // bytes of one [128 rows x 64 elements] panel (Q, P)
+#define AT_PANEL (128 * 128)   // bytes of one [128 rows x 64 elements] panel of Q
 #define AT_TILE (2 * AT_PANEL) // bytes of the [128 x 128] query tile
 #define AT_KPANEL (AT_KEYS * 128)   // bytes of one [64 keys x 64 dims] panel of K or V
 #define AT_KTILE (2 * AT_KPANEL)    // bytes of a [64 keys x 128 dims] tile of K or V
-#define AT_SMEM (AT_TILE + 4 * AT_KTILE + AT_PANEL + 16 * 8 + 64)   // Q, K[2], V[2], P, barriers
+#define AT_SMEM (AT_TILE + 4 * AT_KTILE + 16 * 8 + 64)   // Q, K[2], V[2], barriers
 
 __device__ int g_at_status = 0;    // 0, or which bounded wait ran out (1..10 below), 20: shared memory not 1024-byte aligned
 __device__ __forceinline__ void at_report(int code) {
@@ -74,7 +78,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
   const int n_tiles = tile_last - tile_first + 1;
   const int* pages = block_table + (size_t)b * table_width;
 
-  // shared memory: Q (32 KB), K[2], V[2] (16 KB each), P (16 KB), then barriers
+  // shared memory: Q (32 KB), K[2], V[2] (16 KB each), then barriers
   // Half an SM leaves no room for alignment slack: the dynamic shared memory must start on a
   // 1024-byte boundary (it does when the kernel has no static shared memory); otherwise nothing runs.
   const uint32_t base = smem_u32(smem_raw);
@@ -83,10 +87,9 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
     return;
   }
   uint8_t* base_ptr = smem_raw;
-  const uint32_t sQ = base, sK0 = base + AT_TILE, sV0 = sK0 + 2 * AT_KTILE, sP = sV0 + 2 * AT_KTILE;
+  const uint32_t sQ = base, sK0 = base + AT_TILE, sV0 = sK0 + 2 * AT_KTILE;
   uint8_t* pV0 = base_ptr + AT_TILE + 2 * AT_KTILE;
-  uint8_t* pP = pV0 + 2 * AT_KTILE;
-  uint64_t* bars = reinterpret_cast<uint64_t*>(pP + AT_PANEL);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(pV0 + 2 * AT_KTILE);
   const uint32_t bar0 = smem_u32(bars);
   const uint32_t q_full = bar0, k_full0 = bar0 + 8, v_full0 = bar0 + 24, k_empty0 = bar0 + 40, v_empty0 = bar0 + 56;
   const uint32_t s_full0 = bar0 + 72, p_ready = bar0 + 88, pv_done = bar0 + 96;     // one phase per key tile
@@ -154,9 +157,8 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
         const uint32_t v = sV0 + (uint32_t)st * AT_KTILE;
 #pragma unroll
         for (int ks = 0; ks < AT_KEYS / 16; ++ks) {
-          const uint64_t da = umma_desc(sP + (uint32_t)ks * 32u);
           const uint64_t db = umma_desc_mn(v + (uint32_t)ks * 2048u, AT_KPANEL, 1024u);
-          umma_bf16(tO, da, db, idesc_o, (j > 0 || ks > 0) ? 1u : 0u);
+          umma_bf16_ts(tO, tS0 + (uint32_t)st * AT_KEYS + (uint32_t)ks * 8u, db, idesc_o, (j > 0 || ks > 0) ? 1u : 0u);
         }
         umma_commit(v_empty0 + 8u * st);
         umma_commit(pv_done);
@@ -246,33 +248,27 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
         packed[e >> 1] = *reinterpret_cast<uint32_t*>(&hh);
       }
       l += (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
-      // The P buffer, and O, belong to P V of the tile before until it is done.
-      if (j >= 1) {
+      // O belongs to P V of the tile before until it is done.  It is rescaled only when some row of the warp
+      // needs it; otherwise P goes out first and the wait for that P V (every tile's is waited for, so that the
+      // barrier's phases are followed one by one) comes after, off the path to the next P V.
+      const bool rescale = j >= 1 && __any_sync(0xffffffffu, alpha != 1.0f);
+      if (rescale) {
         ok = mbar_wait(pv_done, (j - 1) & 1);
         if (!ok && lane == 0) at_report(8);
         ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
         if (!ok) break;
-        // O is rescaled only when some row of the warp needs it.
-        if (__any_sync(0xffffffffu, alpha != 1.0f)) {
-          tc_fence_after();
+        tc_fence_after();
 #pragma unroll 1
-          for (int c = 0; c < AT_D; c += 32) {
-            float o[32];
-            tmem_ld32(tO + lane_off + (uint32_t)c, o);
+        for (int c = 0; c < AT_D; c += 32) {
+          float o[32];
+          tmem_ld32(tO + lane_off + (uint32_t)c, o);
 #pragma unroll
-            for (int e = 0; e < 32; ++e) o[e] *= alpha;
-            tmem_st32(tO + lane_off + (uint32_t)c, o);
-          }
+          for (int e = 0; e < 32; ++e) o[e] *= alpha;
+          tmem_st32(tO + lane_off + (uint32_t)c, o);
         }
       }
-      // P as bfloat16 in the MMA's layout: [row][128 bytes], 16-byte chunk index XOR (row % 8)
-      {
-        uint8_t* prow = pP + row * 128;
-#pragma unroll
-        for (int c8 = 0; c8 < AT_KEYS / 8; ++c8)
-          *reinterpret_cast<uint4*>(prow + ((c8 ^ (row & 7)) << 4)) =
-              make_uint4(packed[4 * c8], packed[4 * c8 + 1], packed[4 * c8 + 2], packed[4 * c8 + 3]);
-      }
+      // P as bfloat16 over the scores it came from: this row's lane, two keys to a column
+      tmem_st32_u32(tS, packed);
       // the last tile: rows of V past the newest key were never written (or belong to another owner of the page)
       if (key0 + AT_KEYS - 1 > pos_hi) {
         ok = mbar_wait(v_full0 + 8u * st, (j >> 1) & 1);
@@ -290,6 +286,11 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(p_ready);
+      if (j >= 1 && !rescale) {
+        ok = mbar_wait(pv_done, (j - 1) & 1);
+        if (!ok && lane == 0) at_report(8);
+        ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+      }
     }
     // ---------------- normalise and store ----------------
     if (ok) {
