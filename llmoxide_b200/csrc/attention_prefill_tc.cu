@@ -91,8 +91,11 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
   uint8_t* pV0 = base_ptr + AT_TILE + 2 * AT_KTILE;
   uint64_t* bars = reinterpret_cast<uint64_t*>(pV0 + 2 * AT_KTILE);
   const uint32_t bar0 = smem_u32(bars);
-  const uint32_t q_full = bar0, k_full0 = bar0 + 8, v_full0 = bar0 + 24, k_empty0 = bar0 + 40, v_empty0 = bar0 + 56;
-  const uint32_t s_full0 = bar0 + 72, p_ready = bar0 + 88, pv_done = bar0 + 96;     // one phase per key tile
+  // s_full[st]: the scores of a tile are complete, so its K stage is free as well; pv_done[st]: P V of a tile is
+  // complete, so its V stage is free, O may be rescaled and (for the last tile) read.  One commit each per tile:
+  // the thread that issues the MMAs is what a CTA waits for most, and a commit costs it as much as an MMA.
+  const uint32_t q_full = bar0, k_full0 = bar0 + 8, v_full0 = bar0 + 24;
+  const uint32_t s_full0 = bar0 + 40, pv_done0 = bar0 + 56, p_ready = bar0 + 72;
   uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(bars + 15);
 
   if (threadIdx.x == 0) {
@@ -100,12 +103,10 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
     for (int i = 0; i < 2; ++i) {
       mbar_init(k_full0 + 8u * i, 1);
       mbar_init(v_full0 + 8u * i, 1);
-      mbar_init(k_empty0 + 8u * i, 1);
-      mbar_init(v_empty0 + 8u * i, 1);
       mbar_init(s_full0 + 8u * i, 1);
+      mbar_init(pv_done0 + 8u * i, 1);
     }
     mbar_init(p_ready, 4);                   // one arrival per softmax warp
-    mbar_init(pv_done, 1);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("prefetch.tensormap [%0];" ::"l"(&map_q) : "memory");
     asm volatile("prefetch.tensormap [%0];" ::"l"(&map_k) : "memory");
@@ -133,11 +134,11 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
         const int st = j & 1;
         const uint32_t parity = ((j >> 1) & 1) ^ 1;
         const int row = (pages[tile_first + j] * G + g) * LLMX_PAGE;      // the tile is one page of one kv head
-        if (!mbar_wait(k_empty0 + 8u * st, parity)) { at_report(1); break; }
+        if (!mbar_wait(s_full0 + 8u * st, parity)) { at_report(1); break; }
         mbar_expect_tx(k_full0 + 8u * st, AT_KTILE);
         tma_load_2d(sK0 + (uint32_t)st * AT_KTILE, &map_k, 0, row, k_full0 + 8u * st);
         tma_load_2d(sK0 + (uint32_t)st * AT_KTILE + AT_KPANEL, &map_k, 64, row, k_full0 + 8u * st);
-        if (!mbar_wait(v_empty0 + 8u * st, parity)) { at_report(2); break; }
+        if (!mbar_wait(pv_done0 + 8u * st, parity)) { at_report(2); break; }
         mbar_expect_tx(v_full0 + 8u * st, AT_KTILE);
         tma_load_2d(sV0 + (uint32_t)st * AT_KTILE, &map_v, 0, row, v_full0 + 8u * st);
         tma_load_2d(sV0 + (uint32_t)st * AT_KTILE + AT_KPANEL, &map_v, 64, row, v_full0 + 8u * st);
@@ -149,33 +150,31 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
       constexpr uint32_t idesc_s = at_idesc(false, AT_KEYS), idesc_o = at_idesc(true, AT_D);
       bool ok = mbar_wait(q_full, 0);
       if (!ok) at_report(3);
+      const uint64_t q0 = umma_desc(sQ);
       auto issue_pv = [&](int j) {       // O += P_j V_j
         const int st = j & 1;
         if (!mbar_wait(p_ready, j & 1)) { at_report(5); return false; }
         if (!mbar_wait(v_full0 + 8u * st, (j >> 1) & 1)) { at_report(6); return false; }
         tc_fence_after();
-        const uint32_t v = sV0 + (uint32_t)st * AT_KTILE;
+        const uint64_t v0 = umma_desc_mn(sV0 + (uint32_t)st * AT_KTILE, AT_KPANEL, 1024u);
 #pragma unroll
-        for (int ks = 0; ks < AT_KEYS / 16; ++ks) {
-          const uint64_t db = umma_desc_mn(v + (uint32_t)ks * 2048u, AT_KPANEL, 1024u);
-          umma_bf16_ts(tO, tS0 + (uint32_t)st * AT_KEYS + (uint32_t)ks * 8u, db, idesc_o, (j > 0 || ks > 0) ? 1u : 0u);
-        }
-        umma_commit(v_empty0 + 8u * st);
-        umma_commit(pv_done);
+        for (int ks = 0; ks < AT_KEYS / 16; ++ks)      // 16 keys on: 2048 bytes, 128 in the descriptor's units
+          umma_bf16_ts(tO, tS0 + (uint32_t)st * AT_KEYS + (uint32_t)ks * 8u, v0 + (uint64_t)(ks * 128), idesc_o,
+                       (j > 0 || ks > 0) ? 1u : 0u);
+        umma_commit(pv_done0 + 8u * st);
         return true;
       };
       for (int j = 0; j < n_tiles && ok; ++j) {
         const int st = j & 1;
         if (!mbar_wait(k_full0 + 8u * st, (j >> 1) & 1)) { at_report(4); ok = false; break; }
         tc_fence_after();
-        const uint32_t k = sK0 + (uint32_t)st * AT_KTILE;
+        const uint64_t k0 = umma_desc(sK0 + (uint32_t)st * AT_KTILE);
 #pragma unroll
-        for (int ks = 0; ks < AT_D / 16; ++ks) {
-          const uint32_t qoff = (uint32_t)(ks >> 2) * AT_PANEL + (uint32_t)(ks & 3) * 32u;
-          const uint32_t koff = (uint32_t)(ks >> 2) * AT_KPANEL + (uint32_t)(ks & 3) * 32u;
-          umma_bf16(tS0 + (uint32_t)st * AT_KEYS, umma_desc(sQ + qoff), umma_desc(k + koff), idesc_s, ks > 0 ? 1u : 0u);
+        for (int ks = 0; ks < AT_D / 16; ++ks) {     // (offsets in the descriptors' 16-byte units)
+          const uint32_t qoff = ((uint32_t)(ks >> 2) * AT_PANEL + (uint32_t)(ks & 3) * 32u) >> 4;
+          const uint32_t koff = ((uint32_t)(ks >> 2) * AT_KPANEL + (uint32_t)(ks & 3) * 32u) >> 4;
+          umma_bf16(tS0 + (uint32_t)st * AT_KEYS, q0 + qoff, k0 + koff, idesc_s, ks > 0 ? 1u : 0u);
         }
-        umma_commit(k_empty0 + 8u * st);
         if (!(j == 0 && llmx_withhold))     // (tests: the first tile's scores are never announced)
           umma_commit(s_full0 + 8u * st);
         if (j >= 1) ok = issue_pv(j - 1);
@@ -253,7 +252,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
       // barrier's phases are followed one by one) comes after, off the path to the next P V.
       const bool rescale = j >= 1 && __any_sync(0xffffffffu, alpha != 1.0f);
       if (rescale) {
-        ok = mbar_wait(pv_done, (j - 1) & 1);
+        ok = mbar_wait(pv_done0 + 8u * ((j - 1) & 1), ((j - 1) >> 1) & 1);
         if (!ok && lane == 0) at_report(8);
         ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
         if (!ok) break;
@@ -287,14 +286,14 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
       __syncwarp();
       if (lane == 0) mbar_arrive(p_ready);
       if (j >= 1 && !rescale) {
-        ok = mbar_wait(pv_done, (j - 1) & 1);
+        ok = mbar_wait(pv_done0 + 8u * ((j - 1) & 1), ((j - 1) >> 1) & 1);
         if (!ok && lane == 0) at_report(8);
         ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
       }
     }
     // ---------------- normalise and store ----------------
     if (ok) {
-      ok = mbar_wait(pv_done, (n_tiles - 1) & 1);
+      ok = mbar_wait(pv_done0 + 8u * ((n_tiles - 1) & 1), ((n_tiles - 1) >> 1) & 1);
       if (!ok && lane == 0) at_report(10);
       ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
     }

@@ -147,7 +147,7 @@ def test_prompt_attention_whose_wait_runs_out_is_reported():
         torch.cuda.synchronize()
         with pytest.raises(KernelError, match="attention_prefill_tc"):
             kernels.check_status()
-        assert kernels.attention_prefill_tc_status() in (2, 5, 7)
+        assert kernels.attention_prefill_tc_status() in (1, 2, 5, 7)     # whichever role's wait ran out first
     finally:
         _reset("attention_prefill_tc")
     kernels.attention_prefill_tc(*args)
