@@ -42,11 +42,19 @@ def _tag(t: torch.Tensor) -> int:
 
 
 def _ptr(t):
-    return c_void_p(0) if t is None else c_void_p(t.data_ptr())
+    """A tensor's address as the plain integer (None for no tensor) that a c_void_p argument converts itself."""
+    return None if t is None else t.data_ptr()
+
+
+# The current stream's handle without building a torch.cuda.Stream object for every launch (a prompt step of a
+# few tokens launches some 300 kernels and is bound by the host).
+_raw_stream = getattr(torch._C, "_cuda_getCurrentRawStream", None)
 
 
 def _stream():
-    return c_void_p(torch.cuda.current_stream().cuda_stream)
+    if _raw_stream is not None:
+        return _raw_stream(torch.cuda.current_device())
+    return torch.cuda.current_stream().cuda_stream
 
 
 launch_count = 0  # kernels of this package launched (or replayed from a graph) so far

@@ -9,6 +9,8 @@ not split; a short one against a narrow matrix does (``choose_prompt_splits``)."
 
 from __future__ import annotations
 
+from functools import lru_cache
+
 import torch
 
 from .. import kernels
@@ -21,6 +23,7 @@ MIN_KBLOCKS_PER_SPLIT = 4     # 64-element blocks of K per split, at least
 PAIR_MIN_TOKENS = 128         # above this, CTA pairs (tcgen05 cta_group::2) share each token tile
 
 
+@lru_cache(maxsize=4096)
 def choose_splits(n_rows: int, k: int, n_tokens: int, n_sm: int = 148, max_splits: int = 16) -> int:
     """How many ways to split the reduction over K at ``n_tokens`` tokens, from
     a small time model of the streaming kernel (microseconds): n_sm * CTAS_PER_SM
@@ -49,6 +52,7 @@ def choose_splits(n_rows: int, k: int, n_tokens: int, n_sm: int = 148, max_split
     return best
 
 
+@lru_cache(maxsize=4096)
 def choose_prompt_splits(n_rows: int, k: int, n_tokens: int, n_sm: int = 148, max_splits: int = 8) -> int:
     """The same question for a prompt-sized step (more than 128 tokens), which runs on CTA pairs in units of
     256 rows x 256 tokens.  Whole units are best when there are enough of them to occupy most pairs.  A short
