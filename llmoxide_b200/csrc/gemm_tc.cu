@@ -688,11 +688,19 @@ static int launch(const CUtensorMap& mw, const CUtensorMap& mx, void* Y, int T, 
   constexpr size_t STAGE = (size_t)N_ACC * TC_BM * TC_BK * 2 + (size_t)BN * TC_BK * 2;
   const int total_kb = (K + TC_BK - 1) / TC_BK;
   const int per_split = (total_kb + n_split - 1) / n_split;
+  const int rows = MODE == 1 ? F : N;   // MODE 2 walks all 2F interleaved rows
+  const int row_tiles = (rows + TC_BM - 1) / TC_BM, token_tiles = (T + BN - 1) / BN;
+  const long long n_units = (long long)row_tiles * token_tiles * n_split;
+  if (n_units > 0x7fffffff) return LLMX_REFUSED(3);
   // Decode tiles (few tokens) stream weights: two CTAs per SM, so that more loads are in flight per SM.
-  // Prompt tiles take the whole SM.
-  const int ctas_per_sm = BN <= 64 ? 2 : 1;
-  // (108 KB: six stages of a 16-token tile; two such CTAs and the driver's 1 KB each still fit the SM's 228 KB)
-  const size_t budget = BN <= 64 ? 108 * 1024 : 200 * 1024;
+  // 128-token tiles do the same when there are more units than SMs (gate|up: 192 units are then resident at
+  // once instead of running a second round on a third of the SMs; two accumulator sets of 128 columns per
+  // CTA, so the two CTAs fill tensor memory; not MODE 1, whose CTA takes all of it); with a CTA per SM or
+  // fewer they keep the deep ring.  Wider tiles take the whole SM.
+  const int ctas_per_sm = BN <= 64 || (BN == 128 && MODE != 1 && n_units > sm_count()) ? 2 : 1;
+  // (108 KB: six stages of a 16-token tile, three of a 128-token tile; two such CTAs and the driver's 1 KB
+  // each still fit the SM's 228 KB)
+  const size_t budget = ctas_per_sm == 2 ? 108 * 1024 : 200 * 1024;
   int stages = (int)(budget / STAGE);
   if (stages > 12) stages = 12;
   if (stages < 2) stages = 2;
@@ -705,10 +713,6 @@ static int launch(const CUtensorMap& mw, const CUtensorMap& mx, void* Y, int T, 
     if (e != cudaSuccess) return (int)e;
     attr_set = true;
   }
-  const int rows = MODE == 1 ? F : N;   // MODE 2 walks all 2F interleaved rows
-  const int row_tiles = (rows + TC_BM - 1) / TC_BM, token_tiles = (T + BN - 1) / BN;
-  const long long n_units = (long long)row_tiles * token_tiles * n_split;
-  if (n_units > 0x7fffffff) return LLMX_REFUSED(3);
   const int max_ctas = sm_count() * ctas_per_sm;
   const int grid = n_units < max_ctas ? (int)n_units : max_ctas;
   launch_pdl(kernel, dim3(grid), dim3(TC_THREADS), smem, stream, mw, mx, (TY*)Y, T, N, K, ldy, per_split,
