@@ -40,7 +40,9 @@ class LoadOptions:
     ``max_batch``: most sequences alive at once (slots).
     ``max_step_tokens``: most tokens one step may bring.
     ``overlap_prompt_kernels``: let the kernels of a prompt step start before the kernel before them has
-    ended, as those of decode steps always do (off by default; the rule is stated in ``Engine._step``)."""
+    ended, as those of decode steps always do (off by default; the rule is stated in ``Engine._step``).
+    ``graph_prompt_tokens``: prompt steps of up to this many tokens are bound by their ~300 launches, not by
+    the GPU; one whose shape comes back is captured as a CUDA graph like a decode step (0: never)."""
 
     dtype: str = "bfloat16"
     max_tokens: int = 16384
@@ -50,6 +52,7 @@ class LoadOptions:
     tensor_cores: bool = True
     cuda_graphs: bool = True
     overlap_prompt_kernels: bool = False
+    graph_prompt_tokens: int = 256
 
 
 class Engine:
@@ -78,6 +81,8 @@ class Engine:
         self.host_seconds = 0.0
         self._sampler = None
         self._graphs: dict = {}
+        self._prompt_graphs: dict = {}
+        self._prompt_shapes: dict = {}      # prompt-step shape -> times seen
         self._graph_pool = torch.cuda.graph_pool_handle() if options.cuda_graphs else None
 
     # ---- loading -------------------------------------------------------------
@@ -142,23 +147,78 @@ class Engine:
         ctx.probe = probe
         if feed_tokens is not None:
             ctx.tokens.copy_(feed_tokens)      # on the stream, after the step buffer's copy
-        replayed = bool(self.options.cuda_graphs and ctx.is_decode and self.model.graph_safe and probe is None)
-        if replayed:
+        graphs = bool(self.options.cuda_graphs and self.model.graph_safe and probe is None)
+        replayed = graphs and (ctx.is_decode or self._prompt_shape_came_back(lay, ctx))
+        if replayed and ctx.is_decode:
             logits = self._graphed_forward(lay, ctx, [slot for slot, _ in entries])
+        elif replayed:
+            logits = self._graphed_prompt(lay, ctx)
+            replayed = logits is not None
+            if not replayed:
+                logits = self._ordered_forward(ctx)
         elif ctx.is_decode or self.options.overlap_prompt_kernels:
             logits = self.model.forward(ctx, self.cache)
         else:
-            # Rule: the kernels of a prompt step run fully ordered.  They are long, so overlapping a kernel's
-            # start with the end of the one before gains nothing measurable, and kernels that hold tensor
-            # memory and whole SMs must not wait on one another for resources.
-            kernels.set_overlap(False)
-            try:
-                logits = self.model.forward(ctx, self.cache)
-            finally:
-                kernels.set_overlap(True)
+            logits = self._ordered_forward(ctx)
         self.cache.alloc.commit_many([slot for slot, _ in entries], [len(toks) for _, toks in entries])
         self.n_steps += 1
         return logits, replayed
+
+    def _ordered_forward(self, ctx):
+        """Rule: the kernels of a prompt step run fully ordered.  They are long, so overlapping a kernel's
+        start with the end of the one before gains nothing measurable, and kernels that hold tensor
+        memory and whole SMs must not wait on one another for resources."""
+        kernels.set_overlap(False)
+        try:
+            return self.model.forward(ctx, self.cache)
+        finally:
+            kernels.set_overlap(True)
+
+    def _prompt_key(self, lay, ctx):
+        # what the launches of a prompt step depend on besides the step buffer's contents
+        return (lay.key(), ctx.max_new, ctx.max_len, self.buffers.dev.data_ptr())
+
+    def _prompt_shape_came_back(self, lay, ctx) -> bool:
+        """Whether this prompt step is short enough to be bound by its launches and has a shape that ran
+        before (a capture costs about two steps, so a shape is captured when it is seen the second time)."""
+        if ctx.n_tokens > self.options.graph_prompt_tokens or self.options.overlap_prompt_kernels:
+            return False
+        key = self._prompt_key(lay, ctx)
+        seen = self._prompt_shapes.pop(key, 0) + 1
+        if len(self._prompt_shapes) >= 1024:
+            self._prompt_shapes.pop(next(iter(self._prompt_shapes)))
+        self._prompt_shapes[key] = seen          # (most recently seen last)
+        return seen >= 2
+
+    def _graphed_prompt(self, lay, ctx):
+        """The forward of a short prompt step as a replayed graph of fully ordered kernels, or None if it
+        cannot be captured.  The shape ran eagerly before (every library and kernel it needs is loaded), so
+        nothing runs at capture and state of fixed size advances once, at the replay."""
+        key = self._prompt_key(lay, ctx)
+        entry = self._prompt_graphs.pop(key, None)
+        if entry is None:
+            torch.cuda.current_stream().synchronize()
+            before = kernels.launch_count
+            graph = torch.cuda.CUDAGraph()
+            kernels.set_overlap(False)
+            try:
+                with torch.cuda.graph(graph, pool=self._graph_pool):
+                    logits = self.model.forward(ctx, self.cache)
+            except RuntimeError as e:
+                print(f"[llmoxide_b200] prompt steps are not captured as CUDA graphs: {e}", file=sys.stderr)
+                self.options.graph_prompt_tokens = 0
+                torch.cuda.synchronize()
+                return None
+            finally:
+                kernels.set_overlap(True)
+            entry = (graph, logits, kernels.launch_count - before)
+            if len(self._prompt_graphs) >= 16:
+                self._prompt_graphs.pop(next(iter(self._prompt_graphs)))
+        self._prompt_graphs[key] = entry          # (most recently used last)
+        graph, logits, n_kernels = entry
+        graph.replay()
+        kernels.launch_count += n_kernels
+        return logits
 
     def _prepare(self, entries, want):
         """The step's plan, made by the C++ runtime (csrc/host_runtime.cpp, llmx_plan_step): every check that

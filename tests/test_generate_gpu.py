@@ -171,6 +171,52 @@ def test_libraries_are_resident_before_the_first_step_and_prompts_may_overlap(fo
     assert outs[0] == outs[1]
 
 
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_a_prompt_shape_that_comes_back_is_replayed_as_a_graph(folders, dtype):
+    """A short prompt step is bound by its launches: the second time a shape is seen it is captured and from
+    then on replayed.  Same logits as the eager step, bit for bit, with other tokens in other slots each time;
+    a longer shape and an engine with the option off stay eager."""
+    from llmoxide_b200 import LoadOptions
+    from llmoxide_b200.engine.engine import Engine
+
+    folder = folders[("D", dtype)]
+    eager = Engine.load(folder, LoadOptions(dtype=dtype, max_tokens=4096, max_batch=8, graph_prompt_tokens=0))
+    graphed = Engine.load(folder, LoadOptions(dtype=dtype, max_tokens=4096, max_batch=8, graph_prompt_tokens=200))
+    held = []
+    for rep in range(4):
+        ps = prompts(ALL["D"]["vocab_size"], [70, 3, 100], seed=20 + rep)
+        outs = []
+        for eng in (eager, graphed):
+            slots = [eng.acquire() for _ in ps]
+            before = eng.n_steps
+            logits = eng.step(list(zip(slots, ps)), want=[[0, len(p) - 1] for p in ps])
+            outs.append(logits.clone())
+            # one decode step on top, so that the replayed prompt step's cache entries are read back
+            outs.append(eng.step([(s, [7 + rep]) for s in slots]).clone())
+            assert eng.n_steps == before + 2
+            if rep % 2:
+                held.append((eng, slots))          # the next round's pages lie elsewhere
+            else:
+                for s in slots:
+                    eng.release(s)
+        assert torch.equal(outs[0], outs[2]) and torch.equal(outs[1], outs[3]), rep
+        assert len(graphed._prompt_graphs) == (1 if rep >= 1 else 0)
+    graphed.check_status()
+    assert not eager._prompt_graphs
+    # beyond the limit: eager however often it comes back
+    for rep in range(3):
+        slot = graphed.acquire()
+        graphed.step([(slot, prompts(ALL["D"]["vocab_size"], [230], seed=rep)[0])])
+        graphed.release(slot)
+    assert len(graphed._prompt_graphs) == 1
+    for eng, slots in held:
+        for s in slots:
+            eng.release(s)
+    for eng in (eager, graphed):
+        eng.cache.alloc.check_consistent()
+        assert eng.cache.alloc.pages_held() == 0
+
+
 def test_forward_and_wipe(folders):
     folder = folders[("A", "float32")]
     s = _session(folder, "float32")
