@@ -273,8 +273,11 @@ def main() -> int:
     def prefill_point(lengths, profile=False):
         ms = prefill_time(lengths, profile)
         flops = sum(prefill_flops(n) for n in lengths)
+        # (a short prompt step whose shape comes back is replayed as a graph by the engine: say so)
+        graph = bool(eng.options.cuda_graphs and sum(lengths) <= eng.options.graph_prompt_tokens)
         return dict(value=sum(lengths) / ms * 1e3, tokens=sum(lengths), ms=ms,
-                    frac=flops / (ms * 1e-3) / (pk["bf16_tflops"] * 1e12), tflops=flops / (ms * 1e-3) / 1e12)
+                    frac=flops / (ms * 1e-3) / (pk["bf16_tflops"] * 1e12), tflops=flops / (ms * 1e-3) / 1e12,
+                    graph=graph)
 
     prefill = prefill_point([T], profile=args.cuda_profiler == "prefill")
     print(f"[bench] prefill {T} tokens: {prefill['ms']:.2f} ms", file=sys.stderr)
