@@ -183,6 +183,8 @@ class Engine:
         before (a capture costs about two steps, so a shape is captured when it is seen the second time)."""
         if ctx.n_tokens > self.options.graph_prompt_tokens or self.options.overlap_prompt_kernels:
             return False
+        if lay.n_want * self.spec.vocab_size > (1 << 24):
+            return False                 # a graph keeps its logits: not 64 MB and more per shape
         key = self._prompt_key(lay, ctx)
         seen = self._prompt_shapes.pop(key, 0) + 1
         if len(self._prompt_shapes) >= 1024:
