@@ -9,7 +9,7 @@ import pytest
 import torch
 
 import replay_util as ru
-from tiny_configs import ALL, make_folder, prompts
+from tiny_configs import ALL, drawn_config, make_folder, make_folder_of, prompts
 
 pytestmark = pytest.mark.gpu
 
@@ -63,6 +63,31 @@ def test_three_cuttings_match_the_plain_implementation(folders, tmp_path, name, 
         for what, got in results.items():
             for rid in reqs:
                 assert ru.rel_err(got[rid], results["whole"][rid]) <= 2e-6, (what, rid)
+
+
+@pytest.mark.parametrize("seed", range(24))
+def test_drawn_configurations(tmp_path, seed):
+    """Configurations drawn from a seed (head sizes 16 ... 256, widths that are no multiple of 8 or 16, odd
+    vocabularies, windows), in both dtypes: whole, the tail one by one, unequal batches, chunks beside single
+    tokens.  A size a kernel does not take has to be refused or routed to a kernel that does, never computed
+    wrongly."""
+    cfg = drawn_config(seed)
+    print(cfg)
+    toks = prompts(cfg["vocab_size"], [150, 3, 67, 129, 40], seed=seed)
+    reqs = {f"r{i}": t for i, t in enumerate(toks)}
+    for dtype in ("float32", "bfloat16"):
+        folder = make_folder_of(tmp_path, f"drawn{seed}", cfg, dtype)
+        want = ru.expected_logits(folder, reqs)
+        eng = _engine(folder, dtype, max_tokens=2048)
+        for what, steps in (("whole", ru.trace_whole(reqs)),
+                            ("last 32 one by one", ru.trace_tail_decode(reqs, 32)),
+                            ("unequal batches of 3", ru.trace_batches(reqs, 3, 0.6)),
+                            ("chunks of 48 beside single tokens", ru.trace_chunks(reqs, 48, 5, tail=20, mixed=True))):
+            out = tmp_path / f"{dtype}_{what.replace(' ', '_')}"
+            ru.run_in_process(eng, steps, out)
+            got = ru.collect(steps, out, cfg["vocab_size"])
+            ru.assert_matches(got, want, dtype, f"drawn {seed}/{dtype}/{what}")
+        eng.check_status()
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])

@@ -71,6 +71,42 @@ def make_folder(tmp_path, name: str, dtype: str, seed: int = 1234) -> Path:
     return folder
 
 
+def drawn_config(seed: int) -> dict:
+    """A tiny configuration drawn from a seed: every size and option varies, with the awkward values in the
+    draw (head sizes in steps of 16 up to 256, widths that are no multiple of 8, a feed-forward width that
+    is no multiple of 16, odd vocabularies, windows shorter than a page and longer than one)."""
+    import numpy as np
+
+    rng = np.random.default_rng(1000 + seed)
+    pick = lambda xs: xs[int(rng.integers(len(xs)))]
+    kv = pick([1, 2, 3])
+    layers = pick([1, 2, 3])
+    window = pick([None, None, 17, 70, 130])
+    cfg = dict(
+        architectures=["Qwen3ForCausalLM"], model_type="qwen3", num_hidden_layers=layers,
+        hidden_size=pick([72, 100, 136, 200, 264]), num_attention_heads=kv * pick([1, 2, 4]),
+        num_key_value_heads=kv, head_dim=pick([16, 32, 48, 64, 80, 96, 112, 128, 144, 192, 256]),
+        intermediate_size=pick([88, 100, 144, 200, 272]), vocab_size=pick([131, 257, 300, 511]),
+        rope_theta=pick([10000.0, 500000.0, 1000000.0]), rms_norm_eps=pick([1e-6, 1e-5, 3e-6]),
+        tie_word_embeddings=bool(rng.integers(2)), max_position_embeddings=1024,
+        use_sliding_window=window is not None, sliding_window=window, torch_dtype="float32", eos_token_id=1)
+    if window is not None:
+        cfg["layer_types"] = [pick(["full_attention", "sliding_attention"]) for _ in range(layers)]
+    return cfg
+
+
+def make_folder_of(tmp_path, tag: str, cfg: dict, dtype: str, seed: int = 1234) -> Path:
+    """The same for a configuration given as a dictionary."""
+    from llmoxide_b200.config import read_config
+    from llmoxide_b200.weights import write_model_folder
+
+    cfg = dict(cfg, torch_dtype=dtype)
+    folder = Path(tmp_path) / f"tiny_{tag}_{dtype}"
+    if not (folder / "model.safetensors").exists():
+        write_model_folder(folder, read_config(cfg), seed, dtype)
+    return folder
+
+
 def prompts(vocab: int, lengths, seed: int = 0):
     import numpy as np
 
