@@ -49,11 +49,12 @@ def _ptr(t):
 # The current stream's handle without building a torch.cuda.Stream object for every launch (a prompt step of a
 # few tokens launches some 300 kernels and is bound by the host).
 _raw_stream = getattr(torch._C, "_cuda_getCurrentRawStream", None)
+_raw_device = getattr(torch._C, "_cuda_getDevice", None)
 
 
 def _stream():
-    if _raw_stream is not None:
-        return _raw_stream(torch.cuda.current_device())
+    if _raw_stream is not None and _raw_device is not None:
+        return _raw_stream(_raw_device())
     return torch.cuda.current_stream().cuda_stream
 
 
