@@ -52,7 +52,7 @@ class LoadOptions:
     tensor_cores: bool = True
     cuda_graphs: bool = True
     overlap_prompt_kernels: bool = False
-    graph_prompt_tokens: int = 512
+    graph_prompt_tokens: int = 1024
 
 
 class Engine:
