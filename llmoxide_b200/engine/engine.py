@@ -147,6 +147,19 @@ class Engine:
         ctx.probe = probe
         if feed_tokens is not None:
             ctx.tokens.copy_(feed_tokens)      # on the stream, after the step buffer's copy
+        try:
+            logits, replayed = self._run(lay, ctx, entries, probe)
+        except BaseException:
+            # A step that fails after its pages were reserved (out of device memory for its activations, a
+            # kernel's refusal) gives the reservation back: the sequences keep their lengths and stay usable.
+            for slot, _ in entries:
+                self.cache.alloc.unreserve(slot)
+            raise
+        self.cache.alloc.commit_many([slot for slot, _ in entries], [len(toks) for _, toks in entries])
+        self.n_steps += 1
+        return logits, replayed
+
+    def _run(self, lay, ctx, entries, probe):
         graphs = bool(self.options.cuda_graphs and self.model.graph_safe and probe is None)
         replayed = graphs and (ctx.is_decode or self._prompt_shape_came_back(lay, ctx))
         if replayed and ctx.is_decode:
@@ -160,8 +173,6 @@ class Engine:
             logits = self.model.forward(ctx, self.cache)
         else:
             logits = self._ordered_forward(ctx)
-        self.cache.alloc.commit_many([slot for slot, _ in entries], [len(toks) for _, toks in entries])
-        self.n_steps += 1
         return logits, replayed
 
     def _ordered_forward(self, ctx):

@@ -217,6 +217,40 @@ def test_a_prompt_shape_that_comes_back_is_replayed_as_a_graph(folders, dtype):
         assert eng.cache.alloc.pages_held() == 0
 
 
+def test_a_step_that_fails_midway_gives_its_pages_back(folders):
+    """A step that raises after its pages were reserved (here: the forward itself, as when the device runs out
+    of memory for a step's activations) leaves the sequences as they were: same lengths, no page kept beyond
+    them, and the next step gives the logits it would have given."""
+    from llmoxide_b200 import LoadOptions
+    from llmoxide_b200.engine.engine import Engine
+
+    folder = folders[("B", "float32")]
+    eng = Engine.load(folder, LoadOptions(dtype="float32", max_tokens=1024, max_batch=4))
+    toks = prompts(ALL["B"]["vocab_size"], [150, 40], seed=9)
+    want = ru.expected_logits(folder, {"a": toks[0], "b": toks[1]})
+    a, b = eng.acquire(), eng.acquire()
+    eng.step([(a, toks[0][:30]), (b, toks[1][:10])])
+    held = eng.cache.alloc.pages_held()
+    real = eng.model.forward
+
+    def failing(ctx, cache):
+        real(ctx, cache)
+        raise RuntimeError("out of memory, say")
+
+    eng.model.forward = failing
+    with pytest.raises(RuntimeError):
+        eng.step([(a, toks[0][30:]), (b, toks[1][10:])])          # would have taken two more pages for a
+    eng.model.forward = real
+    assert (eng.length(a), eng.length(b)) == (30, 10)
+    assert eng.cache.alloc.pages_held() == held
+    eng.cache.alloc.check_consistent()
+    got = eng.step([(a, toks[0][30:]), (b, toks[1][10:])]).cpu().numpy()
+    assert ru.rel_err(got[0:1], want["a"][-1:]) <= ru.TOL["float32"]
+    assert ru.rel_err(got[1:2], want["b"][-1:]) <= ru.TOL["float32"]
+    eng.release(a), eng.release(b)
+    assert eng.cache.alloc.pages_held() == 0
+
+
 def test_forward_and_wipe(folders):
     folder = folders[("A", "float32")]
     s = _session(folder, "float32")
