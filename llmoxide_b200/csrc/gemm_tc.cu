@@ -847,7 +847,10 @@ static int launch_pair(const CUtensorMap& mw, const CUtensorMap& mx, void* Y, in
     if (cudaOccupancyMaxActiveClusters(&n, kernel, &cfg) != cudaSuccess || n <= 0) n = sm_count() / 2 - 4;
     max_pairs = n;
   }
-  const int pairs = n_units < max_pairs ? (int)n_units : max_pairs;
+  // As many pairs as make the rounds even: 128 units on 74 pairs are two rounds, and two rounds are 64 pairs at
+  // work all the time (the step runs at the power cap: ten idle-waiting pairs fewer leave the others more clock).
+  const long long rounds = (n_units + max_pairs - 1) / max_pairs;
+  const int pairs = (int)((n_units + rounds - 1) / rounds);
   cfg.gridDim = dim3(2 * pairs);
   cfg.numAttrs = 2;
   cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, mw, mx, my, (TY*)Y, T, N, K, ldy, F, stages, row_pairs, token_tiles,
