@@ -361,7 +361,8 @@ def main() -> int:
         for name, lengths in (("prefill_512", [512]), ("prefill_8192", [8192]), ("prefill_16_unequal", lens16)):
             pp = prefill_point(lengths)
             points[name] = pp["value"]
-            details[name] = dict(tokens=pp["tokens"], ms=pp["ms"], frac=pp["frac"], tflops=pp["tflops"])
+            details[name] = dict(tokens=pp["tokens"], ms=pp["ms"], frac=pp["frac"], tflops=pp["tflops"],
+                                 graph=pp["graph"])
 
     line = dict(
         metric="decode tok/s at batch 8 from depth 2048, Qwen3-8B layer sizes, bf16", value=value, unit="tokens/s",
