@@ -39,8 +39,9 @@ class LoadOptions:
     sequence's count rounded up to a multiple of 64; it sizes the cache.
     ``max_batch``: most sequences alive at once (slots).
     ``max_step_tokens``: most tokens one step may bring.
-    ``overlap_prompt_kernels``: let the kernels of a prompt step start before the kernel before them has
-    ended, as those of decode steps always do (off by default; the rule is stated in ``Engine._step``).
+    ``overlap_prompt_kernels``: let the kernels of every prompt step start before the kernel before them has
+    ended, as those of decode steps and of prompt steps of up to 128 tokens always do (off by default; the rule
+    is stated in ``Engine._overlaps``).
     ``graph_prompt_tokens``: prompt steps of up to this many tokens are bound by their ~300 launches, not by
     the GPU; one whose shape comes back is captured as a CUDA graph like a decode step (0: never)."""
 
@@ -168,17 +169,24 @@ class Engine:
             logits = self._graphed_prompt(lay, ctx)
             replayed = logits is not None
             if not replayed:
-                logits = self._ordered_forward(ctx)
-        elif ctx.is_decode or self.options.overlap_prompt_kernels:
-            logits = self.model.forward(ctx, self.cache)
+                logits = self._forward(ctx)
         else:
-            logits = self._ordered_forward(ctx)
+            logits = self._forward(ctx)
         return logits, replayed
 
-    def _ordered_forward(self, ctx):
-        """Rule: the kernels of a prompt step run fully ordered.  They are long, so overlapping a kernel's
-        start with the end of the one before gains nothing measurable, and kernels that hold tensor
-        memory and whole SMs must not wait on one another for resources."""
+    def _overlaps(self, ctx) -> bool:
+        """Rule: the kernels of a step that is long enough for the CTA-pair kernel run fully ordered.  They are
+        long, so overlapping a kernel's start with the end of the one before gains nothing measurable, and
+        kernels that take whole SMs in pairs must not wait on one another for resources.  A shorter prompt
+        step launches what a decode step launches (and the tcgen05 prompt attention, which waits for the
+        kernel before it ahead of its set-up): each of those CTAs that holds tensor memory holds at most 256
+        of the 512 columns and more than a third of an SM's shared memory, so no more than two are ever
+        resident together and no allocation ever has to wait; their starts overlap as in a decode step."""
+        return ctx.is_decode or self.options.overlap_prompt_kernels or ctx.n_tokens <= kernels.PAIR_MIN_TOKENS
+
+    def _forward(self, ctx):
+        if self._overlaps(ctx):
+            return self.model.forward(ctx, self.cache)
         kernels.set_overlap(False)
         try:
             return self.model.forward(ctx, self.cache)
@@ -192,7 +200,7 @@ class Engine:
     def _prompt_shape_came_back(self, lay, ctx) -> bool:
         """Whether this prompt step is short enough to be bound by its launches and has a shape that ran
         before (a capture costs about two steps, so a shape is captured when it is seen the second time)."""
-        if ctx.n_tokens > self.options.graph_prompt_tokens or self.options.overlap_prompt_kernels:
+        if ctx.n_tokens > self.options.graph_prompt_tokens:
             return False
         if lay.n_want * self.spec.vocab_size > (1 << 24):
             return False                 # a graph keeps its logits: not 64 MB and more per shape
@@ -204,8 +212,8 @@ class Engine:
         return seen >= 2
 
     def _graphed_prompt(self, lay, ctx):
-        """The forward of a short prompt step as a replayed graph of fully ordered kernels, or None if it
-        cannot be captured.  The shape ran eagerly before (every library and kernel it needs is loaded), so
+        """The forward of a short prompt step as a replayed graph (of fully ordered kernels where the rule
+        of ``_overlaps`` says so), or None if it cannot be captured.  The shape ran eagerly before (every library and kernel it needs is loaded), so
         nothing runs at capture and state of fixed size advances once, at the replay."""
         key = self._prompt_key(lay, ctx)
         entry = self._prompt_graphs.pop(key, None)
@@ -213,7 +221,7 @@ class Engine:
             torch.cuda.current_stream().synchronize()
             before = kernels.launch_count
             graph = torch.cuda.CUDAGraph()
-            kernels.set_overlap(False)
+            kernels.set_overlap(self._overlaps(ctx))
             try:
                 with torch.cuda.graph(graph, pool=self._graph_pool):
                     logits = self.model.forward(ctx, self.cache)

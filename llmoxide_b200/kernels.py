@@ -494,6 +494,9 @@ def gemm_fma(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> None:
              out.stride(0), _stream()), "gemm_fma")
 
 
+PAIR_MIN_TOKENS = 128      # the CTA-pair kernel (tcgen05 cta_group::2) takes steps of more tokens than this
+
+
 def gemm_tc_supports(x: torch.Tensor, w: torch.Tensor) -> bool:
     """Shapes the tensor-core kernel takes: bfloat16, dense K axis, K and the
     row strides multiples of 8 elements (TMA wants 16-byte strides and starts)."""
@@ -531,7 +534,7 @@ def gemm_tc(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, n_split: int = 
         ldy, stride = N, 0
     assert pair or not accumulate
     if pair:
-        assert T > 128 and scale is None and not (accumulate and n_split > 1)
+        assert T > PAIR_MIN_TOKENS and scale is None and not (accumulate and n_split > 1)
         f = _fn("gemm_tc", "llmx_gemm_tc_pair",
                 [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_longlong, c_longlong, c_longlong, c_int,
                  c_int, c_int, c_longlong, c_void_p])

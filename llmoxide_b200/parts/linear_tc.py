@@ -20,7 +20,7 @@ from .row_scaled import RowScaled
 TILE_ROWS = 128
 CTAS_PER_SM = 2               # what the kernel fits per SM at decode tile sizes
 MIN_KBLOCKS_PER_SPLIT = 4     # 64-element blocks of K per split, at least
-PAIR_MIN_TOKENS = 128         # above this, CTA pairs (tcgen05 cta_group::2) share each token tile
+PAIR_MIN_TOKENS = kernels.PAIR_MIN_TOKENS     # above this, CTA pairs (tcgen05 cta_group::2) share each token tile
 
 
 @lru_cache(maxsize=4096)
