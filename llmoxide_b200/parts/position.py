@@ -21,6 +21,7 @@ class RotaryNeox:
         if self.n_rot % 2:
             raise ValueError(f"n_rot {self.n_rot} must be even")
         self._tables = None
+        self.rotary_tables()        # made when the model is built (tens of milliseconds), not in its first step
 
     def rotary_tables(self):
         if self._tables is None:
