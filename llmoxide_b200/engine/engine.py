@@ -39,9 +39,8 @@ class LoadOptions:
     sequence's count rounded up to a multiple of 64; it sizes the cache.
     ``max_batch``: most sequences alive at once (slots).
     ``max_step_tokens``: most tokens one step may bring.
-    ``overlap_prompt_kernels``: let the kernels of every prompt step start before the kernel before them has
-    ended, as those of decode steps and of prompt steps of up to 128 tokens always do (off by default; the rule
-    is stated in ``Engine._overlaps``).
+    ``overlap_prompt_kernels``: let the kernels of a prompt step start before the kernel before them has
+    ended, as those of decode steps always do (off by default; the rule is stated in ``Engine._overlaps``).
     ``graph_prompt_tokens``: prompt steps of up to this many tokens are bound by their ~300 launches, not by
     the GPU; one whose shape comes back is captured as a CUDA graph like a decode step (0: never)."""
 
@@ -175,14 +174,12 @@ class Engine:
         return logits, replayed
 
     def _overlaps(self, ctx) -> bool:
-        """Rule: the kernels of a step that is long enough for the CTA-pair kernel run fully ordered.  They are
-        long, so overlapping a kernel's start with the end of the one before gains nothing measurable, and
-        kernels that take whole SMs in pairs must not wait on one another for resources.  A shorter prompt
-        step launches what a decode step launches (and the tcgen05 prompt attention, which waits for the
-        kernel before it ahead of its set-up): each of those CTAs that holds tensor memory holds at most 256
-        of the 512 columns and more than a third of an SM's shared memory, so no more than two are ever
-        resident together and no allocation ever has to wait; their starts overlap as in a decode step."""
-        return ctx.is_decode or self.options.overlap_prompt_kernels or ctx.n_tokens <= kernels.PAIR_MIN_TOKENS
+        """Rule: the kernels of a prompt step run fully ordered.  Long steps gain nothing measurable from
+        overlapping a kernel's start with the end of the one before, and kernels that take whole SMs in pairs
+        must not wait on one another for resources.  Steps of up to 128 tokens launch what a decode step
+        launches and would gain a tenth; they stay ordered too, because the one unexplained wrong result of
+        this engine's tests came while they overlapped."""
+        return ctx.is_decode or self.options.overlap_prompt_kernels
 
     def _forward(self, ctx):
         if self._overlaps(ctx):
